@@ -1,0 +1,59 @@
+// Shared declarations for the kernels of libexl3b200.so (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+#include "../../include/exl3_abi.h"
+
+#define EXL3_PAGE 256
+
+struct exl3_graph;
+
+// Per-device state the ops share.  The reference keeps the equivalent in process-wide singletons
+// (kernels/quant/exl3_devctx.cu:26-70); here it is explicit and owned by the caller.
+struct exl3_ctx {
+    int device;
+    int num_sms;
+    size_t ws_bytes;        // general scratch: split-K partials, attention split-KV partials, A_had
+    uint8_t* ws;
+    int* counters;          // arrival counters, all zero between calls
+    int n_counters;
+    int* status;            // device status word (0 = ok)
+    cudaStream_t side_stream;
+    uint64_t launches;
+    int mma_attn;
+    char err[256];
+};
+
+static inline int exl3_fail(exl3_ctx* ctx, int code, const char* msg)
+{
+    if (ctx) { strncpy(ctx->err, msg, sizeof(ctx->err) - 1); ctx->err[sizeof(ctx->err) - 1] = 0; }
+    return code;
+}
+
+#define EXL3_REQUIRE(cond, msg) do { if (!(cond)) return exl3_fail(ctx, EXL3_ERR_INVALID, msg); } while (0)
+
+static inline int exl3_check_launch(exl3_ctx* ctx, const char* what)
+{
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        char buf[256];
+        snprintf(buf, sizeof(buf), "%s: %s", what, cudaGetErrorString(e));
+        cudaGetLastError();
+        return exl3_fail(ctx, EXL3_ERR_CUDA, buf);
+    }
+    return EXL3_OK;
+}
+
+static inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+
+// Carve `bytes` out of the context scratch starting at *off (256-byte aligned); NULL when it does not fit.
+static inline void* exl3_ws_take(exl3_ctx* ctx, size_t* off, size_t bytes)
+{
+    size_t o = (*off + 255) & ~(size_t)255;
+    if (o + bytes > ctx->ws_bytes) return nullptr;
+    *off = o + bytes;
+    return ctx->ws + o;
+}

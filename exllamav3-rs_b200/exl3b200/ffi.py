@@ -1,0 +1,339 @@
+"""ctypes binding of libexl3b200.so with the op names and argument meaning of the reference's safe wrappers
+(src/ffi.rs:209-686).  Tensors are torch CUDA tensors used only as device buffers: each wrapper checks dtype and
+contiguity, derives the shapes the C-ABI needs and passes raw device pointers.  There is no fallback: if the shared
+library is missing or a call returns an error code, an exception is raised.
+"""
+import ctypes as C
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "libexl3b200.so")
+
+ROPE_NONE, ROPE_GPTJ, ROPE_NEOX = 0, 1, 2   # src/ffi.rs:217-219
+
+
+class Exl3Error(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    """Load the shared library (built by exllamav3-rs_b200/build.py).  Raises if it is absent."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise Exl3Error(f"{LIB_PATH} not found: build it with `python exllamav3-rs_b200/build.py` "
+                            "(there is no fallback implementation)")
+        L = C.CDLL(LIB_PATH)
+        L.exl3_version.restype = C.c_char_p
+        L.exl3_last_error.restype = C.c_char_p
+        L.exl3_last_error.argtypes = [C.c_void_p]
+        L.exl3_ctx_create.argtypes = [C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]
+        L.exl3_ctx_destroy.argtypes = [C.c_void_p]
+        L.exl3_ctx_launch_count.restype = C.c_uint64
+        L.exl3_ctx_launch_count.argtypes = [C.c_void_p]
+        L.exl3_cuda_free_mib.restype = C.c_int64
+        L.exl3_graph_new.restype = C.c_void_p
+        L.exl3_graph_new.argtypes = [C.c_void_p]
+        L.exl3_side_stream.restype = C.c_void_p
+        L.exl3_side_stream.argtypes = [C.c_void_p]
+        for n in ("exl3_graph_free", "exl3_graph_capture_begin", "exl3_graph_capture_end", "exl3_graph_replay"):
+            getattr(L, n).argtypes = [C.c_void_p]
+        _lib = L
+    return _lib
+
+
+def _ptr(t):
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _chk(t, dtype, name):
+    if t is None:
+        return
+    if not t.is_cuda:
+        raise Exl3Error(f"{name} must be a CUDA tensor")
+    if dtype is not None and t.dtype not in (dtype if isinstance(dtype, tuple) else (dtype,)):
+        raise Exl3Error(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if not t.is_contiguous():
+        raise Exl3Error(f"{name} must be contiguous")
+
+
+class Ctx:
+    """One context per device: owns the scratch the ops share (split-K partials, counters, status word)."""
+
+    def __init__(self, device=0, workspace_bytes=0):
+        self._h = C.c_void_p()
+        torch.cuda.set_device(device)
+        rc = lib().exl3_ctx_create(device, workspace_bytes, C.byref(self._h))
+        if rc != 0:
+            raise Exl3Error(f"exl3_ctx_create failed with code {rc}")
+        self.device = device
+
+    def close(self):
+        if self._h:
+            lib().exl3_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def stream(self, stream=None):
+        if stream is None:
+            return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        if isinstance(stream, int):
+            return C.c_void_p(stream)
+        return C.c_void_p(stream.cuda_stream)
+
+    def check(self, rc, what):
+        if rc != 0:
+            raise Exl3Error(f"{what} failed ({rc}): {lib().exl3_last_error(self._h).decode()}")
+
+    def poll_status(self, stream=None):
+        self.check(lib().exl3_ctx_poll_status(self._h, self.stream(stream)), "device status")
+
+    def launch_count(self):
+        return int(lib().exl3_ctx_launch_count(self._h))
+
+    # ------------------------------------------------------------------------------------------ EXL3 linear
+    def exl3_gemm(self, a, trellis, c, suh, a_had, svh, mcg=False, mul1=False, stream=None):
+        """src/ffi.rs:274-291.  a [..,k] fp16, trellis [k/16,n/16,16K] int16, c [..,n] fp16|fp32."""
+        _chk(a, torch.float16, "a"); _chk(trellis, torch.int16, "trellis"); _chk(c, (torch.float16, torch.float32), "c")
+        _chk(suh, torch.float16, "suh"); _chk(svh, torch.float16, "svh"); _chk(a_had, torch.float16, "a_had")
+        k = a.shape[-1]
+        m = a.numel() // k
+        n = trellis.shape[1] * 16
+        K = trellis.shape[2] // 16
+        if trellis.shape[0] * 16 != k or c.shape[-1] != n or c.numel() // n != m:
+            raise Exl3Error("exl3_gemm: shape mismatch")
+        rc = lib().exl3_gemm(self._h, self.stream(stream), _ptr(a), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had),
+                             _ptr(svh), m, k, n, K, int(c.dtype == torch.float32), int(mcg), int(mul1))
+        self.check(rc, "exl3_gemm")
+
+    def reconstruct(self, unpacked, packed, K, mcg=False, mul1=False, stream=None):
+        """src/ffi.rs:611-613."""
+        _chk(unpacked, torch.float16, "unpacked"); _chk(packed, torch.int16, "packed")
+        k, n = packed.shape[0] * 16, packed.shape[1] * 16
+        if tuple(unpacked.shape) != (k, n) or packed.shape[2] != 16 * K:
+            raise Exl3Error("reconstruct: shape mismatch")
+        self.check(lib().exl3_reconstruct(self._h, self.stream(stream), _ptr(unpacked), _ptr(packed), k, n, K,
+                                          int(mcg), int(mul1)), "reconstruct")
+
+    def had_r_128(self, x, out, pre_scale=None, post_scale=None, scale=1.0, stream=None):
+        """src/ffi.rs:606-608."""
+        _chk(x, (torch.float16, torch.float32), "x"); _chk(out, x.dtype, "out")
+        _chk(pre_scale, torch.float16, "pre_scale"); _chk(post_scale, torch.float16, "post_scale")
+        cols = x.shape[-1]
+        rows = x.numel() // cols
+        self.check(lib().exl3_had_r_128(self._h, self.stream(stream), _ptr(x), _ptr(out), _ptr(pre_scale),
+                                        _ptr(post_scale), C.c_float(scale), rows, cols,
+                                        int(x.dtype == torch.float32)), "had_r_128")
+
+    def hgemm(self, a, b, c, stream=None):
+        """src/ffi.rs:335-337."""
+        _chk(a, torch.float16, "a"); _chk(b, torch.float16, "b"); _chk(c, (torch.float16, torch.float32), "c")
+        k = a.shape[-1]
+        m = a.numel() // k
+        n = b.shape[1]
+        if b.shape[0] != k or c.shape[-1] != n:
+            raise Exl3Error("hgemm: shape mismatch")
+        self.check(lib().exl3_hgemm(self._h, self.stream(stream), _ptr(a), _ptr(b), _ptr(c), m, k, n,
+                                    int(c.dtype == torch.float32)), "hgemm")
+
+    # ---------------------------------------------------------------------------------------- norm/rope/act
+    def rms_norm(self, x, w, y, eps, constant_bias=0.0, constant_scale=1.0, stream=None):
+        """src/ffi.rs:294-296."""
+        _chk(x, (torch.float16, torch.float32), "x"); _chk(w, torch.float16, "w"); _chk(y, (torch.float16, torch.float32), "y")
+        dim = x.shape[-1]
+        self.check(lib().exl3_rms_norm(self._h, self.stream(stream), _ptr(x), int(x.dtype == torch.float32), _ptr(w),
+                                       _ptr(y), int(y.dtype == torch.float32), C.c_float(eps), C.c_float(constant_bias),
+                                       C.c_float(constant_scale), x.numel() // dim, dim), "rms_norm")
+
+    def rms_norm_res_in(self, x, w, y, r, eps, constant_bias=0.0, constant_scale=1.0, stream=None):
+        """src/ffi.rs:466-468: r += x, y = norm(r)."""
+        _chk(x, (torch.float16, torch.float32), "x"); _chk(w, torch.float16, "w"); _chk(y, (torch.float16, torch.float32), "y")
+        _chk(r, torch.float32, "r")
+        dim = x.shape[-1]
+        self.check(lib().exl3_rms_norm_res_in(self._h, self.stream(stream), _ptr(x), int(x.dtype == torch.float32),
+                                              _ptr(w), _ptr(y), int(y.dtype == torch.float32), _ptr(r), C.c_float(eps),
+                                              C.c_float(constant_bias), C.c_float(constant_scale), x.numel() // dim,
+                                              dim), "rms_norm_res_in")
+
+    def rope(self, q, k, inv_freq, position=0, positions=None, q_norm=None, k_norm=None, norm_eps=1e-6,
+             norm_constant_bias=0.0, rope_mode=ROPE_NEOX, attn_factor=1.0, row_pos=None, stream=None):
+        """src/ffi.rs:301-333; in place on q [bsz,seq,nq,hd] and k [bsz,seq,nk,hd]."""
+        _chk(q, torch.float16, "q"); _chk(k, torch.float16, "k"); _chk(inv_freq, torch.float32, "inv_freq")
+        _chk(positions, torch.int32, "positions"); _chk(row_pos, torch.int32, "row_pos")
+        _chk(q_norm, torch.float16, "q_norm"); _chk(k_norm, torch.float16, "k_norm")
+        bsz, seq, nq, hd = q.shape
+        nk = 0 if k is None else k.shape[2]
+        self.check(lib().exl3_rope(self._h, self.stream(stream), _ptr(q), _ptr(k), _ptr(inv_freq), inv_freq.numel(),
+                                   C.c_uint32(position), _ptr(positions), _ptr(row_pos), _ptr(q_norm), _ptr(k_norm),
+                                   C.c_float(norm_eps), C.c_float(norm_constant_bias), rope_mode,
+                                   C.c_float(attn_factor), bsz, seq, nq, nk, hd), "rope")
+
+    def silu_mul(self, x, y, z, act_limit=0.0, stream=None):
+        """src/ffi.rs:480-482."""
+        _chk(x, torch.float16, "x"); _chk(y, torch.float16, "y"); _chk(z, torch.float16, "z")
+        self.check(lib().exl3_silu_mul(self._h, self.stream(stream), _ptr(x), _ptr(y), _ptr(z), C.c_float(act_limit),
+                                       C.c_int64(x.numel())), "silu_mul")
+
+    def add(self, x, y, z, stream=None):
+        _chk(x, torch.float16, "x"); _chk(y, torch.float16, "y"); _chk(z, torch.float16, "z")
+        self.check(lib().exl3_add(self._h, self.stream(stream), _ptr(x), _ptr(y), _ptr(z), C.c_int64(x.numel())), "add")
+
+    def argmax_sample(self, logits, ids, max_logit=0, stream=None):
+        """src/ffi.rs:560-562; logits [rows,n] fp16|fp32, ids int64 [rows] or [rows,1]."""
+        _chk(logits, (torch.float16, torch.float32), "logits"); _chk(ids, torch.int64, "ids")
+        rows, n = logits.shape
+        self.check(lib().exl3_argmax_sample(self._h, self.stream(stream), _ptr(logits),
+                                            int(logits.dtype == torch.float32), _ptr(ids), rows, n, max_logit),
+                   "argmax_sample")
+
+    def embed(self, ids, table, out, stream=None):
+        _chk(ids, torch.int64, "ids"); _chk(table, torch.float16, "table"); _chk(out, torch.float32, "out")
+        self.check(lib().exl3_embed(self._h, self.stream(stream), _ptr(ids), _ptr(table), _ptr(out), ids.numel(),
+                                    table.shape[1], table.shape[0]), "embed")
+
+    # ------------------------------------------------------------------------------------------------ paged
+    def paged_kv_cache_update(self, k, v, k_cache, v_cache, block_table, cache_seqlens, cu_q=None, stream=None):
+        """src/ffi.rs:346-358.  Rectangular k,v [bsz,seq,nkv,hd]; ragged (cu_q given) k,v [rows,nkv,hd]."""
+        _chk(k, torch.float16, "k"); _chk(v, torch.float16, "v"); _chk(k_cache, torch.float16, "k_cache")
+        _chk(v_cache, torch.float16, "v_cache"); _chk(block_table, torch.int32, "block_table")
+        _chk(cache_seqlens, torch.int32, "cache_seqlens"); _chk(cu_q, torch.int32, "cu_q")
+        bsz, pps = block_table.shape
+        if cu_q is None:
+            seq, nkv, hd = k.shape[1:]
+        else:
+            seq, (nkv, hd) = k.shape[0], k.shape[1:]
+        self.check(lib().exl3_paged_kv_cache_update(self._h, self.stream(stream), _ptr(k), _ptr(v), _ptr(k_cache),
+                                                    _ptr(v_cache), _ptr(block_table), _ptr(cache_seqlens), _ptr(cu_q),
+                                                    bsz, seq, nkv, hd, k_cache.shape[0], pps), "paged_kv_cache_update")
+
+    def bighead_attn_paged(self, q, k, v, k_cache, v_cache, block_table, cache_seqlens, o, kv_chunk_size=256,
+                           causal=True, sm_scale=0.0, cu_q=None, max_q_len=None, stream=None):
+        """src/ffi.rs:361-380.  Rectangular q [bsz,q_len,nq,hd]; ragged (cu_q given) q [rows,nq,hd]."""
+        _chk(q, torch.float16, "q"); _chk(k, torch.float16, "k"); _chk(v, torch.float16, "v")
+        _chk(k_cache, torch.float16, "k_cache"); _chk(v_cache, torch.float16, "v_cache"); _chk(o, torch.float16, "o")
+        _chk(block_table, torch.int32, "block_table"); _chk(cache_seqlens, torch.int32, "cache_seqlens")
+        _chk(cu_q, torch.int32, "cu_q")
+        bsz, pps = block_table.shape
+        if cu_q is None:
+            q_len, nq, hd = q.shape[1:]
+            kv_append = 0 if k is None else k.shape[1]
+        else:
+            nq, hd = q.shape[1:]
+            q_len = max_q_len if max_q_len is not None else q.shape[0]
+            kv_append = q_len
+        nkv = k_cache.shape[2]
+        self.check(lib().exl3_bighead_attn_paged(self._h, self.stream(stream), _ptr(q), _ptr(k), _ptr(v), _ptr(k_cache),
+                                                 _ptr(v_cache), _ptr(block_table), _ptr(cache_seqlens), _ptr(cu_q),
+                                                 _ptr(o), bsz, q_len, kv_append, nq, nkv, hd, k_cache.shape[0], pps,
+                                                 kv_chunk_size, int(causal), C.c_float(sm_scale)), "bighead_attn_paged")
+
+    def bighead_attn_paged_q(self, q, k, v, qk, sk, qv, sv, block_table, cache_seqlens, o, nkv, kv_chunk_size=256,
+                             causal=True, sm_scale=0.0, compand_a=0.0, cu_q=None, max_q_len=None, stream=None):
+        """src/ffi.rs:383-401 against the quantised pools (qk/qv int32 [pages,256,groups*bits], sk/sv fp16)."""
+        _chk(q, torch.float16, "q"); _chk(k, torch.float16, "k"); _chk(v, torch.float16, "v"); _chk(o, torch.float16, "o")
+        _chk(qk, torch.int32, "qk"); _chk(qv, torch.int32, "qv"); _chk(sk, torch.float16, "sk"); _chk(sv, torch.float16, "sv")
+        _chk(block_table, torch.int32, "block_table"); _chk(cache_seqlens, torch.int32, "cache_seqlens")
+        _chk(cu_q, torch.int32, "cu_q")
+        bsz, pps = block_table.shape
+        if cu_q is None:
+            q_len, nq, hd = q.shape[1:]
+            kv_append = 0 if k is None else k.shape[1]
+        else:
+            nq, hd = q.shape[1:]
+            q_len = max_q_len if max_q_len is not None else q.shape[0]
+            kv_append = q_len
+        groups = sk.shape[2]
+        self.check(lib().exl3_bighead_attn_paged_q(self._h, self.stream(stream), _ptr(q), _ptr(k), _ptr(v), _ptr(qk),
+                                                   _ptr(sk), _ptr(qv), _ptr(sv), _ptr(block_table), _ptr(cache_seqlens),
+                                                   _ptr(cu_q), _ptr(o), bsz, q_len, kv_append, nq, nkv, hd, qk.shape[0],
+                                                   pps, qk.shape[2] // groups, qv.shape[2] // groups, kv_chunk_size,
+                                                   int(causal), C.c_float(sm_scale), C.c_float(compand_a)),
+                   "bighead_attn_paged_q")
+
+    def quant_cache_paged(self, k_in, k_out, k_out_scales, v_in, v_out, v_out_scales, cache_seqlens, block_table,
+                          page_size=256, seq_len=None, compand_a=0.0, in_contiguous=True, cu_q=None, stream=None):
+        """src/ffi.rs:616-637."""
+        _chk(k_in, torch.float16, "k_in"); _chk(v_in, torch.float16, "v_in")
+        _chk(k_out, torch.int32, "k_out"); _chk(v_out, torch.int32, "v_out")
+        _chk(k_out_scales, torch.float16, "k_out_scales"); _chk(v_out_scales, torch.float16, "v_out_scales")
+        _chk(cache_seqlens, torch.int32, "cache_seqlens"); _chk(block_table, torch.int32, "block_table")
+        _chk(cu_q, torch.int32, "cu_q")
+        bsz, pps = block_table.shape
+        groups = k_out_scales.shape[2]
+        dim = groups * 32
+        seq = k_in.shape[0] if cu_q is not None else (seq_len if seq_len is not None else k_in.shape[1])
+        self.check(lib().exl3_quant_cache_paged(self._h, self.stream(stream), _ptr(k_in), _ptr(k_out), _ptr(k_out_scales),
+                                                _ptr(v_in), _ptr(v_out), _ptr(v_out_scales), _ptr(cache_seqlens),
+                                                _ptr(block_table), _ptr(cu_q), bsz, seq, dim, k_out.shape[0], pps,
+                                                k_out.shape[2] // groups, v_out.shape[2] // groups, page_size,
+                                                C.c_float(compand_a), int(in_contiguous)), "quant_cache_paged")
+
+    def dequant_cache_paged(self, k_in, k_in_scales, k_out, v_in, v_in_scales, v_out, cache_seqlens, block_table,
+                            page_size=256, sliding_window=0, compand_a=0.0, stream=None):
+        """src/ffi.rs:640-660."""
+        bsz, pps = block_table.shape
+        groups = k_in_scales.shape[2]
+        self.check(lib().exl3_dequant_cache_paged(self._h, self.stream(stream), _ptr(k_in), _ptr(k_in_scales), _ptr(k_out),
+                                                  _ptr(v_in), _ptr(v_in_scales), _ptr(v_out), _ptr(cache_seqlens),
+                                                  _ptr(block_table), bsz, groups * 32, k_in.shape[0], pps,
+                                                  k_in.shape[2] // groups, v_in.shape[2] // groups, page_size,
+                                                  sliding_window, C.c_float(compand_a)), "dequant_cache_paged")
+
+    def dequant_cache_paged_window(self, k_in, k_in_scales, k_out, v_in, v_in_scales, v_out, cache_seqlens, block_table,
+                                   page_size=256, bonus_len=0, compand_a=0.0, stream=None):
+        """src/ffi.rs:663-685."""
+        bsz, pps = block_table.shape
+        groups = k_in_scales.shape[2]
+        self.check(lib().exl3_dequant_cache_paged_window(self._h, self.stream(stream), _ptr(k_in), _ptr(k_in_scales),
+                                                         _ptr(k_out), _ptr(v_in), _ptr(v_in_scales), _ptr(v_out),
+                                                         _ptr(cache_seqlens), _ptr(block_table), bsz, groups * 32,
+                                                         k_in.shape[0], pps, k_in.shape[2] // groups,
+                                                         v_in.shape[2] // groups, page_size, bonus_len,
+                                                         C.c_float(compand_a)), "dequant_cache_paged_window")
+
+
+class CudaGraph:
+    """RAII wrapper like src/ffi.rs:403-451: capture ops launched on ctx.side_stream, then replay."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+        self._g = lib().exl3_graph_new(ctx.handle)
+        if not self._g:
+            raise Exl3Error("exl3_graph_new failed")
+
+    def capture_begin(self):
+        if lib().exl3_graph_capture_begin(C.c_void_p(self._g)) != 0:
+            raise Exl3Error("graph capture_begin failed")
+
+    def capture_end(self):
+        if lib().exl3_graph_capture_end(C.c_void_p(self._g)) != 0:
+            raise Exl3Error("graph capture_end failed")
+
+    def replay(self):
+        if lib().exl3_graph_replay(C.c_void_p(self._g)) != 0:
+            raise Exl3Error("graph replay failed")
+
+    def side_stream(self):
+        return int(lib().exl3_side_stream(self.ctx.handle) or 0)
+
+    def __del__(self):
+        try:
+            if self._g:
+                lib().exl3_graph_free(C.c_void_p(self._g))
+                self._g = None
+        except Exception:
+            pass

@@ -1,0 +1,216 @@
+/*
+ * exl3_abi.h — C-ABI of libexl3b200.so: the EXL3 decode-step ops for NVIDIA B200 (sm_100a).
+ *
+ * This is the drop-in boundary for the reference's op surface: every function below replaces one
+ * `exl3_shim_*` symbol that the reference's Rust side declares in src/ffi.rs:17-203 and implements in
+ * csrc/exl3_shim.cpp.  The op names and semantics are the same; what changes is the calling convention:
+ *
+ *   reference:  void exl3_shim_<op>(void* tensor_handle, ...)      (at::Tensor* handles, libtorch underneath)
+ *   this ABI:   int  exl3_<op>(exl3_ctx*, exl3_stream, <device pointers>, <shapes>, <scalars>)
+ *
+ * Conventions
+ *   - every pointer named below is a DEVICE pointer unless its comment says "host";
+ *   - tensors are dense row-major with the shapes given; fp16 is IEEE binary16 ("half");
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - the return value is 0 on success or a negative EXL3_ERR_* code; nothing throws, nothing calls libtorch,
+ *     cuBLAS or a CPU fallback;
+ *   - buffers are borrowed for the duration of the call (asynchronous work is ordered on `stream`);
+ *   - a context owns the per-device scratch the reference keeps in hidden globals (kernels/quant/exl3_devctx.cu:59-70):
+ *     split-K partial sums, arrival counters, attention split-KV partials, the device status word.
+ *     One context per device per caller thread; calls on one context must be issued from one thread at a time,
+ *     and kernels of two calls that share a context must not overlap on the GPU (use one stream per context).
+ */
+#ifndef EXL3_ABI_H
+#define EXL3_ABI_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define EXL3_API __attribute__((visibility("default")))
+#else
+#define EXL3_API
+#endif
+
+typedef struct exl3_ctx exl3_ctx;
+typedef void* exl3_stream;
+
+enum {
+    EXL3_OK               = 0,
+    EXL3_ERR_INVALID      = -1,   /* bad shape / null pointer / misaligned pointer */
+    EXL3_ERR_UNSUPPORTED  = -2,   /* a (head_dim, GQA ratio, bits, mode) combination that is not built */
+    EXL3_ERR_WORKSPACE    = -3,   /* context scratch too small for this call */
+    EXL3_ERR_CUDA         = -4,   /* a CUDA runtime call failed; see exl3_last_error */
+    EXL3_ERR_DEVICE_WAIT  = -5,   /* a bounded device-side wait ran out (reported by exl3_ctx_poll_status) */
+    EXL3_ERR_NOMEM        = -6
+};
+
+/* rope_mode values, as src/ffi.rs:217-219 / kernels/rope.cuh:6-8 */
+enum { EXL3_ROPE_NONE = 0, EXL3_ROPE_GPTJ = 1, EXL3_ROPE_NEOX = 2 };
+
+/* ------------------------------------------------------------------------------------------------ context */
+
+/* Create the per-device context (allocates scratch with cudaMalloc on `device`).  `workspace_bytes` = 0 picks the
+ * default (64 MiB).  Replaces the reference's DevCtx singleton (kernels/quant/exl3_devctx.cuh:18-40). */
+EXL3_API int  exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** out);
+EXL3_API void exl3_ctx_destroy(exl3_ctx* ctx);
+/* host string describing the last error on this context (never NULL) */
+EXL3_API const char* exl3_last_error(const exl3_ctx* ctx);
+/* Synchronises `stream`, then returns and clears the device status word: 0 or EXL3_ERR_DEVICE_WAIT. */
+EXL3_API int  exl3_ctx_poll_status(exl3_ctx* ctx, exl3_stream stream);
+/* number of kernels this context has launched since creation (for launch accounting in benchmarks) */
+EXL3_API uint64_t exl3_ctx_launch_count(const exl3_ctx* ctx);
+EXL3_API const char* exl3_version(void);
+
+/* ---------------------------------------------------------------------------------------- EXL3 linear ops */
+
+/* exl3_shim_gemm (src/ffi.rs:18-27, csrc/exl3_shim.cpp:44-53 -> kernels/quant/exl3_gemm.cu:110-339).
+ * C[m,n] = H128( fp16(H128(A o suh)/sqrt128) . W ) / sqrt128 o svh, W decoded from `trellis` [k/16, n/16, 16*K] int16.
+ * A [m,k] fp16; C fp16 (c_fp32 = 0) or fp32; suh [k], svh [n] fp16; A_had: scratch of m*k halfs (may be NULL: the
+ * context's scratch is used).  K = bits per weight 1..8; mcg/mul1 select the codebook (both set is an error).
+ * k % 128 == 0, n % 128 == 0.  Returns 0 (the reference returns a kernel tag where 0 and 90 mean success). */
+EXL3_API int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const void* trellis, void* C, const void* suh,
+              void* A_had, const void* svh, int m, int k, int n, int K, int c_fp32, int mcg, int mul1);
+
+/* exl3_shim_reconstruct (src/ffi.rs:162, csrc/exl3_shim.cpp:162-164 -> kernels/quant/reconstruct.cu:375-386).
+ * Dense fp16 W[k,n] from the packed tensor; bit-exact with the reference. */
+EXL3_API int exl3_reconstruct(exl3_ctx* ctx, exl3_stream stream, void* unpacked, const void* trellis, int k, int n, int K,
+                     int mcg, int mul1);
+
+/* exl3_shim_had_r_128 (src/ffi.rs:159-161, csrc/exl3_shim.cpp:157-159 -> kernels/quant/hadamard.cu:88-173).
+ * y = (x.view(-1,128) @ H128) * scale/sqrt(128) with an optional per-column fp16 pre_scale or post_scale [cols].
+ * x,y [rows,cols] both fp16 (fp32 = 0) or both fp32; cols % 128 == 0; in place allowed. */
+EXL3_API int exl3_had_r_128(exl3_ctx* ctx, exl3_stream stream, const void* x, void* y, const void* pre_scale,
+                   const void* post_scale, float scale, int rows, int cols, int fp32);
+
+/* exl3_shim_hgemm (src/ffi.rs:66, csrc/exl3_shim.cpp:93 -> kernels/hgemm.cu:19-78): C[m,n] = A[m,k] . B[k,n],
+ * fp16 inputs, fp32 accumulation, C fp16 or fp32.  k % 64 == 0, n % 8 == 0. */
+EXL3_API int exl3_hgemm(exl3_ctx* ctx, exl3_stream stream, const void* a, const void* b, void* c, int m, int k, int n,
+               int c_fp32);
+
+/* ------------------------------------------------------------------------------------- norm / rope / act */
+
+/* exl3_shim_rms_norm (src/ffi.rs:43-50 -> kernels/norm.cu:313-360). x fp16|fp32 [rows,dim], w fp16 [dim] or NULL,
+ * y fp16|fp32.  y = x * (w + constant_bias) * rsqrt(mean(x^2) + eps) * constant_scale.  dim % 4 == 0. */
+EXL3_API int exl3_rms_norm(exl3_ctx* ctx, exl3_stream stream, const void* x, int x_fp32, const void* w, void* y, int y_fp32,
+                  float eps, float constant_bias, float constant_scale, int rows, int dim);
+
+/* exl3_shim_rms_norm_res_in (src/ffi.rs:114-117 -> kernels/norm.cu RES_IN): r += x (r fp32 [rows,dim], stored),
+ * then y = norm(r) as above. */
+EXL3_API int exl3_rms_norm_res_in(exl3_ctx* ctx, exl3_stream stream, const void* x, int x_fp32, const void* w, void* y,
+                         int y_fp32, float* r, float eps, float constant_bias, float constant_scale, int rows, int dim);
+
+/* exl3_shim_rope (src/ffi.rs:51-65, csrc/exl3_shim.cpp:79-91 -> kernels/rope.cu:279-440).  In place on
+ * q [bsz,seq,nq,hd] and k [bsz,seq,nk,hd] (k may be NULL).  Optional per-head RMSNorm with fp16 weights
+ * q_norm/k_norm [hd] first, then the rotation of the first 2*n_freq dims; token t of sequence b rotates by
+ * position t + positions[b] (positions int32 [bsz], device) or t + position when positions is NULL.
+ * Ragged form: row_seq/row_pos (int32 [rows], device) non-NULL -> q,k are packed [rows,...] (bsz*seq = rows) and row
+ * r rotates by row_pos[r] (positions/position ignored). */
+EXL3_API int exl3_rope(exl3_ctx* ctx, exl3_stream stream, void* q, void* k, const float* inv_freq, int n_freq,
+              uint32_t position, const int32_t* positions, const int32_t* row_pos, const void* q_norm,
+              const void* k_norm, float norm_eps, float norm_constant_bias, int rope_mode, float attn_factor,
+              int bsz, int seq, int nq, int nk, int hd);
+
+/* exl3_shim_silu_mul (src/ffi.rs:125 -> kernels/activation.cu:24-100): z = silu(x) * y in fp16 arithmetic.
+ * act_limit must be 0. */
+EXL3_API int exl3_silu_mul(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* y, void* z, float act_limit,
+                  int64_t numel);
+/* exl3_shim_add (src/ffi.rs:124 -> kernels/add.cu:44-110): z = x + y, fp16. */
+EXL3_API int exl3_add(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* y, void* z, int64_t numel);
+
+/* exl3_shim_argmax_sample (src/ffi.rs:136 -> kernels/generator/sampling_basic.cu:65-172): ids[r] = argmax of
+ * logits[r, 0:max_logit) (max_logit 0 = n), lowest index on ties.  logits fp16 (fp32 = 0) or fp32; ids int64 [rows]. */
+EXL3_API int exl3_argmax_sample(exl3_ctx* ctx, exl3_stream stream, const void* logits, int fp32, int64_t* ids, int rows, int n,
+                       int max_logit);
+
+/* Token embedding gather, fp16 table [vocab,dim] -> fp32 rows (replaces tch index_select + to_kind(Float),
+ * src/modules.rs:430-436).  ids int64 [rows]. */
+EXL3_API int exl3_embed(exl3_ctx* ctx, exl3_stream stream, const int64_t* ids, const void* table, float* out, int rows,
+               int dim, int vocab);
+
+/* ---------------------------------------------------------------------------------------------- paged KV */
+
+/* exl3_shim_paged_kv_cache_update (src/ffi.rs:76-83, csrc/exl3_shim.cpp:101-106 -> kernels/generator/cache.cu:143-243).
+ * Row s of sequence b (k,v [bsz,seq,nkv,hd] fp16) is written at logical position cache_seqlens[b]+s of caches
+ * [pages,256,nkv,hd] through block_table [bsz,pages_per_seq] int32.
+ * Ragged form: cu_q (int32 [bsz+1], device) non-NULL -> k,v are packed [rows,nkv,hd] and sequence b owns rows
+ * [cu_q[b], cu_q[b+1]); `seq` is then only an upper bound on rows per sequence. */
+EXL3_API int exl3_paged_kv_cache_update(exl3_ctx* ctx, exl3_stream stream, const void* k, const void* v, void* k_cache,
+                               void* v_cache, const int32_t* block_table, const int32_t* cache_seqlens,
+                               const int32_t* cu_q, int bsz, int seq, int nkv, int hd, int pages, int pages_per_seq);
+
+/* exl3_shim_bighead_attn_paged (src/ffi.rs:84-96, csrc/exl3_shim.cpp:110-118 -> kernels/attention.cu:1716-2075).
+ * Appends k,v (as above; kv_append may be 0 with k = v = NULL) then computes causal GQA attention of
+ * q [bsz,q_len,nq,hd] over the first cache_seqlens[b]+kv_append cached keys; query i sees keys
+ * j <= total - q_len + i.  sm_scale 0 = 1/sqrt(hd).  o like q.  kv_chunk_size is accepted and ignored (split sizes
+ * are derived on the device from the real lengths).
+ * Ragged form: cu_q non-NULL -> q,o [rows,nq,hd], k,v [rows,nkv,hd] packed, q_len(b) = kv_append(b) = cu_q[b+1]-cu_q[b],
+ * `q_len` is an upper bound on rows per sequence. */
+EXL3_API int exl3_bighead_attn_paged(exl3_ctx* ctx, exl3_stream stream, const void* q, const void* k, const void* v,
+                            void* k_cache, void* v_cache, const int32_t* block_table, const int32_t* cache_seqlens,
+                            const int32_t* cu_q, void* o, int bsz, int q_len, int kv_append, int nq, int nkv, int hd,
+                            int pages, int pages_per_seq, int kv_chunk_size, int causal, float sm_scale);
+
+/* exl3_shim_bighead_attn_paged_q (src/ffi.rs:97-113, csrc/exl3_shim.cpp:122-129 -> kernels/attention.cu:2086-2290).
+ * Same against the quantised pools: qk/qv [pages,256,groups*bits] int32, sk/sv [pages,256,groups] fp16,
+ * groups = nkv*hd/32.  Fresh rows are quantised in first.  compand_a must be 0. */
+EXL3_API int exl3_bighead_attn_paged_q(exl3_ctx* ctx, exl3_stream stream, const void* q, const void* k, const void* v, void* qk,
+                              void* sk, void* qv, void* sv, const int32_t* block_table, const int32_t* cache_seqlens,
+                              const int32_t* cu_q, void* o, int bsz, int q_len, int kv_append, int nq, int nkv, int hd,
+                              int pages, int pages_per_seq, int k_bits, int v_bits, int kv_chunk_size, int causal,
+                              float sm_scale, float compand_a);
+
+/* exl3_shim_quant_cache_paged (src/ffi.rs:141-146, csrc/exl3_shim.cpp:231-240 -> kernels/cache/q_cache.cu:146-258).
+ * k_in,v_in [bsz,seq,nkv*hd] fp16 contiguous (in_contiguous must be 1) -> codes/scales at cache_seqlens[b]+s.
+ * page_size must be 256; bits 2..8; compand_a must be 0.  cu_q: ragged form as above. */
+EXL3_API int exl3_quant_cache_paged(exl3_ctx* ctx, exl3_stream stream, const void* k_in, void* k_out, void* k_out_scales,
+                           const void* v_in, void* v_out, void* v_out_scales, const int32_t* cache_seqlens,
+                           const int32_t* block_table, const int32_t* cu_q, int bsz, int seq, int dim, int pages,
+                           int pages_per_seq, int k_bits, int v_bits, int page_size, float compand_a,
+                           int in_contiguous);
+
+/* exl3_shim_dequant_cache_paged (src/ffi.rs:147-152 -> kernels/cache/q_cache.cu:271-350): tokens [0, cache_seqlens[b])
+ * of every sequence are dequantised into fp16 pools k_out/v_out [pages,256,dim] at their physical positions.
+ * sliding_window > 0 may skip tokens older than the window. */
+EXL3_API int exl3_dequant_cache_paged(exl3_ctx* ctx, exl3_stream stream, const void* k_in, const void* k_in_scales, void* k_out,
+                             const void* v_in, const void* v_in_scales, void* v_out, const int32_t* cache_seqlens,
+                             const int32_t* block_table, int bsz, int dim, int pages, int pages_per_seq, int k_bits,
+                             int v_bits, int page_size, int sliding_window, float compand_a);
+
+/* exl3_shim_dequant_cache_paged_window (src/ffi.rs:153-158 -> kernels/cache/q_cache.cu:352-435): as above but page p
+ * of sequence b is written compactly at scratch page b*pages_per_seq+p, tokens [0, cache_seqlens[b]+bonus_len). */
+EXL3_API int exl3_dequant_cache_paged_window(exl3_ctx* ctx, exl3_stream stream, const void* k_in, const void* k_in_scales,
+                                    void* k_out, const void* v_in, const void* v_in_scales, void* v_out,
+                                    const int32_t* cache_seqlens, const int32_t* block_table, int bsz, int dim,
+                                    int pages, int pages_per_seq, int k_bits, int v_bits, int page_size,
+                                    int bonus_len, float compand_a);
+
+/* ------------------------------------------------------------------------------- graphs, streams, memory */
+
+/* exl3_graph_* (src/ffi.rs:193-197, csrc/exl3_shim.cpp:287-344): capture on the context's side stream and replay.
+ * capture_begin switches capture on for the side stream (returned by exl3_side_stream); launch ops on it, then
+ * capture_end.  All return 0 on success, 1 on failure like the reference. */
+typedef struct exl3_graph exl3_graph;
+EXL3_API exl3_graph* exl3_graph_new(exl3_ctx* ctx);
+EXL3_API void exl3_graph_free(exl3_graph* g);
+EXL3_API int  exl3_graph_capture_begin(exl3_graph* g);
+EXL3_API int  exl3_graph_capture_end(exl3_graph* g);
+EXL3_API int  exl3_graph_replay(exl3_graph* g);
+/* exl3_use_side_stream / exl3_sync_side_stream (src/ffi.rs:198-199): the side stream handle, and a host sync on it */
+EXL3_API exl3_stream exl3_side_stream(exl3_ctx* ctx);
+EXL3_API int  exl3_sync_side_stream(exl3_ctx* ctx);
+/* exl3_empty_cache (src/ffi.rs:200): nothing is cached by this library; kept for surface compatibility (no-op). */
+EXL3_API void exl3_empty_cache(void);
+/* exl3_cuda_free_mib (src/ffi.rs:202, csrc/exl3_shim.cpp:308-312): free device memory in MiB, -1 on error */
+EXL3_API int64_t exl3_cuda_free_mib(void);
+/* exl3_shim_set_mma_attn (src/ffi.rs:201): 1 = tensor-core attention kernels (default), 0 = scalar kernels for A/B */
+EXL3_API void exl3_set_mma_attn(exl3_ctx* ctx, int on);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXL3_ABI_H */

@@ -1,0 +1,242 @@
+"""numpy front end of the CPU oracle (oracle.c).  TEST INFRASTRUCTURE ONLY.
+
+Only the tests, the smoke check and the benchmark's CPU-baseline leg import this module; the product library never
+does.  Arrays are numpy: fp16 tensors as ``np.float16``, trellis tensors as ``np.int16`` of shape
+``[k/16, n/16, 16*K]``, quantised-KV codes as ``np.uint32``/``np.int32``, block tables and lengths as ``np.int32``.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "liboracle.so")
+
+
+def build(force=False):
+    src = os.path.join(_HERE, "oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
+    return _SO
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        _lib.orc_decode_state.restype = C.c_uint16
+        _lib.orc_decode_state.argtypes = [C.c_int, C.c_uint32]
+        _lib.orc_tile_state.restype = C.c_uint32
+        _lib.orc_num_threads.restype = C.c_int
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    a = np.ascontiguousarray(a)
+    assert a.dtype == dt, (a.dtype, dt)
+    return a
+
+
+def num_threads():
+    return lib().orc_num_threads()
+
+
+def codebook(cb):
+    """All 65536 decoded fp16 values of codebook cb (0 3INST, 1 MCG, 2 MUL1)."""
+    L = lib()
+    return np.array([L.orc_decode_state(cb, s) for s in range(65536)], dtype=np.uint16).view(np.float16)
+
+
+def reconstruct(trellis, K, cb):
+    trellis = _c(trellis, np.int16)
+    tk, tn, w = trellis.shape
+    assert w == 16 * K
+    out = np.empty((tk * 16, tn * 16), np.float16)
+    lib().orc_reconstruct(_p(out), _p(trellis), C.c_int(tk * 16), C.c_int(tn * 16), C.c_int(K), C.c_int(cb))
+    return out
+
+
+def had_r_128(x, pre=None, post=None, scale=1.0, out_dtype=None):
+    """scale multiplies 1/sqrt(128) as in the reference (hadamard.cu:106)."""
+    scale = float(np.float32(scale) * np.float32(0.088388347648))
+    x = np.ascontiguousarray(x)
+    out_dtype = out_dtype or x.dtype
+    rows = int(np.prod(x.shape[:-1]))
+    cols = x.shape[-1]
+    y = np.empty(x.shape, out_dtype)
+    pre = None if pre is None else _c(pre, np.float16)
+    post = None if post is None else _c(post, np.float16)
+    lib().orc_had_r_128(_p(x), _p(y), _p(pre), _p(post), C.c_float(scale), C.c_int64(rows), C.c_int64(cols),
+                        C.c_int(x.dtype == np.float32), C.c_int(out_dtype == np.float32))
+    return y
+
+
+def exl3_gemm(A, trellis, suh, svh, K, cb, c_fp32=False):
+    A = _c(A, np.float16)
+    trellis = _c(trellis, np.int16)
+    m = int(np.prod(A.shape[:-1]))
+    k = A.shape[-1]
+    n = trellis.shape[1] * 16
+    assert trellis.shape[0] * 16 == k and trellis.shape[2] == 16 * K
+    Cm = np.empty(A.shape[:-1] + (n,), np.float32 if c_fp32 else np.float16)
+    suh = None if suh is None else _c(suh, np.float16)
+    svh = None if svh is None else _c(svh, np.float16)
+    lib().orc_exl3_gemm(_p(A), _p(trellis), _p(Cm), C.c_int(c_fp32), _p(suh), _p(svh), C.c_int(m), C.c_int(k),
+                        C.c_int(n), C.c_int(K), C.c_int(cb))
+    return Cm
+
+
+def hgemm(A, B, c_fp32=False):
+    A = _c(A, np.float16)
+    B = _c(B, np.float16)
+    m, k = A.shape
+    n = B.shape[1]
+    Cm = np.empty((m, n), np.float32 if c_fp32 else np.float16)
+    lib().orc_hgemm(_p(A), _p(B), _p(Cm), C.c_int(c_fp32), C.c_int(m), C.c_int(k), C.c_int(n))
+    return Cm
+
+
+def rms_norm(x, w, eps, cbias=0.0, cscale=1.0, res=None, out_dtype=np.float16):
+    """res (fp32, same shape) is updated in place with res += x before the norm (RES_IN)."""
+    x = np.ascontiguousarray(x)
+    dim = x.shape[-1]
+    rows = x.size // dim
+    y = np.empty(x.shape, out_dtype)
+    w = None if w is None else _c(w, np.float16)
+    if res is not None:
+        assert res.dtype == np.float32 and res.flags.c_contiguous
+    lib().orc_rms_norm(_p(x), C.c_int(x.dtype == np.float32), _p(w), _p(y), C.c_int(out_dtype == np.float32), _p(res),
+                       C.c_float(eps), C.c_float(cbias), C.c_float(cscale), C.c_int(rows), C.c_int(dim))
+    return y
+
+
+def rope(q, k, inv_freq, position=0, positions=None, q_norm=None, k_norm=None, norm_eps=1e-6, norm_cbias=0.0,
+         rope_mode=2, attn_factor=1.0):
+    """q [bsz,seq,nq,hd], k [bsz,seq,nk,hd] fp16; returns rotated copies."""
+    q = _c(q, np.float16).copy()
+    k = None if k is None else _c(k, np.float16).copy()
+    inv_freq = _c(inv_freq, np.float32)
+    bsz, seq, nq, hd = q.shape
+    nk = 0 if k is None else k.shape[2]
+    positions = None if positions is None else _c(positions, np.int32)
+    lib().orc_rope(_p(q), _p(k), _p(inv_freq), C.c_int(inv_freq.size), C.c_uint32(position), _p(positions),
+                   _p(None if q_norm is None else _c(q_norm, np.float16)),
+                   _p(None if k_norm is None else _c(k_norm, np.float16)), C.c_float(norm_eps), C.c_float(norm_cbias),
+                   C.c_int(rope_mode), C.c_float(attn_factor), C.c_int(bsz), C.c_int(seq), C.c_int(nq), C.c_int(nk),
+                   C.c_int(hd))
+    return q, k
+
+
+def silu_mul(x, y):
+    x = _c(x, np.float16)
+    y = _c(y, np.float16)
+    z = np.empty_like(x)
+    lib().orc_silu_mul(_p(x), _p(y), _p(z), C.c_int64(x.size))
+    return z
+
+
+def add(x, y):
+    x = _c(x, np.float16)
+    y = _c(y, np.float16)
+    z = np.empty_like(x)
+    lib().orc_add(_p(x), _p(y), _p(z), C.c_int64(x.size))
+    return z
+
+
+def argmax(logits):
+    logits = np.ascontiguousarray(logits)
+    rows, n = logits.shape
+    ids = np.empty(rows, np.int64)
+    lib().orc_argmax(_p(logits), C.c_int(logits.dtype == np.float32), _p(ids), C.c_int(rows), C.c_int(n))
+    return ids
+
+
+def embed(ids, table):
+    ids = _c(ids, np.int64)
+    table = _c(table, np.float16)
+    out = np.empty((ids.size, table.shape[1]), np.float32)
+    lib().orc_embed(_p(ids), _p(table), _p(out), C.c_int(ids.size), C.c_int(table.shape[1]))
+    return out
+
+
+def paged_kv_update(k, v, kc, vc, block_table, seqlens):
+    """k,v [bsz,seq,nkv,hd]; kc,vc [pages,256,nkv,hd] updated in place."""
+    k = _c(k, np.float16)
+    v = _c(v, np.float16)
+    bsz, seq, nkv, hd = k.shape
+    bt = _c(block_table, np.int32)
+    lib().orc_paged_kv_update(_p(k), _p(v), _p(kc), _p(vc), _p(bt), _p(_c(seqlens, np.int32)), C.c_int(bsz),
+                              C.c_int(seq), C.c_int(nkv), C.c_int(hd), C.c_int(bt.shape[1]))
+
+
+def quant_groups(x, bits):
+    x = _c(x, np.float16)
+    groups = x.size // 32
+    q = np.empty((groups, bits), np.uint32)
+    s = np.empty(groups, np.float16)
+    lib().orc_quant_groups(_p(x), _p(q), _p(s), C.c_int64(groups), C.c_int(bits))
+    return q, s
+
+
+def dequant_groups(q, s, bits):
+    q = _c(q, np.uint32)
+    s = _c(s, np.float16)
+    out = np.empty(s.size * 32, np.float16)
+    lib().orc_dequant_groups(_p(q), _p(s), _p(out), C.c_int64(s.size), C.c_int(bits))
+    return out
+
+
+def quant_cache_paged(k_in, qk, sk, v_in, qv, sv, seqlens, block_table, k_bits, v_bits):
+    """k_in,v_in [bsz,seq,nkv,hd]; qk/qv [pages,256,groups*bits] uint32, sk/sv [pages,256,groups] fp16, in place."""
+    k_in = _c(k_in, np.float16)
+    v_in = _c(v_in, np.float16)
+    bsz, seq = k_in.shape[:2]
+    dim = k_in.shape[2] * k_in.shape[3]
+    bt = _c(block_table, np.int32)
+    lib().orc_quant_cache_paged(_p(k_in), _p(qk), _p(sk), _p(v_in), _p(qv), _p(sv), _p(_c(seqlens, np.int32)), _p(bt),
+                                C.c_int(bsz), C.c_int(seq), C.c_int(dim), C.c_int(bt.shape[1]), C.c_int(k_bits),
+                                C.c_int(v_bits))
+
+
+def dequant_cache_paged(qk, sk, k_out, qv, sv, v_out, seqlens, block_table, k_bits, v_bits, compact=False, bonus=0):
+    bt = _c(block_table, np.int32)
+    dim = sk.shape[-1] * 32
+    lib().orc_dequant_cache_paged(_p(qk), _p(sk), _p(k_out), _p(qv), _p(sv), _p(v_out), _p(_c(seqlens, np.int32)),
+                                  _p(bt), C.c_int(bt.shape[0]), C.c_int(dim), C.c_int(bt.shape[1]), C.c_int(k_bits),
+                                  C.c_int(v_bits), C.c_int(compact), C.c_int(bonus))
+
+
+def attn_paged(q, kc, vc, block_table, seqlens, kv_append=None, causal=True, sm_scale=0.0, cu_q=None, nkv=None,
+               quant=None):
+    """Rectangular: q [bsz,q_len,nq,hd].  Ragged: q [rows,nq,hd] with cu_q [bsz+1].
+    quant = (qk, sk, qv, sv, bits) selects the quantised pools (kc/vc ignored; nkv must be given)."""
+    q = _c(q, np.float16)
+    bt = _c(block_table, np.int32)
+    bsz = bt.shape[0]
+    if cu_q is None:
+        _, q_len, nq, hd = q.shape
+        kv_append = q_len if kv_append is None else kv_append
+    else:
+        cu_q = _c(cu_q, np.int32)
+        _, nq, hd = q.shape
+        q_len, kv_append = 0, 0
+    if quant is None:
+        nkv = kc.shape[2]
+        qk = sk = qv = sv = None
+        bits = 0
+    else:
+        qk, sk, qv, sv, bits = quant
+    o = np.empty_like(q)
+    lib().orc_attn_paged(_p(q), _p(kc), _p(vc), _p(qk), _p(sk), _p(qv), _p(sv), C.c_int(bits), _p(bt),
+                         _p(_c(seqlens, np.int32)), _p(cu_q), _p(o), C.c_int(bsz), C.c_int(q_len), C.c_int(kv_append),
+                         C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(bt.shape[1]), C.c_int(causal),
+                         C.c_float(sm_scale))
+    return o

@@ -1,0 +1,248 @@
+// exl3_bighead_attn_paged / exl3_bighead_attn_paged_q: planning, launch and split-KV combine.
+#include "attn_paged.cuh"
+
+namespace {
+
+using namespace exl3;
+
+// Builds the split-KV work list from the REAL sequence lengths (one CTA; bsz is small next to the KV walk).
+// Each sequence gets ceil(total_k / chunk) splits per row block, with chunk sized so that the list has about
+// `target_items` entries; the reference sizes its splits from the padded block-table width instead
+// (kernels/attention.cu:1805), which launches empty CTAs for the short sequences of a ragged batch.
+__global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restrict__ seqlens,
+                                                         const int32_t* __restrict__ cu_q, int bsz, int q_len,
+                                                         int kv_append, int G, int rows_per_cta, int target_items,
+                                                         int max_items, AttnPlan* plan, AttnItem* items, int* seq_base,
+                                                         int* seq_splits)
+{
+    __shared__ long long s_total;
+    __shared__ int s_scan[1024];
+    __shared__ int s_carry, s_chunk;
+    const int tid = threadIdx.x;
+    if (tid == 0) { s_total = 0; s_carry = 0; }
+    __syncthreads();
+    long long local = 0;
+    for (int b = tid; b < bsz; b += 1024) {
+        const int ql = cu_q ? cu_q[b + 1] - cu_q[b] : q_len;
+        const int tk = seqlens[b] + (cu_q ? ql : kv_append);
+        const int rb = (ql * G + rows_per_cta - 1) / rows_per_cta;
+        local += (long long)tk * rb;
+    }
+    atomicAdd((unsigned long long*)&s_total, (unsigned long long)local);
+    __syncthreads();
+    if (tid == 0) {
+        long long c = (s_total + target_items - 1) / target_items;
+        c = (c + AT_TK - 1) / AT_TK * AT_TK;
+        if (c < 256) c = 256;
+        if (c > (1 << 30)) c = 1 << 30;
+        s_chunk = (int)c;
+    }
+    __syncthreads();
+    const int chunk = s_chunk;
+    for (int b0 = 0; b0 < bsz; b0 += 1024) {
+        const int b = b0 + tid;
+        int ql = 0, tk = 0, rb = 0, sp = 0;
+        if (b < bsz) {
+            ql = cu_q ? cu_q[b + 1] - cu_q[b] : q_len;
+            tk = seqlens[b] + (cu_q ? ql : kv_append);
+            rb = (ql * G + rows_per_cta - 1) / rows_per_cta;
+            sp = tk > 0 ? (tk + chunk - 1) / chunk : 1;
+        }
+        const int cnt = rb * sp;
+        s_scan[tid] = cnt;
+        __syncthreads();
+        for (int o = 1; o < 1024; o <<= 1) {                   // inclusive Hillis-Steele scan
+            int v = tid >= o ? s_scan[tid - o] : 0;
+            __syncthreads();
+            s_scan[tid] += v;
+            __syncthreads();
+        }
+        const int base = s_carry + s_scan[tid] - cnt;
+        if (b < bsz) {
+            seq_base[b] = base;
+            seq_splits[b] = sp;
+            for (int j = 0; j < cnt && base + j < max_items; ++j) {
+                AttnItem it; it.b = b; it.rb = j / sp; it.split = j % sp; it.pad = 0;
+                items[base + j] = it;
+            }
+        }
+        __syncthreads();
+        if (tid == 1023) s_carry += s_scan[1023];
+        __syncthreads();
+    }
+    if (tid == 0) {
+        plan->n_items = s_carry < max_items ? s_carry : max_items;
+        plan->chunk = chunk;
+    }
+}
+
+// Merges the split-KV partials of one output row (b, query, head); one warp per row, lane = D/32 dims.
+template <int D>
+__global__ void __launch_bounds__(256) attn_combine_kernel(const AttnParams p, int rows_per_cta, int total_rows)
+{
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (w >= (long long)total_rows * p.nq) return;
+    const int row = (int)(w / p.nq), head = (int)(w % p.nq);
+    int b;
+    if (p.cu_q) {                                              // binary search: cu_q[b] <= row < cu_q[b+1]
+        int lo = 0, hi = p.bsz - 1;
+        while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (p.cu_q[mid] <= row) lo = mid; else hi = mid - 1; }
+        b = lo;
+    } else b = row / p.q_len;
+    const int splits = p.seq_splits[b];
+    if (splits <= 1) return;                                   // the attention kernel wrote the final value itself
+    const int row_base = p.cu_q ? p.cu_q[b] : b * p.q_len;
+    const int G = p.nq / p.nkv, kvh = head / G;
+    const int packed = (row - row_base) * G + (head - kvh * G);
+    const int rb = packed / rows_per_cta, lr = packed - rb * rows_per_cta;
+    const int item0 = p.seq_base[b] + rb * splits;
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s)
+        mm = fmaxf(mm, p.partial[(((size_t)(item0 + s) * p.nkv + kvh) * rows_per_cta + lr) * (D + 2) + D]);
+    float acc[D / 32], ll = 0.f;
+    #pragma unroll
+    for (int e = 0; e < D / 32; ++e) acc[e] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float* pp = p.partial + (((size_t)(item0 + s) * p.nkv + kvh) * rows_per_cta + lr) * (D + 2);
+        const float ms = pp[D];
+        const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+        ll += pp[D + 1] * sc;
+        #pragma unroll
+        for (int e = 0; e < D / 32; ++e) acc[e] += pp[lane * (D / 32) + e] * sc;
+    }
+    const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+    half* op = p.o + ((size_t)row * p.nq + head) * D + lane * (D / 32);
+    #pragma unroll
+    for (int e = 0; e < D / 32; e += 2) *reinterpret_cast<uint32_t*>(op + e) = pack_h2(acc[e] * inv, acc[e + 1] * inv);
+}
+
+template <int D, int WM, int WN, bool QUANT>
+cudaError_t launch_attn(const AttnParams& p, dim3 grid, cudaStream_t st)
+{
+    constexpr int bytes = AttnSmem<D, QUANT>::BYTES;
+    auto kern = attn_paged_kernel<D, WM, WN, QUANT>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kern<<<grid, AT_THREADS, bytes, st>>>(p);
+    return cudaPeekAtLastError();
+}
+
+int attn_impl(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int max_q_len, bool quant)
+{
+    const int D = 128;
+    const int G = p.nq / p.nkv;
+    const bool decode_shape = max_q_len * G <= 16;            // one 16-row tile: spread the keys over the 4 warps
+    const int rows_per_cta = decode_shape ? 16 : 64;
+    const int rb_max = (max_q_len * G + rows_per_cta - 1) / rows_per_cta;
+    const int grid_x = (ctx->num_sms * 3 + p.nkv - 1) / p.nkv;    // about 3 resident CTAs per SM over all kv heads
+    const int target_items = grid_x * 2;
+    const int max_items = target_items + p.bsz * rb_max + 1;
+
+    size_t off = 0;
+    AttnPlan* plan = (AttnPlan*)exl3_ws_take(ctx, &off, sizeof(AttnPlan));
+    AttnItem* items = (AttnItem*)exl3_ws_take(ctx, &off, (size_t)max_items * sizeof(AttnItem));
+    int* seq_base = (int*)exl3_ws_take(ctx, &off, (size_t)p.bsz * 4);
+    int* seq_splits = (int*)exl3_ws_take(ctx, &off, (size_t)p.bsz * 4);
+    float* partial = (float*)exl3_ws_take(ctx, &off, (size_t)max_items * p.nkv * rows_per_cta * (D + 2) * 4);
+    if (!plan || !items || !seq_base || !seq_splits || !partial)
+        return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "attention: context scratch too small for the split-KV partials");
+    p.plan = plan; p.items = items; p.seq_base = seq_base; p.seq_splits = seq_splits; p.partial = partial;
+
+    attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, target_items,
+                                          max_items, plan, items, seq_base, seq_splits);
+    ctx->launches++;
+    dim3 grid(grid_x, p.nkv);
+    cudaError_t e;
+    if (quant) e = decode_shape ? launch_attn<128, 1, 4, true>(p, grid, st) : launch_attn<128, 4, 1, true>(p, grid, st);
+    else       e = decode_shape ? launch_attn<128, 1, 4, false>(p, grid, st) : launch_attn<128, 4, 1, false>(p, grid, st);
+    ctx->launches++;
+    if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
+    const long long warps = (long long)total_rows * p.nq;
+    attn_combine_kernel<128><<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(p, rows_per_cta, total_rows);
+    ctx->launches++;
+    return exl3_check_launch(ctx, "attention");
+}
+
+int check_common(exl3_ctx* ctx, const void* q, const void* o, const int32_t* bt, const int32_t* sl, int bsz, int q_len,
+                 int kv_append, int nq, int nkv, int hd, int pages, int pps)
+{
+    EXL3_REQUIRE(ctx && q && o && bt && sl, "attention: null argument");
+    EXL3_REQUIRE(bsz >= 0 && q_len >= 0 && kv_append >= 0 && nq > 0 && nkv > 0 && pages > 0 && pps > 0, "attention: bad shape");
+    EXL3_REQUIRE(nq % nkv == 0, "attention: n_q_heads must be a multiple of n_kv_heads");
+    EXL3_REQUIRE(nq / nkv <= 16, "attention: GQA ratio above 16");
+    if (hd != 128) return exl3_fail(ctx, EXL3_ERR_UNSUPPORTED, "attention: head_dim must be 128");
+    EXL3_REQUIRE(nkv <= 65535, "attention: too many kv heads");
+    EXL3_REQUIRE(aligned16(q) && aligned16(o), "attention: pointers must be 16-byte aligned");
+    return EXL3_OK;
+}
+
+}  // namespace
+
+extern "C" int exl3_bighead_attn_paged(exl3_ctx* ctx, exl3_stream stream, const void* q, const void* k, const void* v,
+                                       void* k_cache, void* v_cache, const int32_t* block_table,
+                                       const int32_t* cache_seqlens, const int32_t* cu_q, void* o, int bsz, int q_len,
+                                       int kv_append, int nq, int nkv, int hd, int pages, int pages_per_seq,
+                                       int kv_chunk_size, int causal, float sm_scale)
+{
+    (void)kv_chunk_size;
+    int rc = check_common(ctx, q, o, block_table, cache_seqlens, bsz, q_len, kv_append, nq, nkv, hd, pages, pages_per_seq);
+    if (rc) return rc;
+    EXL3_REQUIRE(k_cache && v_cache && aligned16(k_cache) && aligned16(v_cache), "attention: bad cache pointers");
+    if (bsz == 0 || q_len == 0) return EXL3_OK;
+    const int append = cu_q ? q_len : kv_append;
+    if (append > 0) {
+        EXL3_REQUIRE(k && v, "attention: kv_append > 0 needs k and v");
+        rc = exl3_paged_kv_cache_update(ctx, stream, k, v, k_cache, v_cache, block_table, cache_seqlens, cu_q, bsz, append,
+                                        nkv, hd, pages, pages_per_seq);
+        if (rc) return rc;
+    }
+    AttnParams p;
+    memset(&p, 0, sizeof(p));
+    p.q = (const half*)q; p.o = (half*)o; p.kc = (const half*)k_cache; p.vc = (const half*)v_cache;
+    p.block_table = block_table; p.seqlens = cache_seqlens; p.cu_q = cu_q;
+    p.bsz = bsz; p.q_len = q_len; p.kv_append = kv_append; p.nq = nq; p.nkv = nkv; p.pps = pages_per_seq; p.pages = pages;
+    p.causal = causal;
+    p.scale_log2 = (sm_scale == 0.0f ? rsqrtf((float)hd) : sm_scale) * 1.4426950408889634f;
+    const int total_rows = cu_q ? kv_append : bsz * q_len;
+    return attn_impl(ctx, (cudaStream_t)stream, p, total_rows, q_len, false);
+}
+
+extern "C" int exl3_bighead_attn_paged_q(exl3_ctx* ctx, exl3_stream stream, const void* q, const void* k,
+                                         const void* v, void* qk, void* sk, void* qv, void* sv,
+                                         const int32_t* block_table, const int32_t* cache_seqlens, const int32_t* cu_q,
+                                         void* o, int bsz, int q_len, int kv_append, int nq, int nkv, int hd, int pages,
+                                         int pages_per_seq, int k_bits, int v_bits, int kv_chunk_size, int causal,
+                                         float sm_scale, float compand_a)
+{
+    (void)kv_chunk_size;
+    int rc = check_common(ctx, q, o, block_table, cache_seqlens, bsz, q_len, kv_append, nq, nkv, hd, pages, pages_per_seq);
+    if (rc) return rc;
+    EXL3_REQUIRE(qk && sk && qv && sv, "attention: null quantised pool");
+    EXL3_REQUIRE(k_bits >= 2 && k_bits <= 8 && v_bits >= 2 && v_bits <= 8, "attention: bits must be 2..8");
+    if (compand_a > 0.0f) return exl3_fail(ctx, EXL3_ERR_UNSUPPORTED, "attention: compand_a > 0 is not supported");
+    if (bsz == 0 || q_len == 0) return EXL3_OK;
+    const int append = cu_q ? q_len : kv_append;
+    if (append > 0) {
+        EXL3_REQUIRE(k && v, "attention: kv_append > 0 needs k and v");
+        rc = exl3_quant_cache_paged(ctx, stream, k, qk, sk, v, qv, sv, cache_seqlens, block_table, cu_q, bsz, append,
+                                    nkv * hd, pages, pages_per_seq, k_bits, v_bits, EXL3_PAGE, 0.0f, 1);
+        if (rc) return rc;
+    }
+    AttnParams p;
+    memset(&p, 0, sizeof(p));
+    p.q = (const half*)q; p.o = (half*)o;
+    p.qk = (const uint32_t*)qk; p.sk = (const half*)sk; p.qv = (const uint32_t*)qv; p.sv = (const half*)sv;
+    p.block_table = block_table; p.seqlens = cache_seqlens; p.cu_q = cu_q;
+    p.bsz = bsz; p.q_len = q_len; p.kv_append = kv_append; p.nq = nq; p.nkv = nkv; p.pps = pages_per_seq; p.pages = pages;
+    p.causal = causal; p.k_bits = k_bits; p.v_bits = v_bits;
+    p.scale_log2 = (sm_scale == 0.0f ? rsqrtf((float)hd) : sm_scale) * 1.4426950408889634f;
+    const int total_rows = cu_q ? kv_append : bsz * q_len;
+    return attn_impl(ctx, (cudaStream_t)stream, p, total_rows, q_len, true);
+}

@@ -1,0 +1,160 @@
+// exl3_gemm: host-side dispatch of the fused EXL3 trellis-decode GEMM.
+#include "gemm_small.cuh"
+
+namespace {
+
+using namespace exl3;
+
+// Input transform: a_dup[row][k] = (h, h) with h = fp16(H128(A o suh)/sqrt128), rowsum[row] = sum_k h.
+// One CTA per row; warp w takes 128-blocks w, w+8, ...; the row sum is reduced in a fixed order.
+// Arithmetic as kernels/quant/hadamard_inner.cuh:93-147 (fp16 pre-scale multiply, fp32 butterflies, one fp16 rounding).
+__global__ void __launch_bounds__(256) gemm_prologue_kernel(const half* __restrict__ A, const half* __restrict__ suh,
+                                                            uint32_t* __restrict__ a_dup, float* __restrict__ rowsum,
+                                                            int k)
+{
+    __shared__ float sh[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t row = blockIdx.x;
+    float part = 0.0f;
+    for (int blk = warp; blk < k / 128; blk += 8) {
+        uint2 raw = reinterpret_cast<const uint2*>(A + row * k + blk * 128)[lane];
+        half2 a = *reinterpret_cast<half2*>(&raw.x), b = *reinterpret_cast<half2*>(&raw.y);
+        if (suh) {
+            uint2 sr = reinterpret_cast<const uint2*>(suh + blk * 128)[lane];
+            a = __hmul2(a, *reinterpret_cast<half2*>(&sr.x));
+            b = __hmul2(b, *reinterpret_cast<half2*>(&sr.y));
+        }
+        float v0 = __low2float(a), v1 = __high2float(a), v2 = __low2float(b), v3 = __high2float(b);
+        if (suh) {
+            float s0 = v0 + v1, d0 = v0 - v1, s1 = v2 + v3, d1 = v2 - v3;
+            v0 = s0 + s1; v1 = d0 + d1; v2 = s0 - s1; v3 = d0 - d1;
+            #pragma unroll
+            for (int i = 1; i < 32; i <<= 1) {
+                float p0 = __shfl_xor_sync(0xffffffffu, v0, i), p1 = __shfl_xor_sync(0xffffffffu, v1, i);
+                float p2 = __shfl_xor_sync(0xffffffffu, v2, i), p3 = __shfl_xor_sync(0xffffffffu, v3, i);
+                const bool up = lane & i;
+                v0 = (up ? -v0 : v0) + p0; v1 = (up ? -v1 : v1) + p1;
+                v2 = (up ? -v2 : v2) + p2; v3 = (up ? -v3 : v3) + p3;
+            }
+            v0 *= GS_R128; v1 *= GS_R128; v2 *= GS_R128; v3 *= GS_R128;
+        }
+        const uint32_t h0 = __half_as_ushort(__float2half_rn(v0)), h1 = __half_as_ushort(__float2half_rn(v1));
+        const uint32_t h2 = __half_as_ushort(__float2half_rn(v2)), h3 = __half_as_ushort(__float2half_rn(v3));
+        uint4 o = make_uint4(h0 * 0x10001u, h1 * 0x10001u, h2 * 0x10001u, h3 * 0x10001u);
+        reinterpret_cast<uint4*>(a_dup + row * k + blk * 128)[lane] = o;
+        part += __half2float(__ushort_as_half((unsigned short)h0)) + __half2float(__ushort_as_half((unsigned short)h1)) +
+                __half2float(__ushort_as_half((unsigned short)h2)) + __half2float(__ushort_as_half((unsigned short)h3));
+    }
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) sh[warp] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+        for (int w = 0; w < 8; ++w) s += sh[w];
+        rowsum[row] = s;
+    }
+}
+
+template <int K, int CB, int MT>
+cudaError_t launch_small(const GemmSmallParams& p, dim3 grid, cudaStream_t st)
+{
+    constexpr int bytes = GemmSmallSmem<K, MT>::BYTES;
+    static bool configured[64] = {};    // per (K, CB, MT) instantiation and device: the attribute is per device
+    auto kern = gemm_small_kernel<K, CB, MT>;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kern<<<grid, 256, bytes, st>>>(p);
+    return cudaPeekAtLastError();
+}
+
+template <int K, int CB>
+cudaError_t launch_small_mt(int mt, const GemmSmallParams& p, dim3 grid, cudaStream_t st)
+{
+    if (mt == 1) return launch_small<K, CB, 1>(p, grid, st);
+    if (mt == 2) return launch_small<K, CB, 2>(p, grid, st);
+    return launch_small<K, CB, 4>(p, grid, st);
+}
+
+template <int K>
+cudaError_t launch_small_cb(int cb, int mt, const GemmSmallParams& p, dim3 grid, cudaStream_t st)
+{
+    if (cb == 0) return launch_small_mt<K, 0>(mt, p, grid, st);
+    if (cb == 1) return launch_small_mt<K, 1>(mt, p, grid, st);
+    return launch_small_mt<K, 2>(mt, p, grid, st);
+}
+
+cudaError_t launch_small_k(int K, int cb, int mt, const GemmSmallParams& p, dim3 grid, cudaStream_t st)
+{
+    switch (K) {
+        case 1: return launch_small_cb<1>(cb, mt, p, grid, st);
+        case 2: return launch_small_cb<2>(cb, mt, p, grid, st);
+        case 3: return launch_small_cb<3>(cb, mt, p, grid, st);
+        case 4: return launch_small_cb<4>(cb, mt, p, grid, st);
+        case 5: return launch_small_cb<5>(cb, mt, p, grid, st);
+        case 6: return launch_small_cb<6>(cb, mt, p, grid, st);
+        case 7: return launch_small_cb<7>(cb, mt, p, grid, st);
+        default: return launch_small_cb<8>(cb, mt, p, grid, st);
+    }
+}
+
+}  // namespace
+
+// Rows are processed in passes of up to 64; each pass = input transform + one fused decode/MMA/output-transform launch.
+extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const void* trellis, void* C,
+                         const void* suh, void* A_had, const void* svh, int m, int k, int n, int K, int c_fp32,
+                         int mcg, int mul1)
+{
+    (void)A_had;   // the transformed activations live in the context scratch in a duplicated layout
+    EXL3_REQUIRE(ctx && A && trellis && C, "exl3_gemm: null argument");
+    EXL3_REQUIRE(m >= 0 && k > 0 && n > 0 && k % 128 == 0 && n % 128 == 0, "exl3_gemm: k % 128 == 0 and n % 128 == 0 required");
+    EXL3_REQUIRE(K >= 1 && K <= 8, "exl3_gemm: K must be 1..8");
+    EXL3_REQUIRE(!(mcg && mul1), "exl3_gemm: both mcg and mul1 set");
+    EXL3_REQUIRE(aligned16(A) && aligned16(trellis) && aligned16(C) && aligned16(suh) && aligned16(svh),
+                 "exl3_gemm: pointers must be 16-byte aligned");
+    if (m == 0) return EXL3_OK;
+    const int cb = mcg ? 1 : (mul1 ? 2 : 0);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int NB = n / 128, NST = k / 128;
+    EXL3_REQUIRE(NB <= ctx->n_counters, "exl3_gemm: n too large for the context's counters");
+
+    for (int row0 = 0; row0 < m; row0 += 64) {
+        const int rows = m - row0 < 64 ? m - row0 : 64;
+        const int mt = rows <= 16 ? 1 : (rows <= 32 ? 2 : 4);
+        size_t off = 0;
+        uint32_t* a_dup = (uint32_t*)exl3_ws_take(ctx, &off, (size_t)rows * k * 4);
+        float* rowsum = (float*)exl3_ws_take(ctx, &off, (size_t)rows * 4);
+        if (!a_dup || !rowsum) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the activations");
+        // split K so that the grid covers the SMs a few times over; partial sums must fit the remaining scratch
+        const int ctas_per_sm = mt == 1 ? 3 : (mt == 2 ? 2 : 1);
+        int splits = (ctx->num_sms * ctas_per_sm * 2 + NB - 1) / NB;
+        if (splits > NST / 2) splits = NST / 2;
+        if (splits < 1) splits = 1;
+        size_t part_off = off;
+        float* partial = nullptr;
+        while (splits > 1) {
+            part_off = off;
+            partial = (float*)exl3_ws_take(ctx, &part_off, (size_t)splits * rows * n * 4);
+            if (partial) break;
+            splits /= 2;
+        }
+        if (splits <= 1) { splits = 1; partial = nullptr; }
+
+        gemm_prologue_kernel<<<rows, 256, 0, st>>>((const half*)A + (size_t)row0 * k, (const half*)suh, a_dup, rowsum, k);
+        ctx->launches++;
+        GemmSmallParams p;
+        p.a_dup = a_dup; p.rowsum = rowsum; p.trellis = (const uint32_t*)trellis; p.partial = partial;
+        p.counters = ctx->counters; p.svh = (const half*)svh; p.status = ctx->status;
+        p.C = c_fp32 ? (void*)((float*)C + (size_t)row0 * n) : (void*)((half*)C + (size_t)row0 * n);
+        p.m = rows; p.k = k; p.n = n; p.splits = splits; p.c_fp32 = c_fp32;
+        cudaError_t e = launch_small_k(K, cb, mt, p, dim3(NB, splits), st);
+        ctx->launches++;
+        if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
+    }
+    return EXL3_OK;
+}

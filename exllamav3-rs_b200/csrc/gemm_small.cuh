@@ -1,0 +1,232 @@
+// EXL3 GEMM for small and medium M (the HBM-bound decode path): trellis tiles staged to shared memory by the bulk-copy
+// engine, decoded in registers and multiplied with mma.sync m16n8k16.
+//
+// Function computed (reference: kernels/quant/exl3_gemm_kernel.cuh:14-50, exl3_gemm_inner.cuh:456-480):
+//   C = H128( fp16(H128(A o suh)/sqrt128) . W ) / sqrt128 o svh
+//
+// Decode trick.  For codebooks 0/1 a weight is the fp16 sum of the two halves of one 32-bit register y; for codebook 2
+// it is k_inv*(h - 1534) + delta with h = fp16 in the low half of y and -1534 in its high half.  Instead of adding the
+// halves on the CUDA cores, y is fed to the tensor core as two consecutive k-entries of the B fragment and the
+// activation is duplicated in the two matching k-entries of the A fragment, so the MMA forms a*(lo+hi) in fp32.
+// One 16x16 weight tile then costs four m16n8k16 MMAs (16 real k = 32 MMA k) and no repacking instructions.
+#pragma once
+#include "common.cuh"
+#include "exl3_decode.cuh"
+#include "async_copy.cuh"
+
+namespace exl3 {
+
+constexpr int GS_KS = 8;            // weight-tile rows (16 k each) per pipeline stage: one 128-wide Hadamard block
+constexpr int GS_STAGES = 4;
+constexpr int GS_ASTRIDE = GS_KS * 16 + 8;   // words per activation row in shared memory (+8: conflict-free LDS.64)
+constexpr float GS_R128 = 0.088388347648f;
+// codebook 2: weight = K_INV*(h-1534) + DELTA, DELTA = k_bias + 1534*k_inv with the fp16 constants of the reference
+constexpr float GS_MUL1_KINV = 0.00676727294921875f;
+constexpr float GS_MUL1_DELTA = -10.3828125f + 1534.0f * 0.00676727294921875f;
+
+struct GemmSmallParams {
+    const uint32_t* a_dup;     // [m][k] words, each = (a, a) as two fp16: the Hadamard-transformed activations
+    const float* rowsum;       // [m] sum over k of the transformed activations (codebook 2 only)
+    const uint32_t* trellis;   // [k/16][n/16][8K] words
+    float* partial;            // [S][m][n] fp32 split-K partial sums (S > 1)
+    int* counters;             // [n/128] arrival counters, zero on entry and on exit
+    void* C;                   // [m][n] fp16 or fp32
+    const half* svh;           // [n] or NULL
+    int* status;
+    int m, k, n, splits, c_fp32;
+};
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int K, int MT>
+struct GemmSmallSmem {
+    static constexpr int B_STAGE_WORDS = GS_KS * 8 * 8 * K;            // GS_KS tile rows x 8 tiles x 8K words
+    static constexpr int A_STAGE_WORDS = MT * 16 * GS_ASTRIDE;
+    static constexpr int STAGE_WORDS = B_STAGE_WORDS + A_STAGE_WORDS;
+    static constexpr int C_WORDS = MT * 16 * 132;                        // epilogue tile [rows][128+4] fp32
+    static constexpr int PIPE_WORDS = GS_STAGES * STAGE_WORDS;
+    static constexpr int BYTES = (PIPE_WORDS > C_WORDS ? PIPE_WORDS : C_WORDS) * 4 + GS_STAGES * 8 + 16;
+};
+
+// grid (n/128, splits); 256 threads = 8 warps, warp w owns the 16 columns of tile w of the CTA's 128-column block.
+template <int K, int CB, int MT>
+__global__ void __launch_bounds__(256) gemm_small_kernel(const GemmSmallParams p)
+{
+    using SM = GemmSmallSmem<K, MT>;
+    extern __shared__ __align__(128) uint32_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (SM::PIPE_WORDS > SM::C_WORDS ? SM::PIPE_WORDS : SM::C_WORDS));
+    __shared__ int s_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int nb = blockIdx.x, split = blockIdx.y;
+    const int tiles_n = p.n >> 4;
+    const int KT = p.k >> 4;                                  // tile rows in the whole weight
+    const int NST = KT / GS_KS;                               // 128-k stages in the whole weight (k % 128 == 0)
+    const int st0 = (int)(((long long)NST * split) / p.splits);
+    const int st1 = (int)(((long long)NST * (split + 1)) / p.splits);
+    const int nstages = st1 - st0;
+    const int mrows = p.m < MT * 16 ? p.m : MT * 16;
+
+    if (tid == 0) {
+        #pragma unroll
+        for (int s = 0; s < GS_STAGES; ++s) mbar_init(&bars[s], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // producer: one thread issues all bulk copies of a stage
+    auto issue = [&](int stage_idx) {
+        const int slot = stage_idx % GS_STAGES;
+        uint32_t* sb = smem + slot * SM::STAGE_WORDS;
+        uint32_t* sa = sb + SM::B_STAGE_WORDS;
+        const int kt0 = (st0 + stage_idx) * GS_KS;
+        const uint32_t bytes = GS_KS * 8 * 8 * K * 4 + (uint32_t)mrows * GS_KS * 16 * 4;
+        mbar_expect_tx(&bars[slot], bytes);
+        #pragma unroll
+        for (int r = 0; r < GS_KS; ++r)
+            bulk_g2s(sb + r * 64 * K, p.trellis + ((size_t)(kt0 + r) * tiles_n + nb * 8) * 8 * K, 64 * K * 4, &bars[slot]);
+        for (int r = 0; r < mrows; ++r)
+            bulk_g2s(sa + r * GS_ASTRIDE, p.a_dup + (size_t)r * p.k + kt0 * 16, GS_KS * 16 * 4, &bars[slot]);
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < GS_STAGES - 1 && s < nstages; ++s) issue(s);
+    }
+
+    float acc[MT][2][4];
+    #pragma unroll
+    for (int i = 0; i < MT; ++i)
+        #pragma unroll
+        for (int j = 0; j < 2; ++j)
+            #pragma unroll
+            for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.0f;
+
+    bool failed = false;
+    for (int s = 0; s < nstages; ++s) {
+        const int slot = s % GS_STAGES;
+        if (tid == 0 && s + GS_STAGES - 1 < nstages) issue(s + GS_STAGES - 1);
+        const bool ok = mbar_wait(&bars[slot], (s / GS_STAGES) & 1);
+        if (ok) {
+            const uint32_t* sb = smem + slot * SM::STAGE_WORDS + warp * 8 * K;
+            const uint32_t* sa = smem + slot * SM::STAGE_WORDS + SM::B_STAGE_WORDS;
+            #pragma unroll 2
+            for (int r = 0; r < GS_KS; ++r) {
+                uint32_t st[8], y[8];
+                lane_states<K>(sb + r * 64 * K, lane, st);
+                #pragma unroll
+                for (int j = 0; j < 8; ++j) y[j] = decode_raw<CB>(st[j]);
+                #pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint32_t* ar0 = sa + (mt * 16 + g) * GS_ASTRIDE + r * 16 + 2 * t;
+                    const uint32_t* ar1 = ar0 + 8 * GS_ASTRIDE;
+                    uint2 lo0 = *reinterpret_cast<const uint2*>(ar0);         // rows g   : k 2t, 2t+1
+                    uint2 lo1 = *reinterpret_cast<const uint2*>(ar1);         // rows g+8
+                    uint2 hi0 = *reinterpret_cast<const uint2*>(ar0 + 8);     // k 2t+8, 2t+9
+                    uint2 hi1 = *reinterpret_cast<const uint2*>(ar1 + 8);
+                    mma16816(acc[mt][0], lo0.x, lo1.x, lo0.y, lo1.y, y[0], y[1]);
+                    mma16816(acc[mt][0], hi0.x, hi1.x, hi0.y, hi1.y, y[2], y[3]);
+                    mma16816(acc[mt][1], lo0.x, lo1.x, lo0.y, lo1.y, y[4], y[5]);
+                    mma16816(acc[mt][1], hi0.x, hi1.x, hi0.y, hi1.y, y[6], y[7]);
+                }
+            }
+        }
+        // all warps are done with this slot (it is refilled at the top of the next iteration); a wait that ran out
+        // anywhere in the CTA ends the loop for everyone
+        if (__syncthreads_or(!ok)) { failed = true; break; }
+    }
+    if (failed) {
+        if (tid == 0) atomicExch(p.status, 1);
+        return;
+    }
+
+    // ---- epilogue: accumulators -> shared tile [rows][132] fp32
+    float* sc = reinterpret_cast<float*>(smem);
+    #pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+        #pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int col = warp * 16 + j * 8 + 2 * t;
+            *reinterpret_cast<float2*>(sc + (mt * 16 + g) * 132 + col) = make_float2(acc[mt][j][0], acc[mt][j][1]);
+            *reinterpret_cast<float2*>(sc + (mt * 16 + g + 8) * 132 + col) = make_float2(acc[mt][j][2], acc[mt][j][3]);
+        }
+    __syncthreads();
+
+    if (p.splits > 1) {
+        // publish this split's partial sums, then the last CTA to arrive for this column block finishes the job
+        for (int i = tid; i < mrows * 32; i += 256) {
+            const int row = i >> 5, c4 = i & 31;
+            float4 v = *reinterpret_cast<const float4*>(sc + row * 132 + c4 * 4);
+            *reinterpret_cast<float4*>(p.partial + ((size_t)split * p.m + row) * p.n + nb * 128 + c4 * 4) = v;
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int old = atomicAdd(&p.counters[nb], 1);
+            s_flag = (old == p.splits - 1);
+            if (s_flag) p.counters[nb] = 0;
+        }
+        __syncthreads();
+        if (!s_flag) return;
+        __threadfence();
+        for (int i = tid; i < mrows * 32; i += 256) {
+            const int row = i >> 5, c4 = i & 31;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < p.splits; ++s) {        // fixed order: the result does not depend on arrival order
+                float4 v = __ldcg(reinterpret_cast<const float4*>(p.partial + ((size_t)s * p.m + row) * p.n + nb * 128 + c4 * 4));
+                a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+            }
+            *reinterpret_cast<float4*>(sc + row * 132 + c4 * 4) = a;
+        }
+        __syncthreads();
+    }
+
+    // output transform: one warp per row, lane holds 4 consecutive columns
+    for (int row = warp; row < mrows; row += 8) {
+        float4 v = *reinterpret_cast<const float4*>(sc + row * 132 + lane * 4);
+        if constexpr (CB == 2) {
+            const float rs = p.rowsum[row] * GS_MUL1_DELTA;
+            v.x = fmaf(v.x, GS_MUL1_KINV, rs); v.y = fmaf(v.y, GS_MUL1_KINV, rs);
+            v.z = fmaf(v.z, GS_MUL1_KINV, rs); v.w = fmaf(v.w, GS_MUL1_KINV, rs);
+        }
+        const size_t off = (size_t)row * p.n + nb * 128 + lane * 4;
+        if (p.svh) {
+            float s0 = v.x + v.y, d0 = v.x - v.y, s1 = v.z + v.w, d1 = v.z - v.w;
+            v.x = s0 + s1; v.y = d0 + d1; v.z = s0 - s1; v.w = d0 - d1;
+            #pragma unroll
+            for (int i = 1; i < 32; i <<= 1) {
+                float p0 = __shfl_xor_sync(0xffffffffu, v.x, i), p1 = __shfl_xor_sync(0xffffffffu, v.y, i);
+                float p2 = __shfl_xor_sync(0xffffffffu, v.z, i), p3 = __shfl_xor_sync(0xffffffffu, v.w, i);
+                const bool up = lane & i;
+                v.x = (up ? -v.x : v.x) + p0; v.y = (up ? -v.y : v.y) + p1;
+                v.z = (up ? -v.z : v.z) + p2; v.w = (up ? -v.w : v.w) + p3;
+            }
+            v.x *= GS_R128; v.y *= GS_R128; v.z *= GS_R128; v.w *= GS_R128;
+            uint2 sr = *reinterpret_cast<const uint2*>(p.svh + nb * 128 + lane * 4);
+            half2 sa = *reinterpret_cast<half2*>(&sr.x), sb2 = *reinterpret_cast<half2*>(&sr.y);
+            if (p.c_fp32) {
+                v.x *= __low2float(sa); v.y *= __high2float(sa); v.z *= __low2float(sb2); v.w *= __high2float(sb2);
+                *reinterpret_cast<float4*>((float*)p.C + off) = v;
+            } else {
+                half2 a = __hmul2(__floats2half2_rn(v.x, v.y), sa), b = __hmul2(__floats2half2_rn(v.z, v.w), sb2);
+                uint2 o; o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
+                *reinterpret_cast<uint2*>((half*)p.C + off) = o;
+            }
+        } else {
+            if (p.c_fp32) *reinterpret_cast<float4*>((float*)p.C + off) = v;
+            else {
+                half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+                uint2 o; o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
+                *reinterpret_cast<uint2*>((half*)p.C + off) = o;
+            }
+        }
+    }
+}
+
+}  // namespace exl3

@@ -234,7 +234,7 @@ class Ctx:
         else:
             nq, hd = q.shape[1:]
             q_len = max_q_len if max_q_len is not None else q.shape[0]
-            kv_append = q_len
+            kv_append = q.shape[0]          # ragged form: total packed rows
         nkv = k_cache.shape[2]
         self.check(lib().exl3_bighead_attn_paged(self._h, self.stream(stream), _ptr(q), _ptr(k), _ptr(v), _ptr(k_cache),
                                                  _ptr(v_cache), _ptr(block_table), _ptr(cache_seqlens), _ptr(cu_q),
@@ -255,7 +255,7 @@ class Ctx:
         else:
             nq, hd = q.shape[1:]
             q_len = max_q_len if max_q_len is not None else q.shape[0]
-            kv_append = q_len
+            kv_append = q.shape[0]          # ragged form: total packed rows
         groups = sk.shape[2]
         self.check(lib().exl3_bighead_attn_paged_q(self._h, self.stream(stream), _ptr(q), _ptr(k), _ptr(v), _ptr(qk),
                                                    _ptr(sk), _ptr(qv), _ptr(sv), _ptr(block_table), _ptr(cache_seqlens),

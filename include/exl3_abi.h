@@ -55,7 +55,7 @@ enum { EXL3_ROPE_NONE = 0, EXL3_ROPE_GPTJ = 1, EXL3_ROPE_NEOX = 2 };
 /* ------------------------------------------------------------------------------------------------ context */
 
 /* Create the per-device context (allocates scratch with cudaMalloc on `device`).  `workspace_bytes` = 0 picks the
- * default (64 MiB).  Replaces the reference's DevCtx singleton (kernels/quant/exl3_devctx.cuh:18-40). */
+ * default (256 MiB).  Replaces the reference's DevCtx singleton (kernels/quant/exl3_devctx.cuh:18-40). */
 EXL3_API int  exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** out);
 EXL3_API void exl3_ctx_destroy(exl3_ctx* ctx);
 /* host string describing the last error on this context (never NULL) */
@@ -86,11 +86,6 @@ EXL3_API int exl3_reconstruct(exl3_ctx* ctx, exl3_stream stream, void* unpacked,
  * x,y [rows,cols] both fp16 (fp32 = 0) or both fp32; cols % 128 == 0; in place allowed. */
 EXL3_API int exl3_had_r_128(exl3_ctx* ctx, exl3_stream stream, const void* x, void* y, const void* pre_scale,
                    const void* post_scale, float scale, int rows, int cols, int fp32);
-
-/* exl3_shim_hgemm (src/ffi.rs:66, csrc/exl3_shim.cpp:93 -> kernels/hgemm.cu:19-78): C[m,n] = A[m,k] . B[k,n],
- * fp16 inputs, fp32 accumulation, C fp16 or fp32.  k % 64 == 0, n % 8 == 0. */
-EXL3_API int exl3_hgemm(exl3_ctx* ctx, exl3_stream stream, const void* a, const void* b, void* c, int m, int k, int n,
-               int c_fp32);
 
 /* ------------------------------------------------------------------------------------- norm / rope / act */
 
@@ -148,8 +143,9 @@ EXL3_API int exl3_paged_kv_cache_update(exl3_ctx* ctx, exl3_stream stream, const
  * q [bsz,q_len,nq,hd] over the first cache_seqlens[b]+kv_append cached keys; query i sees keys
  * j <= total - q_len + i.  sm_scale 0 = 1/sqrt(hd).  o like q.  kv_chunk_size is accepted and ignored (split sizes
  * are derived on the device from the real lengths).
- * Ragged form: cu_q non-NULL -> q,o [rows,nq,hd], k,v [rows,nkv,hd] packed, q_len(b) = kv_append(b) = cu_q[b+1]-cu_q[b],
- * `q_len` is an upper bound on rows per sequence. */
+ * Ragged form: cu_q non-NULL -> q,o [rows,nq,hd], k,v [rows,nkv,hd] packed; sequence b owns rows [cu_q[b], cu_q[b+1])
+ * and appends exactly those rows.  Then `q_len` is an upper bound on the rows of any one sequence and `kv_append`
+ * carries the total number of packed rows (cu_q[bsz]). */
 EXL3_API int exl3_bighead_attn_paged(exl3_ctx* ctx, exl3_stream stream, const void* q, const void* k, const void* v,
                             void* k_cache, void* v_cache, const int32_t* block_table, const int32_t* cache_seqlens,
                             const int32_t* cu_q, void* o, int bsz, int q_len, int kv_append, int nq, int nkv, int hd,

@@ -1,0 +1,204 @@
+"""GPU parity of paged attention (fp16 and quantised KV; decode, verify, prefill-chunk and ragged mixes) through the
+C-ABI.  Bars: max |diff| <= 2e-3 * RMS(out) with fp16 KV, 1e-2 * RMS(out) with quantised KV."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tests import helpers as H
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+TOL_FP16 = 2e-3
+TOL_QUANT = 1e-2
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _close(got, want, tol):
+    """tol * RMS, or one fp16 rounding step of the reference value (outputs are stored as fp16)"""
+    return H.gemm_mismatch(got, want, tol, True)
+
+
+def _run_fp16(ctx, c, causal=True):
+    torch = _torch()
+    kc, vc = H.to_dev(c["kc"]), H.to_dev(c["vc"])
+    o = torch.full(c["q"].shape, float("nan"), dtype=torch.float16, device="cuda")
+    ctx.bighead_attn_paged(H.to_dev(c["q"]), H.to_dev(c["k"]), H.to_dev(c["v"]), kc, vc, H.to_dev(c["block_table"]),
+                           H.to_dev(c["seqlens"]), o, causal=causal)
+    ctx.poll_status()
+    return o.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy()
+
+
+def _oracle_fp16(c, causal=True):
+    from oracle import oracle as O
+    kc, vc = c["kc"].copy(), c["vc"].copy()
+    O.paged_kv_update(c["k"], c["v"], kc, vc, c["block_table"], c["seqlens"])
+    return O.attn_paged(c["q"], kc, vc, c["block_table"], c["seqlens"], causal=causal), kc, vc
+
+
+@pytest.mark.parametrize("name", [n for n, _ in cases.attn_cases()])
+def test_attention_golden_cases(ctx, name):
+    c = dict(cases.attn_cases())[name]
+    g = np.load(cases.__file__.replace("cases.py", "golden_ref.npz"))
+    got, kc, vc = _run_fp16(ctx, c)
+    want, wkc, wvc = _oracle_fp16(c)
+    assert np.isfinite(got).all()
+    assert np.array_equal(kc.view(np.uint16), wkc.view(np.uint16)) and np.array_equal(vc.view(np.uint16), wvc.view(np.uint16))
+    assert _close(got, want, TOL_FP16) <= 1.0
+    for mma in (0, 1):
+        key = f"{name}_mma{mma}"
+        if key in g.files:
+            assert _close(got, g[key], TOL_FP16) <= 1.0, key
+
+
+def _make_case(seed, ctx_lens, q_len, nq, nkv, hd=128):
+    r = H.rng(seed)
+    seqlens = np.asarray(ctx_lens, np.int32)
+    bsz = len(seqlens)
+    bt, pages = H.make_paged(r, bsz, seqlens, nkv, hd, append=q_len)
+    return dict(q=r.standard_normal((bsz, q_len, nq, hd)).astype(np.float16),
+                k=(0.5 * r.standard_normal((bsz, q_len, nkv, hd))).astype(np.float16),
+                v=(0.5 * r.standard_normal((bsz, q_len, nkv, hd))).astype(np.float16),
+                kc=(0.5 * r.standard_normal((pages, 256, nkv, hd))).astype(np.float16),
+                vc=(0.5 * r.standard_normal((pages, 256, nkv, hd))).astype(np.float16),
+                block_table=bt, seqlens=seqlens)
+
+
+def _ref_fp16(ref, c, mma):
+    torch = _torch()
+    bsz, q_len, nq, hd = c["q"].shape
+    nkv, pages = c["kc"].shape[2], c["kc"].shape[0]
+    ref.ref_set_mma_attn(mma)
+    t = [H.to_dev(c[n]) for n in ("q", "k", "v", "kc", "vc", "block_table", "seqlens")]
+    o = torch.zeros(c["q"].shape, dtype=torch.float16, device="cuda")
+    assert ref.ref_bighead_attn_paged(*[H.ptr(x) for x in t], H.ptr(o), bsz, q_len, q_len, nq, nkv, hd, pages,
+                                      c["block_table"].shape[1], 256, 1, C.c_float(0.0)) == 0
+    torch.cuda.synchronize()
+    return o.cpu().numpy()
+
+
+@pytest.mark.parametrize("q_len,nq,nkv", [(1, 40, 8), (1, 16, 8), (8, 40, 8), (3, 16, 8), (64, 16, 8), (256, 40, 8)])
+def test_attention_shapes(ctx, ref, q_len, nq, nkv):
+    """decode (G=5 and G=2), verify (8 rows), short and full prefill chunks over contexts that straddle pages"""
+    ctx_lens = [0, 1, 255, 256, 257, 1000, 4095] if q_len <= 8 else [0, 300, 1000]
+    c = _make_case(900 + q_len + nq, ctx_lens, q_len, nq, nkv)
+    got, _, _ = _run_fp16(ctx, c)
+    want, _, _ = _oracle_fp16(c)
+    assert np.isfinite(got).all()
+    assert _close(got, want, TOL_FP16) <= 1.0
+    if ref is not None:
+        rgot = _ref_fp16(ref, c, 1 if q_len > 1 else 0)
+        assert _close(got, rgot, TOL_FP16) <= 1.0
+
+
+def test_attention_long_context_split_kv(ctx, ref):
+    """attention-alone benchmark shape at reduced batch: contexts log-uniform in [128, 32768], 40 q / 8 kv heads"""
+    r = H.rng(77)
+    ctx_lens = np.exp(r.uniform(np.log(128), np.log(32768), 6)).astype(np.int32)
+    ctx_lens[0], ctx_lens[1] = 32767, 128
+    c = _make_case(78, ctx_lens, 1, 40, 8)
+    got, _, _ = _run_fp16(ctx, c)
+    want, _, _ = _oracle_fp16(c)
+    assert _close(got, want, TOL_FP16) <= 1.0
+    if ref is not None:
+        assert _close(got, _ref_fp16(ref, c, 0), TOL_FP16) <= 1.0
+
+
+def test_attention_non_causal_and_no_append(ctx):
+    from oracle import oracle as O
+    torch = _torch()
+    c = _make_case(55, [40, 700], 4, 16, 8)
+    got, _, _ = _run_fp16(ctx, c, causal=False)
+    want, _, _ = _oracle_fp16(c, causal=False)
+    assert _close(got, want, TOL_FP16) <= 1.0
+    # kv_append = 0: attend over what is already cached (query rows see every cached key <= total - q_len + i)
+    o = torch.empty(c["q"].shape, dtype=torch.float16, device="cuda")
+    ctx.bighead_attn_paged(H.to_dev(c["q"]), None, None, H.to_dev(c["kc"]), H.to_dev(c["vc"]), H.to_dev(c["block_table"]),
+                           H.to_dev(c["seqlens"]), o)
+    want = O.attn_paged(c["q"], c["kc"], c["vc"], c["block_table"], c["seqlens"], kv_append=0)
+    assert _close(o.cpu().numpy(), want, TOL_FP16) <= 1.0
+
+
+def test_attention_ragged_equals_per_sequence(ctx):
+    """One ragged call over mixed decode / verify / prefill-chunk sequences == the rectangular calls one by one."""
+    from oracle import oracle as O
+    torch = _torch()
+    r = H.rng(123)
+    nq, nkv, hd = 40, 8, 128
+    qlens = np.array([1, 8, 1, 256, 0, 70, 1], np.int32)
+    ctx_lens = np.array([500, 1300, 0, 2048, 10, 255, 9000], np.int32)
+    cu = np.concatenate([[0], np.cumsum(qlens)]).astype(np.int32)
+    bt, pages = H.make_paged(r, len(qlens), ctx_lens + qlens, nkv, hd)
+    rows = int(cu[-1])
+    q = r.standard_normal((rows, nq, hd)).astype(np.float16)
+    k = (0.5 * r.standard_normal((rows, nkv, hd))).astype(np.float16)
+    v = (0.5 * r.standard_normal((rows, nkv, hd))).astype(np.float16)
+    kc0 = (0.5 * r.standard_normal((pages, 256, nkv, hd))).astype(np.float16)
+    vc0 = (0.5 * r.standard_normal((pages, 256, nkv, hd))).astype(np.float16)
+    kc, vc = H.to_dev(kc0), H.to_dev(vc0)
+    o = torch.full((rows, nq, hd), float("nan"), dtype=torch.float16, device="cuda")
+    ctx.bighead_attn_paged(H.to_dev(q), H.to_dev(k), H.to_dev(v), kc, vc, H.to_dev(bt), H.to_dev(ctx_lens), o,
+                           cu_q=H.to_dev(cu), max_q_len=int(qlens.max()))
+    ctx.poll_status()
+    got = o.cpu().numpy()
+    wk, wv = kc0.copy(), vc0.copy()
+    for b in range(len(qlens)):
+        if qlens[b]:
+            O.paged_kv_update(k[None, cu[b]:cu[b + 1]], v[None, cu[b]:cu[b + 1]], wk, wv, bt[b:b + 1], ctx_lens[b:b + 1])
+    want = O.attn_paged(q, wk, wv, bt, ctx_lens, cu_q=cu)
+    assert np.isfinite(got).all()
+    assert _close(got, want, TOL_FP16) <= 1.0
+
+
+@pytest.mark.parametrize("bits", [4, 8, 6, 2])
+@pytest.mark.parametrize("q_len", [1, 8])
+def test_attention_quantised_kv(ctx, ref, q_len, bits):
+    from oracle import oracle as O
+    torch = _torch()
+    nq, nkv, hd = 40, 8, 128
+    c = _make_case(300 + bits + q_len, [0, 200, 1500, 5000], q_len, nq, nkv)
+    bsz = 4
+    groups = nkv * hd // 32
+    pages = c["kc"].shape[0]
+    # the cached context is the quantised form of the fp16 pools
+    oq = [np.zeros((pages, 256, groups * bits), np.uint32), np.zeros((pages, 256, groups), np.float16),
+          np.zeros((pages, 256, groups * bits), np.uint32), np.zeros((pages, 256, groups), np.float16)]
+    qk, sk = O.quant_groups(c["kc"].reshape(-1), bits)
+    qv, sv = O.quant_groups(c["vc"].reshape(-1), bits)
+    oq[0][:] = qk.reshape(oq[0].shape); oq[1][:] = sk.reshape(oq[1].shape)
+    oq[2][:] = qv.reshape(oq[2].shape); oq[3][:] = sv.reshape(oq[3].shape)
+    d = [H.to_dev(oq[0].view(np.int32)), H.to_dev(oq[1]), H.to_dev(oq[2].view(np.int32)), H.to_dev(oq[3])]
+    o = torch.full(c["q"].shape, float("nan"), dtype=torch.float16, device="cuda")
+    dq, dk, dv, dbt, dsl = [H.to_dev(c[n]) for n in ("q", "k", "v", "block_table", "seqlens")]
+    ctx.bighead_attn_paged_q(dq, dk, dv, d[0], d[1], d[2], d[3], dbt, dsl, o, nkv)
+    ctx.poll_status()
+    got = o.cpu().numpy()
+    O.quant_cache_paged(c["k"], oq[0], oq[1], c["v"], oq[2], oq[3], c["seqlens"], c["block_table"], bits, bits)
+    want = O.attn_paged(c["q"], None, None, c["block_table"], c["seqlens"], nkv=nkv,
+                        quant=(oq[0], oq[1], oq[2], oq[3], bits))
+    assert np.isfinite(got).all()
+    assert _close(got, want, TOL_QUANT) <= 1.0
+    if ref is not None and bits in (4, 6, 8):
+        d2 = [H.to_dev(x) for x in (qk.reshape(oq[0].shape).view(np.int32), sk.reshape(oq[1].shape),
+                                    qv.reshape(oq[2].shape).view(np.int32), sv.reshape(oq[3].shape))]
+        o2 = torch.zeros_like(o)
+        assert ref.ref_bighead_attn_paged_q(H.ptr(dq), H.ptr(dk), H.ptr(dv), *[H.ptr(x) for x in d2], H.ptr(dbt), H.ptr(dsl),
+                                            H.ptr(o2), bsz, q_len, q_len, nq, nkv, hd, pages, c["block_table"].shape[1],
+                                            bits, bits, 256, 1, C.c_float(0.0)) == 0
+        torch.cuda.synchronize()
+        assert _close(got, o2.cpu().numpy(), TOL_QUANT) <= 1.0
+
+
+def test_attention_rejects_unsupported(ctx):
+    import exl3b200
+    torch = _torch()
+    q = torch.zeros(1, 1, 4, 64, dtype=torch.float16, device="cuda")
+    kc = torch.zeros(2, 256, 2, 64, dtype=torch.float16, device="cuda")
+    bt = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
+    sl = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(exl3b200.Exl3Error):
+        ctx.bighead_attn_paged(q, None, None, kc, kc.clone(), bt, sl, torch.zeros_like(q))

@@ -1,0 +1,219 @@
+"""GPU parity of the EXL3 linear ops (reconstruct, had_r_128, exl3_gemm) through the C-ABI.
+
+Checked against the CPU oracle on identical seeded inputs and, where oracle/_ref/libexl3ref.so exists, side by side
+against the reference's own CUDA ops.  Bars: dequantised weights bit-exact; GEMM within 2e-3 * RMS(out).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+GEMM_TOL = 2e-3   # max |diff| / RMS(out), the north-star tolerance for fp16 GEMM outputs
+
+
+def _torch():
+    import torch
+    return torch
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_reconstruct_bit_exact_vs_oracle(ctx, K, cb):
+    from oracle import oracle as O
+    torch = _torch()
+    r = H.rng(100 + K * 3 + cb)
+    tr = H.rand_trellis(r, 256, 384, K)
+    out = torch.empty(256, 384, dtype=torch.float16, device="cuda")
+    ctx.reconstruct(out, H.to_dev(tr), K, mcg=cb == 1, mul1=cb == 2)
+    want = O.reconstruct(tr, K, cb)
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+def test_reconstruct_all_states(ctx, cb):
+    """Every 16-bit state appears: at K=8 with 16-bit aligned fields, state(t) is made of two chosen bytes."""
+    from oracle import oracle as O
+    torch = _torch()
+    r = H.rng(7)
+    tr = H.rand_trellis(r, 1024, 1024, 8)     # 1M weights -> all 65536 states with overwhelming probability
+    out = torch.empty(1024, 1024, dtype=torch.float16, device="cuda")
+    ctx.reconstruct(out, H.to_dev(tr), 8, mcg=cb == 1, mul1=cb == 2)
+    want = O.reconstruct(tr, 8, cb)
+    got = out.cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    assert len(np.unique(got.view(np.uint16))) > 500     # codebook 2 has only 1021 distinct values
+
+
+@pytest.mark.parametrize("K", [2, 3, 4, 5, 8])
+def test_reconstruct_full_size_vs_reference(ctx, ref, K):
+    """5120 x 17408 (the GEMM sweep shape): bit-exact against the reference CUDA op and the oracle."""
+    from oracle import oracle as O
+    torch = _torch()
+    r = H.rng(200 + K)
+    k, n = 5120, 17408
+    tr = H.rand_trellis(r, k, n, K)
+    d_tr = H.to_dev(tr)
+    out = torch.empty(k, n, dtype=torch.float16, device="cuda")
+    ctx.reconstruct(out, d_tr, K, mcg=True)
+    got = out.cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, O.reconstruct(tr, K, 1).view(np.uint16))
+    if ref is not None:
+        out2 = torch.empty_like(out)
+        assert ref.ref_reconstruct(H.ptr(out2), H.ptr(d_tr), k, n, K, 1, 0) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(got, out2.cpu().numpy().view(np.uint16))
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_reconstruct_vs_reference_all_formats(ctx, ref, K, cb):
+    if ref is None:
+        pytest.skip("reference op library not built")
+    torch = _torch()
+    r = H.rng(300 + K * 3 + cb)
+    d_tr = H.to_dev(H.rand_trellis(r, 512, 1024, K))
+    a = torch.empty(512, 1024, dtype=torch.float16, device="cuda")
+    b = torch.empty_like(a)
+    ctx.reconstruct(a, d_tr, K, mcg=cb == 1, mul1=cb == 2)
+    assert ref.ref_reconstruct(H.ptr(b), H.ptr(d_tr), 512, 1024, K, int(cb == 1), int(cb == 2)) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("mode", ["plain", "pre", "post"])
+@pytest.mark.parametrize("fp32", [False, True])
+def test_had_r_128(ctx, ref, mode, fp32):
+    from oracle import oracle as O
+    torch = _torch()
+    r = H.rng(11)
+    rows, cols = 37, 640
+    x = r.standard_normal((rows, cols)).astype(np.float32 if fp32 else np.float16)
+    sc = H.rand_signs(r, cols) * np.float16(1.5)
+    pre = sc if mode == "pre" else None
+    post = sc if mode == "post" else None
+    dx = H.to_dev(x)
+    y = torch.empty_like(dx)
+    ctx.had_r_128(dx, y, None if pre is None else H.to_dev(pre), None if post is None else H.to_dev(post), 1.0)
+    want = O.had_r_128(x, pre, post, 1.0)
+    got = y.cpu().numpy()
+    if fp32:
+        assert np.allclose(got, want, rtol=1e-6, atol=1e-6)
+    else:
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    if ref is not None:
+        y2 = torch.empty_like(dx)
+        dsc = H.to_dev(sc)
+        assert ref.ref_had_r_128(H.ptr(dx), H.ptr(y2), H.ptr(dsc if pre is not None else None),
+                                 H.ptr(dsc if post is not None else None), C.c_float(1.0), rows, cols, int(fp32)) == 0
+        torch.cuda.synchronize()
+        if fp32:
+            assert torch.allclose(y, y2, rtol=1e-6, atol=1e-6)
+        else:
+            assert torch.equal(y, y2)
+    # involution: H(H(x)) == x up to rounding
+    if mode == "plain":
+        z = torch.empty_like(dx)
+        ctx.had_r_128(y, z, None, None, 1.0)
+        assert H.rel_rms_err(z.cpu().numpy(), x) < (1e-5 if fp32 else 4e-3)
+
+
+def _gemm_case(ctx, ref, m, k, n, K, cb, c_fp32, seed, check_oracle=True):
+    from oracle import oracle as O
+    torch = _torch()
+    r = H.rng(seed)
+    A = r.standard_normal((m, k)).astype(np.float16)
+    tr = H.rand_trellis(r, k, n, K)
+    suh, svh = H.rand_signs(r, k), H.rand_signs(r, n)
+    dA, dtr, dsuh, dsvh = H.to_dev(A), H.to_dev(tr), H.to_dev(suh), H.to_dev(svh)
+    Cd = torch.full((m, n), float("nan"), dtype=torch.float32 if c_fp32 else torch.float16, device="cuda")
+    ctx.exl3_gemm(dA, dtr, Cd, dsuh, None, dsvh, mcg=cb == 1, mul1=cb == 2)
+    ctx.poll_status()
+    got = Cd.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    if check_oracle:
+        want = O.exl3_gemm(A, tr, suh, svh, K, cb, c_fp32=c_fp32).astype(np.float32)
+        err = H.gemm_mismatch(got, want, GEMM_TOL, not c_fp32)
+        assert err <= 1.0, f"vs oracle: {err} x the allowed difference"
+    if ref is not None:
+        C2 = torch.zeros_like(Cd)
+        ah = torch.empty(m, k, dtype=torch.float16, device="cuda")
+        tag = ref.ref_exl3_gemm(H.ptr(dA), H.ptr(dtr), H.ptr(C2), H.ptr(dsuh), H.ptr(ah), H.ptr(dsvh), m, k, n, K,
+                                int(c_fp32), int(cb == 1), int(cb == 2), -1)
+        torch.cuda.synchronize()
+        assert tag in (0, 90) or tag > 0, tag
+        err = H.gemm_mismatch(got, C2.float().cpu().numpy(), GEMM_TOL, not c_fp32)
+        assert err <= 1.0, f"vs reference CUDA op: {err} x the allowed difference"
+    return got
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_gemm_formats(ctx, ref, K, cb):
+    _gemm_case(ctx, ref, 5, 1024, 1024, K, cb, False, 400 + K * 3 + cb)
+
+
+@pytest.mark.parametrize("m", [1, 2, 8, 16, 17, 32, 33, 64, 65, 100, 150])
+def test_gemm_row_counts(ctx, ref, m):
+    _gemm_case(ctx, ref, m, 2048, 1024, 4, 1, False, 500 + m)
+
+
+@pytest.mark.parametrize("c_fp32", [False, True])
+@pytest.mark.parametrize("k,n", [(128, 128), (1024, 3072), (3072, 1024), (5120, 1024), (1024, 151936 // 128 * 128)])
+def test_gemm_shapes(ctx, ref, k, n, c_fp32):
+    _gemm_case(ctx, ref, 8, k, n, 4, 0, c_fp32, 600 + k + n)
+
+
+@pytest.mark.parametrize("K", [2, 3, 4, 5, 8])
+@pytest.mark.parametrize("m", [1, 4, 16, 64])
+def test_gemm_sweep_shape(ctx, ref, m, K):
+    """K=5120, N=17408 sweep of the benchmark configs at the small-M sizes, against oracle and reference op."""
+    _gemm_case(ctx, ref, m, 5120, 17408, K, 1, False, 700 + m + K, check_oracle=(m <= 16))
+
+
+def test_gemm_deterministic_and_reusable(ctx):
+    """Two calls in a row give identical bits (fixed-order split-K reduction, counters return to zero)."""
+    torch = _torch()
+    r = H.rng(9)
+    m, k, n, K = 3, 5120, 1024, 4
+    dA, dtr = H.to_dev(r.standard_normal((m, k)).astype(np.float16)), H.to_dev(H.rand_trellis(r, k, n, K))
+    dsuh, dsvh = H.to_dev(H.rand_signs(r, k)), H.to_dev(H.rand_signs(r, n))
+    c1 = torch.empty(m, n, dtype=torch.float16, device="cuda")
+    c2 = torch.empty_like(c1)
+    ctx.exl3_gemm(dA, dtr, c1, dsuh, None, dsvh, mcg=True)
+    ctx.exl3_gemm(dA, dtr, c2, dsuh, None, dsvh, mcg=True)
+    ctx.poll_status()
+    assert torch.equal(c1, c2)
+
+
+def test_gemm_linearity(ctx):
+    """Size-independent property: gemm(a) + gemm(b) == gemm(a + b) up to fp16 rounding of the operands."""
+    torch = _torch()
+    r = H.rng(10)
+    k, n, K = 5120, 17408, 4
+    a = (r.integers(-8, 9, size=(1, k)) / 8.0).astype(np.float16)      # exactly representable, sums stay exact
+    b = (r.integers(-8, 9, size=(1, k)) / 8.0).astype(np.float16)
+    dtr, dsuh, dsvh = H.to_dev(H.rand_trellis(r, k, n, K)), H.to_dev(H.rand_signs(r, k)), H.to_dev(H.rand_signs(r, n))
+    outs = []
+    for x in (a, b, (a + b).astype(np.float16)):
+        c = torch.empty(1, n, dtype=torch.float32, device="cuda")
+        ctx.exl3_gemm(H.to_dev(x), dtr, c, dsuh, None, dsvh)
+        outs.append(c.cpu().numpy())
+    ctx.poll_status()
+    assert H.rel_rms_err(outs[0] + outs[1], outs[2]) < 2e-3
+
+
+def test_gemm_rejects_bad_arguments(ctx):
+    import exl3b200
+    torch = _torch()
+    a = torch.zeros(1, 100, dtype=torch.float16, device="cuda")
+    tr = torch.zeros(100 // 16 + 1, 8, 64, dtype=torch.int16, device="cuda")
+    c = torch.zeros(1, 128, dtype=torch.float16, device="cuda")
+    with pytest.raises(exl3b200.Exl3Error):
+        ctx.exl3_gemm(a, tr, c, None, None, None)
+    a = torch.zeros(1, 128, dtype=torch.float16, device="cuda")
+    tr = torch.zeros(8, 8, 64, dtype=torch.int16, device="cuda")
+    with pytest.raises(exl3b200.Exl3Error):
+        ctx.exl3_gemm(a, tr, c, None, None, None, mcg=True, mul1=True)

@@ -1,0 +1,295 @@
+#!/usr/bin/env python
+"""Benchmark of the ragged continuous-batching decode step (27B-class dense model, EXL3 4 bpw, paged fp16 KV).
+
+    python bench.py --gpus N --steps K --warmup W              # this library, one rank per GPU (torchrun for N > 1)
+    python bench.py --impl reference --steps K --warmup W      # CPU restatement of the same ops on the host cores
+
+Workload (per GPU, weak scaling: sequences are partitioned across GPUs, a weight replica and a paged pool per GPU, no
+collective on the step): 32 sequences = 28 decoding one token + 4 prefill chunks of 256 tokens, contexts uniform in
+[512, 16384], 64 layers, hidden 5120, 40 q / 8 kv heads, head_dim 128, MLP 17408, vocab 151936, all weights seeded
+random EXL3 codes.  The 256-sequence batch of the full configuration is this shard times 8 GPUs; on fewer GPUs the
+fp16 KV of 256 sequences (about 567 GB) does not fit, so every GPU always holds 32 sequences.
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "exllamav3-rs_b200"))
+
+CFG = dict(n_layers=64, hidden=5120, nq=40, nkv=8, hd=128, inter=17408, vocab=151936, K=4, cb=1)
+SEQ_PER_GPU, N_PREFILL, CHUNK = 32, 4, 256
+CTX_LO, CTX_HI = 512, 16384
+
+
+def shard_batch(rank, seed=1234):
+    """Per-rank sequences: (q_lens, ctx_lens, block_table, pages, ids)."""
+    r = np.random.default_rng(seed + rank)
+    q_lens = np.array([1] * (SEQ_PER_GPU - N_PREFILL) + [CHUNK] * N_PREFILL, np.int32)
+    ctx = r.integers(CTX_LO, CTX_HI + 1, SEQ_PER_GPU).astype(np.int32)
+    need = (ctx + q_lens + 255) // 256
+    pps = int(need.max())
+    pages = int(need.sum()) + 1
+    perm = r.permutation(pages).astype(np.int32)
+    bt = np.zeros((SEQ_PER_GPU, pps), np.int32)
+    o = 0
+    for b in range(SEQ_PER_GPU):
+        bt[b, :need[b]] = perm[o:o + need[b]]
+        o += need[b]
+    ids = r.integers(0, CFG["vocab"], int(q_lens.sum())).astype(np.int64)
+    return q_lens, ctx, bt, pages, ids
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz, self._stop = index, [], set(), None, threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                     nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
+            while not self._stop.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                time.sleep(0.05)
+        except Exception as e:  # NVML missing: report that rather than invent numbers
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self):
+        self._stop.set()
+        self.join(timeout=2)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def cpu_sample(steps=10, warmup=1):
+    """Bounded CPU sample of the same step: ONE layer of the model (full widths) over 8 decode rows with contexts in
+    [512, 2048], composed from the oracle's ops; a whole step is 64 such layers plus the head, so tokens/s is
+    rows / (64 * t_layer).  Returns (tokens_per_s, seconds_per_layer, threads)."""
+    from oracle import oracle as O
+    from oracle import oracle_model
+    r = np.random.default_rng(7)
+    c = CFG
+    rows = 8
+
+    def lin(k, n):
+        return dict(trellis=r.integers(-32768, 32768, size=(k // 16, n // 16, 16 * c["K"]), dtype=np.int16),
+                    suh=(r.integers(0, 2, k) * 2 - 1).astype(np.float16),
+                    svh=((r.integers(0, 2, n) * 2 - 1) / np.sqrt(k)).astype(np.float16), K=c["K"], cb=c["cb"])
+
+    ctx = r.integers(512, 2049, rows).astype(np.int32)
+    need = (ctx + 1 + 255) // 256
+    pages = int(need.sum()) + 1
+    bt = np.zeros((rows, int(need.max())), np.int32)
+    o = 0
+    for b in range(rows):
+        bt[b, :need[b]] = np.arange(o, o + need[b]); o += need[b]
+    hid, nq, nkv, hd = c["hidden"], c["nq"], c["nkv"], c["hd"]
+    layer = dict(q_proj=lin(hid, nq * hd), k_proj=lin(hid, nkv * hd), v_proj=lin(hid, nkv * hd), o_proj=lin(nq * hd, hid),
+                 gate_proj=lin(hid, c["inter"]), up_proj=lin(hid, c["inter"]), down_proj=lin(c["inter"], hid),
+                 attn_norm=np.ones(hid, np.float16), mlp_norm=np.ones(hid, np.float16),
+                 q_norm=np.ones(hd, np.float16), k_norm=np.ones(hd, np.float16),
+                 k_cache=(0.5 * r.standard_normal((pages, 256, nkv, hd))).astype(np.float16),
+                 v_cache=(0.5 * r.standard_normal((pages, 256, nkv, hd))).astype(np.float16))
+    small_vocab = 1024     # the head is excluded from the sample (one layer only); a tiny head keeps the call valid
+    m = dict(cfg=dict(c, vocab=small_vocab, kv_bits=0), embed=r.standard_normal((small_vocab, hid)).astype(np.float16),
+             final_norm=np.ones(hid, np.float16), inv_freq=(1.0 / (1e6 ** (np.arange(0, hd, 2) / hd))).astype(np.float32),
+             lm_head=dict(lin(hid, small_vocab)), layers=[layer])
+    ids = r.integers(0, small_vocab, rows).astype(np.int64)
+    q_lens = np.ones(rows, np.int32)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        oracle_model.step(m, ids, q_lens, ctx, bt)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    t_layer = float(np.mean(times))
+    return rows / (c["n_layers"] * t_layer), t_layer, O.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tps, t_layer, threads = cpu_sample(steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    sample = ("one layer of the 64 (full widths, 4 bpw) over 8 decode rows, contexts in [512, 2048], composed from "
+              "oracle/ ops; step time extrapolated as 64 x layer time")
+    line = {"impl": "reference", "metric": "ragged decode-step tokens/s", "value": tps, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 64e3 * t_layer,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+            "config": {"workload": WORKLOAD_NAME},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+WORKLOAD_NAME = ("27B-class dense decode step, 4 bpw EXL3, fp16 paged KV: per GPU 28 decode rows + 4 prefill chunks of 256 "
+                 "(1052 packed rows, 32 sequences), contexts U[512,16384]")
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1400.0, "fallback"
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import exl3b200
+    from exl3b200.step import SyntheticModel
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = f"cuda:{local}"
+    ctx = exl3b200.Ctx(local, workspace_bytes=1 << 30)
+    q_lens, ctx_lens, bt, pages, ids = shard_batch(rank)
+    rows, bsz = int(q_lens.sum()), len(q_lens)
+    model = SyntheticModel(pages=pages, kv_bits=0, seed=100 + rank, device=dev, **CFG)
+    model.fill_kv(seed=200 + rank)
+    torch.cuda.synchronize()
+
+    # host-side (pinned) step inputs for the end-to-end leg, device-resident copies for the kernel-only leg
+    h_ids = torch.from_numpy(ids).pin_memory(); h_q = torch.from_numpy(q_lens).pin_memory()
+    h_sl = torch.from_numpy(ctx_lens).pin_memory(); h_bt = torch.from_numpy(bt).pin_memory()
+    d_ids, d_q, d_sl, d_bt = h_ids.to(dev), h_q.to(dev), h_sl.to(dev), h_bt.to(dev)
+    max_q = int(q_lens.max())
+    stream = torch.cuda.current_stream()
+
+    def step_resident():
+        return model.step(ctx, d_ids, d_q, d_sl, d_bt, max_q)[0]
+
+    def step_e2e():
+        d_ids.copy_(h_ids, non_blocking=True); d_q.copy_(h_q, non_blocking=True)
+        d_sl.copy_(h_sl, non_blocking=True); d_bt.copy_(h_bt, non_blocking=True)
+        tok = model.step(ctx, d_ids, d_q, d_sl, d_bt, max_q)[0]
+        return tok.cpu()                       # device -> host read of the sampled tokens (synchronises)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    ctx.poll_status()
+    sampler = ClockSampler(local)
+    sampler.start()
+    l0 = ctx.launch_count()
+    ms_total = timed(step_resident, args.steps)
+    launches = (ctx.launch_count() - l0) // max(args.steps, 1)
+    clocks = sampler.stop()
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    ctx.poll_status()
+
+    ms_step = ms_total / args.steps
+    total_rows = rows * world
+    value = total_rows / (ms_step * 1e-3)
+    e2e_value = total_rows / (ms_e2e / args.steps * 1e-3)
+    h2d = int(ids.nbytes + q_lens.nbytes + ctx_lens.nbytes + bt.nbytes)
+
+    # ---- roofline of the dominant kernel: the EXL3 GEMM at the step's row count, timed on L2-cold weights (the 64
+    # layers' gate_proj tensors in turn; 44.6 MB each, 2.9 GB in total)
+    hbm_peak, tf_peak, which = peaks()
+    roof = None
+    if rank == 0:
+        x = (torch.randn(rows, CFG["hidden"], device=dev) * 0.1).to(torch.float16)
+        y = torch.empty(rows, CFG["inter"], dtype=torch.float16, device=dev)
+        lins = [L["gate_proj"] for L in model.layers]
+        for l in lins[:3]:
+            ctx.exl3_gemm(x, l.trellis, y, l.suh, None, l.svh, mcg=True)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        g0 = ctx.launch_count()
+        e0.record(stream)
+        for l in lins:
+            ctx.exl3_gemm(x, l.trellis, y, l.suh, None, l.svh, mcg=True)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        t_op = e0.elapsed_time(e1) * 1e-3 / len(lins)
+        flops = 2.0 * rows * CFG["hidden"] * CFG["inter"]
+        ach = flops / t_op / 1e12
+        kv_bytes = float((ctx_lens + q_lens).sum()) * CFG["nkv"] * CFG["hd"] * 2 * 2 * CFG["n_layers"]
+        step_bytes = model.weight_bytes() + kv_bytes
+        roof = {"bound": "tensor", "kernel": "exl3_gemm (gate_proj 5120x17408, M=%d)" % rows, "achieved": ach,
+                "peak": tf_peak, "unit": "TFLOP/s", "frac": ach / tf_peak, "traffic": None, "peak_source": which,
+                "launches_per_op": (ctx.launch_count() - g0) // len(lins), "op_ms": t_op * 1e3,
+                "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9, "step_hbm_frac": step_bytes / (ms_step * 1e-3) / 1e9 / hbm_peak}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tps, t_layer, threads = cpu_sample()
+        cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": "one layer of the 64 (full widths) over 8 decode rows, contexts in [512, 2048], oracle/ ops; "
+                         "step time extrapolated as 64 x layer time (%.2f s per layer)" % t_layer}
+    if rank == 0:
+        line = {"metric": "ragged decode-step tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+                "config": {"workload": WORKLOAD_NAME, "rows_per_gpu": rows, "sequences_per_gpu": bsz,
+                           "generated_tokens_per_s": bsz * world / (ms_step * 1e-3),
+                           "l2": "inputs larger than L2 (11 GB of weights and the KV pool are streamed every step)"},
+                "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                        "d2h_bytes_per_step": bsz * 8},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

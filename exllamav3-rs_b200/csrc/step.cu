@@ -1,0 +1,191 @@
+// Step runner: one forward pass of a dense EXL3 transformer over a packed ragged batch, with the per-row descriptors
+// built on the device.  Op order and dtypes follow the reference's forward_paged_batched (src/model.rs:1171-1194),
+// TransformerBlock::forward (src/modules.rs:1020-1035), Attention::forward (:634-789), GatedMlp::forward (:932-940)
+// and finalize_head (src/model.rs:1038-1050): fp32 residual stream, fp16 activations, residual adds fused into the
+// next RMSNorm.
+#include "common.cuh"
+
+namespace {
+
+__global__ void __launch_bounds__(1024) build_desc_kernel(const int32_t* __restrict__ q_lens,
+                                                          const int32_t* __restrict__ seqlens, int bsz, int rows,
+                                                          int32_t* __restrict__ cu_q, int32_t* __restrict__ row_pos,
+                                                          int32_t* __restrict__ last_row)
+{
+    __shared__ int s_scan[1024];
+    __shared__ int s_carry;
+    const int tid = threadIdx.x;
+    if (tid == 0) { s_carry = 0; cu_q[0] = 0; }
+    __syncthreads();
+    for (int b0 = 0; b0 < bsz; b0 += 1024) {
+        const int b = b0 + tid;
+        const int ql = b < bsz ? q_lens[b] : 0;
+        s_scan[tid] = ql;
+        __syncthreads();
+        for (int o = 1; o < 1024; o <<= 1) {
+            int v = tid >= o ? s_scan[tid - o] : 0;
+            __syncthreads();
+            s_scan[tid] += v;
+            __syncthreads();
+        }
+        if (b < bsz) {
+            const int end = s_carry + s_scan[tid];
+            cu_q[b + 1] = end;
+            last_row[b] = (ql > 0 && end <= rows) ? end - 1 : -1;
+            const int start = end - ql, pos0 = seqlens[b];
+            for (int i = 0; i < ql && start + i < rows; ++i) row_pos[start + i] = pos0 + i;
+        }
+        __syncthreads();
+        if (tid == 1023) s_carry += s_scan[1023];
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(256) advance_kernel(int32_t* seqlens, const int32_t* q_lens, int bsz)
+{
+    const int b = blockIdx.x * 256 + threadIdx.x;
+    if (b < bsz) seqlens[b] += q_lens[b];
+}
+
+// out[i] = in[idx[i]] (16-byte chunks); rows with idx < 0 are zero-filled
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                          const int32_t* __restrict__ idx, int n_out, int chunks)
+{
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (long long)n_out * chunks) return;
+    const int r = (int)(i / chunks), c = (int)(i % chunks);
+    const int src = idx[r];
+    out[i] = src >= 0 ? in[(size_t)src * chunks + c] : make_uint4(0, 0, 0, 0);
+}
+
+struct Scratch {
+    int32_t *cu_q, *row_pos, *last_row;
+    float *resid, *resid_last;
+    half *a_in, *q, *k, *v, *attn_o, *proj, *gate, *up, *act, *pend_last, *y_last;
+    float* logits;
+};
+
+size_t carve(const exl3_model* m, int max_rows, int max_bsz, uint8_t* base, Scratch* s)
+{
+    size_t off = 0;
+    auto take = [&](size_t bytes) -> void* {
+        off = (off + 255) & ~(size_t)255;
+        void* p = base ? base + off : nullptr;
+        off += bytes;
+        return p;
+    };
+    const size_t R = max_rows, B = max_bsz;
+    Scratch t;
+    t.cu_q = (int32_t*)take((B + 1) * 4);
+    t.row_pos = (int32_t*)take(R * 4);
+    t.last_row = (int32_t*)take(B * 4);
+    t.resid = (float*)take(R * m->hidden * 4);
+    t.resid_last = (float*)take(B * m->hidden * 4);
+    t.a_in = (half*)take(R * m->hidden * 2);
+    t.q = (half*)take(R * m->nq * m->hd * 2);
+    t.k = (half*)take(R * m->nkv * m->hd * 2);
+    t.v = (half*)take(R * m->nkv * m->hd * 2);
+    t.attn_o = (half*)take(R * m->nq * m->hd * 2);
+    t.proj = (half*)take(R * m->hidden * 2);
+    t.gate = (half*)take(R * m->inter * 2);
+    t.up = (half*)take(R * m->inter * 2);
+    t.act = (half*)take(R * m->inter * 2);
+    t.pend_last = (half*)take(B * m->hidden * 2);
+    t.y_last = (half*)take(B * m->hidden * 2);
+    t.logits = (float*)take(B * (size_t)m->vocab * 4);
+    if (s) *s = t;
+    return (off + 255) & ~(size_t)255;
+}
+
+int linear(exl3_ctx* ctx, exl3_stream st, const exl3_linear& w, const void* x, void* y, int rows, int c_fp32)
+{
+    return exl3_gemm(ctx, st, x, w.trellis, y, w.suh, nullptr, w.svh, rows, w.k, w.n, w.K, c_fp32, w.cb == 1, w.cb == 2);
+}
+
+}  // namespace
+
+extern "C" size_t exl3_step_scratch_bytes(const exl3_model* model, int max_rows, int max_bsz)
+{
+    if (!model || max_rows <= 0 || max_bsz <= 0) return 0;
+    return carve(model, max_rows, max_bsz, nullptr, nullptr);
+}
+
+extern "C" int exl3_step_build_descriptors(exl3_ctx* ctx, exl3_stream stream, const int32_t* q_lens,
+                                           const int32_t* cache_seqlens, int bsz, int rows, int32_t* cu_q,
+                                           int32_t* row_pos, int32_t* last_row)
+{
+    EXL3_REQUIRE(ctx && q_lens && cache_seqlens && cu_q && row_pos && last_row, "step_build_descriptors: null argument");
+    EXL3_REQUIRE(bsz > 0 && rows >= 0, "step_build_descriptors: bad shape");
+    build_desc_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(q_lens, cache_seqlens, bsz, rows, cu_q, row_pos, last_row);
+    ctx->launches++;
+    return exl3_check_launch(ctx, "step_build_descriptors");
+}
+
+#define STEP_TRY(expr) do { int rc_ = (expr); if (rc_ != EXL3_OK) return rc_; } while (0)
+
+extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_model* m, const exl3_batch* b,
+                                 void* scratch, size_t scratch_bytes, int64_t* out_tokens, float* logits)
+{
+    EXL3_REQUIRE(ctx && m && b && scratch && out_tokens, "step_forward: null argument");
+    EXL3_REQUIRE(m->layers && m->n_layers > 0 && m->embed && m->final_norm && m->inv_freq, "step_forward: incomplete model");
+    EXL3_REQUIRE(b->ids && b->q_lens && b->cache_seqlens && b->block_table, "step_forward: incomplete batch");
+    EXL3_REQUIRE(b->bsz > 0 && b->rows > 0 && b->max_q_len > 0 && b->pages_per_seq > 0, "step_forward: bad batch shape");
+    EXL3_REQUIRE(aligned16(scratch), "step_forward: scratch must be 16-byte aligned");
+    EXL3_REQUIRE(m->kv_bits == 0 || (m->kv_bits >= 2 && m->kv_bits <= 8), "step_forward: kv_bits must be 0 or 2..8");
+    Scratch s;
+    const size_t need = carve(m, b->rows, b->bsz, (uint8_t*)scratch, &s);
+    if (need > scratch_bytes) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "step_forward: scratch buffer too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int rows = b->rows, bsz = b->bsz, hidden = m->hidden;
+
+    STEP_TRY(exl3_step_build_descriptors(ctx, stream, b->q_lens, b->cache_seqlens, bsz, rows, s.cu_q, s.row_pos, s.last_row));
+    STEP_TRY(exl3_embed(ctx, stream, b->ids, m->embed, s.resid, rows, hidden, m->vocab));
+
+    const half* pending = nullptr;      // output of the previous block's MLP, added to the residual by the next norm
+    for (int l = 0; l < m->n_layers; ++l) {
+        const exl3_layer& L = m->layers[l];
+        if (pending) STEP_TRY(exl3_rms_norm_res_in(ctx, stream, pending, 0, L.attn_norm, s.a_in, 0, s.resid, m->norm_eps, 0.f, 1.f, rows, hidden));
+        else         STEP_TRY(exl3_rms_norm(ctx, stream, s.resid, 1, L.attn_norm, s.a_in, 0, m->norm_eps, 0.f, 1.f, rows, hidden));
+        STEP_TRY(linear(ctx, stream, L.q_proj, s.a_in, s.q, rows, 0));
+        STEP_TRY(linear(ctx, stream, L.k_proj, s.a_in, s.k, rows, 0));
+        STEP_TRY(linear(ctx, stream, L.v_proj, s.a_in, s.v, rows, 0));
+        STEP_TRY(exl3_rope(ctx, stream, s.q, s.k, m->inv_freq, m->n_freq, 0, nullptr, s.row_pos, L.q_norm, L.k_norm,
+                           m->norm_eps, 0.f, m->rope_mode, m->attn_factor, 1, rows, m->nq, m->nkv, m->hd));
+        if (m->kv_bits == 0)
+            STEP_TRY(exl3_bighead_attn_paged(ctx, stream, s.q, s.k, s.v, L.k_cache, L.v_cache, b->block_table,
+                                             b->cache_seqlens, s.cu_q, s.attn_o, bsz, b->max_q_len, rows, m->nq, m->nkv,
+                                             m->hd, m->pages, b->pages_per_seq, 256, 1, 0.f));
+        else
+            STEP_TRY(exl3_bighead_attn_paged_q(ctx, stream, s.q, s.k, s.v, L.qk, L.sk, L.qv, L.sv, b->block_table,
+                                               b->cache_seqlens, s.cu_q, s.attn_o, bsz, b->max_q_len, rows, m->nq,
+                                               m->nkv, m->hd, m->pages, b->pages_per_seq, m->kv_bits, m->kv_bits, 256, 1,
+                                               0.f, 0.f));
+        STEP_TRY(linear(ctx, stream, L.o_proj, s.attn_o, s.proj, rows, 0));
+        STEP_TRY(exl3_rms_norm_res_in(ctx, stream, s.proj, 0, L.mlp_norm, s.a_in, 0, s.resid, m->norm_eps, 0.f, 1.f, rows, hidden));
+        STEP_TRY(linear(ctx, stream, L.gate_proj, s.a_in, s.gate, rows, 0));
+        STEP_TRY(linear(ctx, stream, L.up_proj, s.a_in, s.up, rows, 0));
+        STEP_TRY(exl3_silu_mul(ctx, stream, s.gate, s.up, s.act, 0.f, (int64_t)rows * m->inter));
+        STEP_TRY(linear(ctx, stream, L.down_proj, s.act, s.proj, rows, 0));
+        pending = s.proj;
+    }
+
+    // head: only the last row of every sequence (src/model.rs:1038-1050 last_only), logits in fp32
+    {
+        const long long it = (long long)bsz * (hidden * 4 / 16);
+        gather_rows_kernel<<<(unsigned)((it + 255) / 256), 256, 0, st>>>((const uint4*)s.resid, (uint4*)s.resid_last, s.last_row, bsz, hidden * 4 / 16);
+        const long long ih = (long long)bsz * (hidden * 2 / 16);
+        gather_rows_kernel<<<(unsigned)((ih + 255) / 256), 256, 0, st>>>((const uint4*)pending, (uint4*)s.pend_last, s.last_row, bsz, hidden * 2 / 16);
+        ctx->launches += 2;
+        STEP_TRY(exl3_check_launch(ctx, "step gather"));
+    }
+    STEP_TRY(exl3_rms_norm_res_in(ctx, stream, s.pend_last, 0, m->final_norm, s.y_last, 0, s.resid_last, m->norm_eps, 0.f, 1.f, bsz, hidden));
+    float* lg = logits ? logits : s.logits;
+    STEP_TRY(linear(ctx, stream, m->lm_head, s.y_last, lg, bsz, 1));
+    STEP_TRY(exl3_argmax_sample(ctx, stream, lg, 1, out_tokens, bsz, m->vocab, 0));
+    if (b->advance) {
+        advance_kernel<<<(bsz + 255) / 256, 256, 0, st>>>(b->cache_seqlens, b->q_lens, bsz);
+        ctx->launches++;
+        STEP_TRY(exl3_check_launch(ctx, "step advance"));
+    }
+    return EXL3_OK;
+}

@@ -206,6 +206,72 @@ EXL3_API int64_t exl3_cuda_free_mib(void);
 /* exl3_shim_set_mma_attn (src/ffi.rs:201): 1 = tensor-core attention kernels (default), 0 = scalar kernels for A/B */
 EXL3_API void exl3_set_mma_attn(exl3_ctx* ctx, int on);
 
+/* ------------------------------------------------------------------------------- step-level entry points
+ * The decode step of the reference is host code that builds `ids / block_table / seqlens`, copies them to the device
+ * and walks the layers issuing one shim call per op (src/generator.rs:1541-1581 decode_round, :1329-1352
+ * prefill_round, :1667-1704 spec_verify_round; src/model.rs:1171-1194 forward_paged_batched;
+ * src/modules.rs:634-789,932-940,1020-1035).  Here one call runs the whole step over a PACKED ragged batch: decode
+ * rows (1 token), verify rows (a few tokens) and prefill chunks (up to a page) of different sequences share every
+ * GEMM, and the per-row descriptors are built on the device.  The result equals running the reference's calls
+ * sequence by sequence. */
+
+typedef struct {
+    const void* trellis;   /* [k/16, n/16, 16*K] int16 */
+    const void* suh;       /* [k] fp16 */
+    const void* svh;       /* [n] fp16 */
+    int k, n, K, cb;       /* cb: 0 3INST, 1 MCG, 2 MUL1 */
+} exl3_linear;
+
+typedef struct {
+    exl3_linear q_proj, k_proj, v_proj, o_proj, gate_proj, up_proj, down_proj;
+    const void* attn_norm; /* [hidden] fp16 */
+    const void* mlp_norm;  /* [hidden] fp16 */
+    const void* q_norm;    /* [hd] fp16 or NULL */
+    const void* k_norm;    /* [hd] fp16 or NULL */
+    void* k_cache;         /* fp16 pool [pages,256,nkv,hd]              (kv_bits == 0) */
+    void* v_cache;
+    void* qk; void* sk;    /* quantised pools (kv_bits > 0), see exl3_bighead_attn_paged_q */
+    void* qv; void* sv;
+} exl3_layer;
+
+typedef struct {
+    int n_layers, hidden, nq, nkv, hd, inter, vocab;
+    int kv_bits;           /* 0 = fp16 KV pools, 2..8 = quantised pools */
+    int pages;             /* pages in every layer's pool */
+    float norm_eps;
+    float attn_factor;
+    int rope_mode;         /* EXL3_ROPE_* */
+    int n_freq;
+    const float* inv_freq; /* [n_freq] fp32, device */
+    const void* embed;     /* [vocab, hidden] fp16 */
+    const void* final_norm;/* [hidden] fp16 */
+    exl3_linear lm_head;
+    const exl3_layer* layers;   /* HOST array of n_layers entries (device pointers inside) */
+} exl3_model;
+
+typedef struct {
+    const int64_t* ids;         /* [rows] packed token ids, sequence after sequence */
+    const int32_t* q_lens;      /* [bsz] rows of each sequence in this step (0 allowed) */
+    int32_t* cache_seqlens;     /* [bsz] tokens already cached; advanced by q_lens at the end of the step when `advance` */
+    const int32_t* block_table; /* [bsz, pages_per_seq] */
+    int bsz, rows, max_q_len, pages_per_seq, advance;
+} exl3_batch;
+
+/* bytes of device scratch exl3_step_forward needs for up to `max_rows` packed rows and `max_bsz` sequences */
+EXL3_API size_t exl3_step_scratch_bytes(const exl3_model* model, int max_rows, int max_bsz);
+
+/* Device-side descriptor build (replaces the host loops of src/generator.rs:1548-1571): from q_lens/cache_seqlens it
+ * writes cu_q [bsz+1], row_pos [rows] (RoPE position of every packed row) and last_row [bsz] (row whose logits are
+ * sampled; -1 for empty sequences).  All outputs are device int32 arrays. */
+EXL3_API int exl3_step_build_descriptors(exl3_ctx* ctx, exl3_stream stream, const int32_t* q_lens,
+                                         const int32_t* cache_seqlens, int bsz, int rows, int32_t* cu_q,
+                                         int32_t* row_pos, int32_t* last_row);
+
+/* One forward step over the packed batch.  Writes the greedy token of every sequence to out_tokens [bsz] (int64,
+ * device; 0 for empty sequences) and, when logits != NULL, the fp32 logits [bsz, vocab] of the sampled rows. */
+EXL3_API int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_model* model, const exl3_batch* batch,
+                               void* scratch, size_t scratch_bytes, int64_t* out_tokens, float* logits);
+
 #ifdef __cplusplus
 }
 #endif

@@ -71,14 +71,16 @@ def fp16_ulp(x):
     return 2.0 ** (np.floor(np.log2(ax)) - 10)
 
 
-def gemm_mismatch(got, want, tol, fp16_out):
+def gemm_mismatch(got, want, tol, fp16_out, steps=1):
     """Worst violation of the GEMM parity bar: |got - want| <= tol * RMS(want).  For fp16 outputs a difference of one
     fp16 rounding step of the reference value is also accepted: two correct fp32 results that straddle a rounding
-    boundary differ by one step, which at |value| > 2*RMS already exceeds tol * RMS."""
+    boundary differ by one step, which at |value| > 2*RMS already exceeds tol * RMS.  `steps` = 2 is used against the
+    reference's CUDA GEMM, whose cross-CTA partial sums pass through the fp16 output buffer, and for multi-row
+    attention, where both sides round the softmax weights to fp16 before the PV product."""
     got = np.asarray(got, np.float64)
     want = np.asarray(want, np.float64)
     rms = np.sqrt((want * want).mean()) + 1e-30
     allowed = np.full(want.shape, tol * rms)
     if fp16_out:
-        allowed = np.maximum(allowed, fp16_ulp(want) * 1.001)
+        allowed = np.maximum(allowed, fp16_ulp(want) * (steps + 0.001))
     return float((np.abs(got - want) / allowed).max())

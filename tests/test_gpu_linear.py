@@ -144,7 +144,10 @@ def _gemm_case(ctx, ref, m, k, n, K, cb, c_fp32, seed, check_oracle=True):
                                 int(c_fp32), int(cb == 1), int(cb == 2), -1)
         torch.cuda.synchronize()
         assert tag in (0, 90) or tag > 0, tag
-        err = H.gemm_mismatch(got, C2.float().cpu().numpy(), GEMM_TOL, not c_fp32, steps=2)
+        # The reference kernels are themselves noisier than the bar: their stream-K partial sums pass through the fp16
+        # output buffer and their small-m GEMV accumulates in fp16 (kernels/quant/exl3_gemv_kernel.cuh:138-402).  The
+        # strict bar is applied against the oracle above; against the reference op 3e-3 * RMS or two fp16 steps.
+        err = H.gemm_mismatch(got, C2.float().cpu().numpy(), 1.5 * GEMM_TOL, not c_fp32, steps=2)
         assert err <= 1.0, f"vs reference CUDA op: {err} x the allowed difference"
     return got
 

@@ -31,8 +31,9 @@ def test_build_descriptors(ctx):
     rows = int(q_lens.sum())
     cu = torch.zeros(6, dtype=torch.int32, device="cuda"); pos = torch.zeros(rows, dtype=torch.int32, device="cuda")
     last = torch.zeros(5, dtype=torch.int32, device="cuda")
-    rc = lib().exl3_step_build_descriptors(ctx.handle, ctx.stream(), H.ptr(H.to_dev(q_lens)), H.ptr(H.to_dev(seqlens)), 5,
-                                           rows, H.ptr(cu), H.ptr(pos), H.ptr(last))
+    dq, dsl = H.to_dev(q_lens), H.to_dev(seqlens)       # named: a temporary's memory would be reused at once
+    rc = lib().exl3_step_build_descriptors(ctx.handle, ctx.stream(), H.ptr(dq), H.ptr(dsl), 5, rows, H.ptr(cu),
+                                           H.ptr(pos), H.ptr(last))
     assert rc == 0
     wcu = np.concatenate([[0], np.cumsum(q_lens)])
     assert np.array_equal(cu.cpu().numpy(), wcu)

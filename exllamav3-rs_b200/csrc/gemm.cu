@@ -158,3 +158,105 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
     }
     return EXL3_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// exl3_gemm_noalloc: the small-M EXL3 GEMM for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need a matrix product: code that runs
+// inside a memory-pool or allocator callback, a real-time decode loop whose latency budget forbids the implicit
+// device synchronisation an allocation can cause, or a plug-in that was handed a fixed device-memory budget and may
+// not grow it.  exl3_ctx_create allocates, so those callers cannot use exl3_gemm.  This entry point needs no context:
+// the scratch the kernel uses (the transformed activations, split-K partial sums, arrival counters, status word) lives
+// in the fixed array below, which is part of the library image.  Every GPU that loads the library holds these 8 MiB
+// until the process exits, whether or not the entry point is ever called.
+namespace {
+
+constexpr size_t NA_BYTES      = (size_t)8 << 20;      // whole scratch
+constexpr int    NA_MAX_M      = 16;                   // rows per call
+constexpr int    NA_MAX_K      = 32768;
+constexpr int    NA_MAX_N      = 524288;
+constexpr size_t NA_OFF_CNT    = 0;                                    // int[NA_MAX_N / 128] arrival counters
+constexpr size_t NA_OFF_STATUS = NA_OFF_CNT + (NA_MAX_N / 128) * 4;    // int status word (+ padding)
+constexpr size_t NA_OFF_ROWSUM = NA_OFF_STATUS + 256;                  // float[NA_MAX_M]
+constexpr size_t NA_OFF_ADUP   = NA_OFF_ROWSUM + 256;                  // uint32[NA_MAX_M][k]
+constexpr size_t NA_ADUP_BYTES = (size_t)NA_MAX_M * NA_MAX_K * 4;
+constexpr size_t NA_OFF_PART   = NA_OFF_ADUP + NA_ADUP_BYTES;          // float[splits][m][n]
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NA_BYTES];
+
+// In host code the name g_noalloc_scratch is only a handle for the runtime, not a device address; the address a
+// kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+struct NoAllocDev { unsigned char* base; int num_sms; bool ready; };
+NoAllocDev g_na_dev[64];
+
+int noalloc_setup(int dev, NoAllocDev** out)
+{
+    if (dev < 0 || dev >= 64) return EXL3_ERR_UNSUPPORTED;
+    NoAllocDev& d = g_na_dev[dev];
+    if (!d.ready) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            fprintf(stderr, "exl3_gemm_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+            cudaGetLastError();
+            return EXL3_ERR_CUDA;
+        }
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || sms <= 0) { cudaGetLastError(); return EXL3_ERR_CUDA; }
+        d.base = (unsigned char*)p; d.num_sms = sms; d.ready = true;
+    }
+    *out = &d;
+    return EXL3_OK;
+}
+
+}  // namespace
+
+extern "C" int exl3_gemm_noalloc(exl3_stream stream, const void* A, const void* trellis, void* C, const void* suh,
+                                 const void* svh, int m, int k, int n, int K, int c_fp32, int mcg, int mul1)
+{
+    if (!A || !trellis || !C) { fprintf(stderr, "exl3_gemm_noalloc: null argument\n"); return EXL3_ERR_INVALID; }
+    if (m < 0 || k <= 0 || n <= 0 || k % 128 || n % 128 || K < 1 || K > 8 || (mcg && mul1) || !aligned16(A) ||
+        !aligned16(trellis) || !aligned16(C) || !aligned16(suh) || !aligned16(svh)) {
+        fprintf(stderr, "exl3_gemm_noalloc: bad shape or alignment (k %% 128 == 0, n %% 128 == 0, K in 1..8, 16-byte aligned pointers)\n");
+        return EXL3_ERR_INVALID;
+    }
+    if (m > NA_MAX_M || k > NA_MAX_K || n > NA_MAX_N) {
+        fprintf(stderr, "exl3_gemm_noalloc: m=%d k=%d n=%d exceeds the fixed scratch (limits: m <= %d, k <= %d, n <= %d); "
+                        "use exl3_gemm with a context for larger problems\n", m, k, n, NA_MAX_M, NA_MAX_K, NA_MAX_N);
+        return EXL3_ERR_WORKSPACE;
+    }
+    if (m == 0) return EXL3_OK;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return EXL3_ERR_CUDA; }
+    NoAllocDev* d = nullptr;
+    int rc = noalloc_setup(dev, &d);
+    if (rc != EXL3_OK) return rc;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    const int cb = mcg ? 1 : (mul1 ? 2 : 0);
+    const int NB = n / 128, NST = k / 128;
+    int splits = (d->num_sms * 3 * 2 + NB - 1) / NB;
+    if (splits > NST / 2) splits = NST / 2;
+    const size_t part_room = NA_BYTES - NA_OFF_PART;
+    while (splits > 1 && (size_t)splits * m * n * 4 > part_room) splits /= 2;
+    if (splits < 1) splits = 1;
+
+    // the array keeps whatever the previous call left: counters and status must start at zero
+    if (cudaMemsetAsync(d->base + NA_OFF_CNT, 0, NA_OFF_ROWSUM - NA_OFF_CNT, st) != cudaSuccess) { cudaGetLastError(); return EXL3_ERR_CUDA; }
+    uint32_t* a_dup = (uint32_t*)(d->base + NA_OFF_ADUP);
+    float* rowsum = (float*)(d->base + NA_OFF_ROWSUM);
+    gemm_prologue_kernel<<<m, 256, 0, st>>>((const half*)A, (const half*)suh, a_dup, rowsum, k);
+    GemmSmallParams p;
+    p.a_dup = a_dup; p.rowsum = rowsum; p.trellis = (const uint32_t*)trellis;
+    p.partial = splits > 1 ? (float*)(d->base + NA_OFF_PART) : nullptr;
+    p.counters = (int*)(d->base + NA_OFF_CNT); p.svh = (const half*)svh; p.status = (int*)(d->base + NA_OFF_STATUS);
+    p.C = C; p.m = m; p.k = k; p.n = n; p.splits = splits; p.c_fp32 = c_fp32;
+    cudaError_t e = launch_small_k(K, cb, 1, p, dim3(NB, splits), st);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "exl3_gemm_noalloc: launch failed: %s\n", cudaGetErrorString(e));
+        cudaGetLastError();
+        return EXL3_ERR_CUDA;
+    }
+    return EXL3_OK;
+}

@@ -76,6 +76,19 @@ EXL3_API const char* exl3_version(void);
 EXL3_API int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const void* trellis, void* C, const void* suh,
               void* A_had, const void* svh, int m, int k, int n, int K, int c_fp32, int mcg, int mul1);
 
+/* No counterpart in the reference.  The same product as exl3_gemm for up to 16 rows, for callers that cannot allocate
+ * device memory (code running inside an allocator or memory-pool callback, latency-critical loops that must avoid the
+ * device synchronisation an allocation may trigger, plug-ins held to a fixed memory budget): it takes no context and
+ * calls no cudaMalloc / cudaFree or other allocating routine.  Its scratch is an 8 MiB array built into the library
+ * image, present on every GPU that loads the library until the process exits.
+ * Limits: m <= 16, k <= 32768, n <= 524288 (larger sizes return EXL3_ERR_WORKSPACE and print the limits to stderr).
+ * The first call on a device looks up the array's device address; make that first call outside any stream capture.
+ * All calls on a device share the one array, which still holds the previous call's contents (the entry point clears the
+ * parts that must start at zero on `stream`): two calls whose kernels can overlap on the GPU - different streams without
+ * an ordering between them - race on it.  Call with the target device current. */
+EXL3_API int exl3_gemm_noalloc(exl3_stream stream, const void* A, const void* trellis, void* C, const void* suh,
+                               const void* svh, int m, int k, int n, int K, int c_fp32, int mcg, int mul1);
+
 /* exl3_shim_reconstruct (src/ffi.rs:162, csrc/exl3_shim.cpp:162-164 -> kernels/quant/reconstruct.cu:375-386).
  * Dense fp16 W[k,n] from the packed tensor; bit-exact with the reference. */
 EXL3_API int exl3_reconstruct(exl3_ctx* ctx, exl3_stream stream, void* unpacked, const void* trellis, int k, int n, int K,

@@ -1,6 +1,7 @@
 // Context, CUDA-graph and memory entry points of libexl3b200.so.
 #include "common.cuh"
 #include <new>
+#include <stdlib.h>
 
 struct exl3_graph {
     exl3_ctx* ctx;
@@ -23,6 +24,7 @@ extern "C" int exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** ou
     memset(ctx, 0, sizeof(*ctx));
     ctx->device = device;
     ctx->mma_attn = 1;
+    ctx->use_tc = getenv("EXL3_B200_NO_TC") ? 0 : 1;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete ctx; cudaGetLastError(); return EXL3_ERR_CUDA; }
     if (prop.major != 10) {

@@ -40,6 +40,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// Warp-uniform bounded wait: every lane polls, the warp agrees on the outcome (keeps .aligned instructions and
+// __syncwarp that follow the wait convergent even if a time-out hits only some lanes).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22))
+{
+    const bool ok = mbar_wait(bar, parity, limit);
+    return __all_sync(0xffffffffu, ok);
+}
 // global -> shared bulk copy; dst/src 16-byte aligned, bytes % 16 == 0; completion counted on `bar`
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
 {

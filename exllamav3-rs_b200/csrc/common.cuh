@@ -24,6 +24,7 @@ struct exl3_ctx {
     cudaStream_t side_stream;
     uint64_t launches;
     int mma_attn;
+    int use_tc;             // 1: tcgen05 GEMM for large M (default), 0: small-M kernel in passes (for A/B runs)
     char err[256];
 };
 

@@ -1,5 +1,6 @@
 // exl3_gemm: host-side dispatch of the fused EXL3 trellis-decode GEMM.
 #include "gemm_small.cuh"
+#include "gemm_tc.cuh"
 
 namespace {
 
@@ -103,6 +104,124 @@ cudaError_t launch_small_k(int K, int cb, int mt, const GemmSmallParams& p, dim3
     }
 }
 
+
+// Input transform for the tensor-core path: plain fp16 A_had[row][k] (one CTA per row, as above without duplication).
+__global__ void __launch_bounds__(256) gemm_prologue_plain_kernel(const half* __restrict__ A, const half* __restrict__ suh,
+                                                                  half* __restrict__ a_had, int k)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t row = blockIdx.x;
+    for (int blk = warp; blk < k / 128; blk += 8) {
+        uint2 raw = reinterpret_cast<const uint2*>(A + row * k + blk * 128)[lane];
+        half2 a = *reinterpret_cast<half2*>(&raw.x), b = *reinterpret_cast<half2*>(&raw.y);
+        if (suh) {
+            uint2 sr = reinterpret_cast<const uint2*>(suh + blk * 128)[lane];
+            a = __hmul2(a, *reinterpret_cast<half2*>(&sr.x));
+            b = __hmul2(b, *reinterpret_cast<half2*>(&sr.y));
+            float v0 = __low2float(a), v1 = __high2float(a), v2 = __low2float(b), v3 = __high2float(b);
+            float s0 = v0 + v1, d0 = v0 - v1, s1 = v2 + v3, d1 = v2 - v3;
+            v0 = s0 + s1; v1 = d0 + d1; v2 = s0 - s1; v3 = d0 - d1;
+            #pragma unroll
+            for (int i = 1; i < 32; i <<= 1) {
+                float p0 = __shfl_xor_sync(0xffffffffu, v0, i), p1 = __shfl_xor_sync(0xffffffffu, v1, i);
+                float p2 = __shfl_xor_sync(0xffffffffu, v2, i), p3 = __shfl_xor_sync(0xffffffffu, v3, i);
+                const bool up = lane & i;
+                v0 = (up ? -v0 : v0) + p0; v1 = (up ? -v1 : v1) + p1;
+                v2 = (up ? -v2 : v2) + p2; v3 = (up ? -v3 : v3) + p3;
+            }
+            a = __floats2half2_rn(v0 * GS_R128, v1 * GS_R128);
+            b = __floats2half2_rn(v2 * GS_R128, v3 * GS_R128);
+        }
+        uint2 o; o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
+        reinterpret_cast<uint2*>(a_had + row * k + blk * 128)[lane] = o;
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_tiled()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+template <int K, int CB>
+cudaError_t launch_tc(const CUtensorMap& amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
+{
+    constexpr int bytes = TcSmem<K>::BYTES;
+    static bool configured[64] = {};
+    auto kern = gemm_tc_kernel<K, CB>;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kern<<<grid, TC_THREADS, bytes, st>>>(amap, p);
+    return cudaPeekAtLastError();
+}
+
+template <int K>
+cudaError_t launch_tc_cb(int cb, const CUtensorMap& amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
+{
+    if (cb == 0) return launch_tc<K, 0>(amap, p, grid, st);
+    if (cb == 1) return launch_tc<K, 1>(amap, p, grid, st);
+    return launch_tc<K, 2>(amap, p, grid, st);
+}
+
+cudaError_t launch_tc_k(int K, int cb, const CUtensorMap& amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
+{
+    switch (K) {
+        case 1: return launch_tc_cb<1>(cb, amap, p, grid, st);
+        case 2: return launch_tc_cb<2>(cb, amap, p, grid, st);
+        case 3: return launch_tc_cb<3>(cb, amap, p, grid, st);
+        case 4: return launch_tc_cb<4>(cb, amap, p, grid, st);
+        case 5: return launch_tc_cb<5>(cb, amap, p, grid, st);
+        case 6: return launch_tc_cb<6>(cb, amap, p, grid, st);
+        case 7: return launch_tc_cb<7>(cb, amap, p, grid, st);
+        default: return launch_tc_cb<8>(cb, amap, p, grid, st);
+    }
+}
+
+// Tensor-core path for rows [0, m): one launch of the input transform and one of the tcgen05 kernel.
+int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, const void* trellis, void* C, const half* suh,
+                 const half* svh, int m, int k, int n, int K, int c_fp32, int cb)
+{
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled is not available from this driver");
+    size_t off = 0;
+    half* a_had = (half*)exl3_ws_take(ctx, &off, (size_t)m * k * 2);
+    if (!a_had) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the activations");
+    gemm_prologue_plain_kernel<<<m, 256, 0, st>>>(A, suh, a_had, k);
+    ctx->launches++;
+    CUtensorMap amap;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a_had, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled failed");
+    GemmTcParams p;
+    p.trellis = (const uint32_t*)trellis; p.C = C; p.svh = svh; p.status = ctx->status;
+    p.m = m; p.k = k; p.n = n; p.c_fp32 = c_fp32;
+    cudaError_t e = launch_tc_k(K, cb, amap, p, dim3(n / TC_BN, (m + TC_BM - 1) / TC_BM), st);
+    ctx->launches++;
+    if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
+    return EXL3_OK;
+}
+
 }  // namespace
 
 // Rows are processed in passes of up to 64; each pass = input transform + one fused decode/MMA/output-transform launch.
@@ -123,7 +242,16 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
     const int NB = n / 128, NST = k / 128;
     EXL3_REQUIRE(NB <= ctx->n_counters, "exl3_gemm: n too large for the context's counters");
 
-    for (int row0 = 0; row0 < m; row0 += 64) {
+    // Large M with n % 256 == 0: tcgen05 kernel over 256-row blocks; a remainder of up to 64 rows (the decode rows of a
+    // mixed step) goes through the small-M kernel instead of a mostly empty 256-row block.
+    int tc_rows = 0;
+    if (m > 128 && n % TC_BN == 0 && ctx->use_tc) {
+        const int rem = m % TC_BM;
+        tc_rows = (rem != 0 && rem <= 64) ? m - rem : m;
+        int rc = gemm_tc_rows(ctx, st, (const half*)A, trellis, C, (const half*)suh, (const half*)svh, tc_rows, k, n, K, c_fp32, cb);
+        if (rc != EXL3_OK) return rc;
+    }
+    for (int row0 = tc_rows; row0 < m; row0 += 64) {
         const int rows = m - row0 < 64 ? m - row0 : 64;
         const int mt = rows <= 16 ? 1 : (rows <= 32 ? 2 : 4);
         size_t off = 0;

@@ -1,0 +1,289 @@
+// EXL3 GEMM for large M (prefill chunks, verify batches, big packed steps): a real contraction on the 5th-generation
+// tensor cores.  Activations arrive by TMA (tiled, 128-byte swizzle), trellis codes by bulk copies; eight decoder
+// warps turn codes into fp16 weights and write them straight into the K-major swizzled B operand tile in shared memory;
+// one thread issues tcgen05.mma with both accumulators (2 x 128 rows x 256 columns, all 512 TMEM columns) resident in
+// tensor memory; the epilogue reads TMEM, applies the 128-wide output Hadamard in registers and stores fp16/fp32.
+//
+// CTA tile: 256 rows x 256 columns, K step 64.  Roles: warp 0 = producer (TMA + bulk copies), warp 1 = MMA issuer and
+// TMEM owner, warps 2..9 = decoders, then epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+// Every mbarrier wait is bounded; a wait that runs out makes the CTA skip to the tear-down (TMEM is always freed) and
+// sets the status word.
+#pragma once
+#include <cuda.h>
+#include "common.cuh"
+#include "exl3_decode.cuh"
+#include "async_copy.cuh"
+
+namespace exl3 {
+
+constexpr int TC_BM = 256, TC_BN = 256, TC_BK = 64;
+constexpr int TC_SA = 3, TC_SR = 3, TC_SB = 2;          // stages: activations, raw codes, decoded weights
+constexpr int TC_THREADS = 320;                          // 10 warps
+constexpr int TC_A_STAGE = TC_BM * TC_BK * 2;            // 32 KB
+constexpr int TC_B_STAGE = TC_BN * TC_BK * 2;            // 32 KB
+constexpr float TC_R128 = 0.088388347648f;
+
+template <int K> struct TcSmem {
+    static constexpr int RAW_STAGE = (TC_BK / 16) * (TC_BN / 16) * 32 * K;      // 4 tile rows x 16 tiles x 32K bytes
+    static constexpr int OFF_A = 0;
+    static constexpr int OFF_B = OFF_A + TC_SA * TC_A_STAGE;
+    static constexpr int OFF_RAW = OFF_B + TC_SB * TC_B_STAGE;
+    static constexpr int OFF_SVH = OFF_RAW + TC_SR * RAW_STAGE;
+    static constexpr int OFF_BAR = OFF_SVH + TC_BN * 2;
+    static constexpr int N_BARS = 2 * TC_SA + 2 * TC_SR + 2 * TC_SB + 1;
+    static constexpr int OFF_TMEM = OFF_BAR + N_BARS * 8;
+    static constexpr int BYTES = OFF_TMEM + 16 + 1024;      // + slack to align the base to 1024 bytes
+};
+
+struct GemmTcParams {
+    const uint32_t* trellis;   // [k/16][n/16][8K] words
+    void* C;                   // [m][n] fp16 or fp32
+    const half* svh;           // [n] or NULL
+    int* status;
+    int m, k, n, c_fp32;
+};
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], fp16 inputs, fp32 accumulate
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32])
+{
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart (SBO), descriptor version 1
+__device__ __forceinline__ uint64_t tc_smem_desc(const void* p)
+{
+    const uint32_t a = smem_u32(p);
+    uint64_t d = 0;
+    d |= (uint64_t)((a >> 4) & 0x3fff);            // start address
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzled K-major; 1 as CUTLASS sets)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+    return d;
+}
+
+// instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = 256
+constexpr uint32_t TC_IDESC = (1u << 4) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+
+// in-register unnormalised 128-point Walsh-Hadamard transform (Sylvester order)
+__device__ __forceinline__ void fwht128(float (&v)[128])
+{
+    #pragma unroll
+    for (int h = 1; h < 128; h <<= 1) {
+        #pragma unroll
+        for (int i = 0; i < 128; i += 2 * h) {
+            #pragma unroll
+            for (int j = i; j < i + h; ++j) { const float a = v[j], b = v[j + h]; v[j] = a + b; v[j + h] = a - b; }
+        }
+    }
+}
+
+// grid (n / 256, ceil(m / 256)); the activations come through `amap` (A_had [m][k] fp16, box 64 x 256, 128B swizzle)
+template <int K, int CB>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const GemmTcParams p)
+{
+    using SM = TcSmem<K>;
+    extern __shared__ uint8_t smem_unaligned[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
+    uint64_t* a_full = bars;                 uint64_t* a_empty = a_full + TC_SA;
+    uint64_t* r_full = a_empty + TC_SA;      uint64_t* r_empty = r_full + TC_SR;
+    uint64_t* b_full = r_empty + TC_SR;      uint64_t* b_empty = b_full + TC_SB;
+    uint64_t* acc_full = b_empty + TC_SB;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::OFF_TMEM);
+    __shared__ int s_failed;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM;
+    const int tiles_n = p.n >> 4;
+    const int ksteps = p.k / TC_BK;
+
+    if (tid == 0) {
+        s_failed = 0;
+        for (int i = 0; i < TC_SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < TC_SR; ++i) { mbar_init(&r_full[i], 1); mbar_init(&r_empty[i], 8); }
+        for (int i = 0; i < TC_SB; ++i) { mbar_init(&b_full[i], 8); mbar_init(&b_empty[i], 1); }
+        mbar_init(acc_full, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (p.svh) for (int i = tid; i < TC_BN; i += TC_THREADS) reinterpret_cast<half*>(smem + SM::OFF_SVH)[i] = p.svh[n0 + i];
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        // ===== producer: activations by TMA, trellis codes by bulk copies
+        if (lane == 0) {
+            for (int ks = 0; ks < ksteps; ++ks) {
+                const int sa = ks % TC_SA, sr = ks % TC_SR;
+                if (ks >= TC_SA && !mbar_wait(&a_empty[sa], ((ks / TC_SA) - 1) & 1)) { failed = true; break; }
+                mbar_expect_tx(&a_full[sa], TC_A_STAGE);
+                tma_load_2d(smem + SM::OFF_A + sa * TC_A_STAGE, &amap, ks * TC_BK, m0, &a_full[sa]);
+                if (ks >= TC_SR && !mbar_wait(&r_empty[sr], ((ks / TC_SR) - 1) & 1)) { failed = true; break; }
+                mbar_expect_tx(&r_full[sr], SM::RAW_STAGE);
+                #pragma unroll
+                for (int r = 0; r < TC_BK / 16; ++r)
+                    bulk_g2s(smem + SM::OFF_RAW + sr * SM::RAW_STAGE + r * (TC_BN / 16) * 32 * K,
+                             p.trellis + ((size_t)(ks * (TC_BK / 16) + r) * tiles_n + (n0 >> 4)) * 8 * K,
+                             (TC_BN / 16) * 32 * K, &r_full[sr]);
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer
+        if (lane == 0) {
+            for (int ks = 0; ks < ksteps; ++ks) {
+                const int sa = ks % TC_SA, sb = ks % TC_SB;
+                if (!mbar_wait(&a_full[sa], (ks / TC_SA) & 1) || !mbar_wait(&b_full[sb], (ks / TC_SB) & 1)) { failed = true; break; }
+                tc_fence_after();
+                const uint64_t adesc0 = tc_smem_desc(smem + SM::OFF_A + sa * TC_A_STAGE);
+                const uint64_t adesc1 = tc_smem_desc(smem + SM::OFF_A + sa * TC_A_STAGE + 128 * 128);
+                const uint64_t bdesc = tc_smem_desc(smem + SM::OFF_B + sb * TC_B_STAGE);
+                #pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk) {
+                    const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+                    tc_mma_f16(tmem_base, adesc0 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);          // +32 bytes per K=16
+                    tc_mma_f16(tmem_base + TC_BN, adesc1 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);
+                }
+                tc_commit(&a_empty[sa]);      // arrive when the MMAs above have finished reading the stage
+                tc_commit(&b_empty[sb]);
+            }
+            if (!failed) tc_commit(acc_full);
+        }
+    } else {
+        // ===== decoders: raw codes -> fp16 weights in the K-major swizzled B tile
+        const int dw = warp - 2;                                   // 0..7: owns tiles nt = 2*dw, 2*dw+1 of every tile row
+        const int g = lane >> 2, t = lane & 3;
+        for (int ks = 0; ks < ksteps; ++ks) {
+            const int sr = ks % TC_SR, sb = ks % TC_SB;
+            if (!mbar_wait_warp(&r_full[sr], (ks / TC_SR) & 1)) { failed = true; break; }
+            if (ks >= TC_SB && !mbar_wait_warp(&b_empty[sb], ((ks / TC_SB) - 1) & 1)) { failed = true; break; }
+            const uint32_t* raw = reinterpret_cast<const uint32_t*>(smem + SM::OFF_RAW + sr * SM::RAW_STAGE);
+            uint8_t* bt = smem + SM::OFF_B + sb * TC_B_STAGE;
+            #pragma unroll
+            for (int r = 0; r < TC_BK / 16; ++r) {
+                #pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int nt = 2 * dw + q;
+                    uint32_t st[8];
+                    lane_states<K>(raw + (r * (TC_BN / 16) + nt) * 8 * K, lane, st);
+                    const half2 w0 = decode_pair<CB>(st[0], st[1]);      // rows 2t, 2t+1   col g
+                    const half2 w1 = decode_pair<CB>(st[2], st[3]);      // rows 2t+8, +9   col g
+                    const half2 w2 = decode_pair<CB>(st[4], st[5]);      // rows 2t, 2t+1   col g+8
+                    const half2 w3 = decode_pair<CB>(st[6], st[7]);      // rows 2t+8, +9   col g+8
+                    // B tile row = n (128 bytes = 64 k), 16-byte chunk index XOR (n & 7)
+                    const int na = nt * 16 + g, nb = na + 8;
+                    const int c0 = 2 * r, c1 = 2 * r + 1;                 // chunks of k = 16r + [0,8) and [8,16)
+                    uint8_t* ra = bt + na * 128; uint8_t* rb = bt + nb * 128;
+                    *reinterpret_cast<half2*>(ra + ((c0 ^ (na & 7)) << 4) + 4 * t) = w0;
+                    *reinterpret_cast<half2*>(ra + ((c1 ^ (na & 7)) << 4) + 4 * t) = w1;
+                    *reinterpret_cast<half2*>(rb + ((c0 ^ (nb & 7)) << 4) + 4 * t) = w2;
+                    *reinterpret_cast<half2*>(rb + ((c1 ^ (nb & 7)) << 4) + 4 * t) = w3;
+                }
+            }
+            fence_proxy_async();                 // make the generic-proxy stores visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&b_full[sb]); mbar_arrive(&r_empty[sr]); }
+        }
+    }
+
+    // ===== epilogue (warps 2..9): TMEM -> registers -> output transform -> global
+    if (warp >= 2 && !failed) {
+        if (!mbar_wait_warp(acc_full, 0)) failed = true;
+        if (!failed) {
+            tc_fence_after();
+            const int q = warp & 3, sel = (warp - 2) >> 2;            // TMEM lane quadrant, 128-column half of the tile
+            const half* svh_s = reinterpret_cast<const half*>(smem + SM::OFF_SVH) + sel * 128;
+            #pragma unroll 1
+            for (int mt = 0; mt < 2; ++mt) {
+                const int row = m0 + mt * 128 + q * 32 + lane;
+                float v[128];
+                #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float part[32];
+                    tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + mt * TC_BN + sel * 128 + j * 32, part);
+                    tc_wait_ld();
+                    #pragma unroll
+                    for (int e = 0; e < 32; ++e) v[j * 32 + e] = part[e];
+                }
+                if (p.svh) {
+                    fwht128(v);
+                    #pragma unroll
+                    for (int e = 0; e < 128; ++e) v[e] *= TC_R128;
+                }
+                if (row < p.m) {
+                    const size_t off = (size_t)row * p.n + n0 + sel * 128;
+                    if (p.c_fp32) {
+                        float4* dst = reinterpret_cast<float4*>((float*)p.C + off);
+                        #pragma unroll
+                        for (int e = 0; e < 128; e += 4) {
+                            float4 o = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                            if (p.svh) {
+                                o.x *= __half2float(svh_s[e]); o.y *= __half2float(svh_s[e + 1]);
+                                o.z *= __half2float(svh_s[e + 2]); o.w *= __half2float(svh_s[e + 3]);
+                            }
+                            dst[e >> 2] = o;
+                        }
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>((half*)p.C + off);
+                        #pragma unroll
+                        for (int e = 0; e < 128; e += 8) {
+                            uint32_t w[4];
+                            #pragma unroll
+                            for (int h = 0; h < 4; ++h) {
+                                half2 x = __floats2half2_rn(v[e + 2 * h], v[e + 2 * h + 1]);
+                                if (p.svh) x = __hmul2(x, *reinterpret_cast<const half2*>(svh_s + e + 2 * h));
+                                w[h] = *reinterpret_cast<uint32_t*>(&x);
+                            }
+                            dst[e >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ===== tear-down: every path arrives here; TMEM is released by the warp that allocated it
+    if (failed) s_failed = 1;
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+    if (tid == 0 && s_failed) atomicExch(p.status, 2);
+}
+
+}  // namespace exl3

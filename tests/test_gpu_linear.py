@@ -220,3 +220,68 @@ def test_gemm_rejects_bad_arguments(ctx):
     tr = torch.zeros(8, 8, 64, dtype=torch.int16, device="cuda")
     with pytest.raises(exl3b200.Exl3Error):
         ctx.exl3_gemm(a, tr, c, None, None, None, mcg=True, mul1=True)
+
+
+# ------------------------------------------------------------------------------------------ tensor-core (tcgen05) path
+
+@pytest.fixture(scope="module")
+def ctx_small_only():
+    """A second context with the tcgen05 path switched off: large M then runs as 64-row passes of the small-M kernel."""
+    import os
+    import exl3b200
+    os.environ["EXL3_B200_NO_TC"] = "1"
+    try:
+        c = exl3b200.Ctx(0)
+    finally:
+        del os.environ["EXL3_B200_NO_TC"]
+    yield c
+    c.close()
+
+
+def _tc_case(ctx, ctx_small_only, ref, m, k, n, K, cb, c_fp32, seed, oracle=False):
+    torch = _torch()
+    r = H.rng(seed)
+    A = r.standard_normal((m, k)).astype(np.float16)
+    tr = H.rand_trellis(r, k, n, K)
+    suh, svh = H.rand_signs(r, k), H.rand_signs(r, n)
+    dA, dtr, dsuh, dsvh = H.to_dev(A), H.to_dev(tr), H.to_dev(suh), H.to_dev(svh)
+    dt = torch.float32 if c_fp32 else torch.float16
+    c_tc = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+    c_sm = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+    ctx.exl3_gemm(dA, dtr, c_tc, dsuh, None, dsvh, mcg=cb == 1, mul1=cb == 2)
+    ctx.poll_status()
+    ctx_small_only.exl3_gemm(dA, dtr, c_sm, dsuh, None, dsvh, mcg=cb == 1, mul1=cb == 2)
+    ctx_small_only.poll_status()
+    got, want = c_tc.float().cpu().numpy(), c_sm.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    err = H.gemm_mismatch(got, want, GEMM_TOL, not c_fp32)
+    assert err <= 1.0, f"tensor-core path vs small-M path: {err} x the allowed difference"
+    if oracle:
+        from oracle import oracle as O
+        w = O.exl3_gemm(A, tr, suh, svh, K, cb, c_fp32=c_fp32).astype(np.float32)
+        assert H.gemm_mismatch(got, w, GEMM_TOL, not c_fp32) <= 1.0
+    if ref is not None:
+        C2 = torch.zeros_like(c_tc)
+        ah = torch.empty(m, k, dtype=torch.float16, device="cuda")
+        tag = ref.ref_exl3_gemm(H.ptr(dA), H.ptr(dtr), H.ptr(C2), H.ptr(dsuh), H.ptr(ah), H.ptr(dsvh), m, k, n, K,
+                                int(c_fp32), int(cb == 1), int(cb == 2), -1)
+        torch.cuda.synchronize()
+        assert tag >= 0
+        assert H.gemm_mismatch(got, C2.float().cpu().numpy(), 1.5 * GEMM_TOL, not c_fp32, steps=2) <= 1.0
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_gemm_tc_formats(ctx, ctx_small_only, K, cb):
+    _tc_case(ctx, ctx_small_only, None, 200, 512, 512, K, cb, False, 1000 + K * 3 + cb, oracle=True)
+
+
+@pytest.mark.parametrize("m", [129, 256, 257, 300, 320, 512, 1052])
+def test_gemm_tc_row_counts(ctx, ctx_small_only, ref, m):
+    """block edges, the zero-filled tail of the last 256-row block, and the 'remainder goes to the small kernel' split"""
+    _tc_case(ctx, ctx_small_only, ref if m <= 512 else None, m, 1024, 768, 4, 1, m % 2 == 0, 1100 + m)
+
+
+def test_gemm_tc_step_shape(ctx, ctx_small_only):
+    """the benchmark step's row count on the 5120 x 17408 projection"""
+    _tc_case(ctx, ctx_small_only, None, 1052, 5120, 17408, 4, 1, False, 1200)

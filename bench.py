@@ -277,15 +277,98 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_ops(args):
+    """Op-level measurements (not the headline line): --op gemm (one shape), gemm_sweep (K=5120, N=17408 sweep of
+    bits x M), attn (paged attention alone: 64 sequences, contexts log-uniform in [128, 32768], 40 q / 8 kv heads).
+    Every timed launch reads weights / KV that were not touched by the previous launch (a ring of tensors larger
+    than L2).  One JSON line per measurement."""
+    import torch
+    import exl3b200
+    torch.cuda.set_device(0)
+    ctx = exl3b200.Ctx(0, workspace_bytes=1 << 30)
+    hbm_peak, tf_peak, which = peaks()
+    stream = torch.cuda.current_stream()
+    g = torch.Generator(device="cuda"); g.manual_seed(5)
+
+    def time_calls(fns, reps):
+        for f in fns[:2]:
+            f()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        n = 0
+        for _ in range(reps):
+            for f in fns:
+                f(); n += 1
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / n
+
+    def gemm_point(m, k, n, K, reps, cb=1):
+        ring = max(2, min(8, int(300e6 // (k * n * K / 8)) + 1))        # > 126 MB of L2 between reuses
+        ws = [torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device="cuda", generator=g)
+              for _ in range(ring)]
+        suh = (torch.randint(0, 2, (k,), device="cuda", generator=g) * 2 - 1).to(torch.float16)
+        svh = (torch.randint(0, 2, (n,), device="cuda", generator=g) * 2 - 1).to(torch.float16)
+        a = torch.randn(m, k, device="cuda", generator=g).to(torch.float16)
+        c = torch.empty(m, n, dtype=torch.float16, device="cuda")
+        fns = [(lambda w=w: ctx.exl3_gemm(a, w, c, suh, None, svh, mcg=cb == 1, mul1=cb == 2)) for w in ws]
+        t = time_calls(fns, reps)
+        byts = k * n * K / 8 + 2 * (k + n) + 2 * m * k + 2 * m * n
+        fl = 2.0 * m * k * n
+        return {"op": "exl3_gemm", "m": m, "k": k, "n": n, "bits": K, "us": t * 1e6, "GBps": byts / t / 1e9,
+                "hbm_frac": byts / t / 1e9 / hbm_peak, "TFLOPs": fl / t / 1e12, "tensor_frac": fl / t / 1e12 / tf_peak,
+                "peaks": which}
+
+    if args.op == "gemm":
+        print(json.dumps(gemm_point(args.m, args.k, args.n, args.bits, args.reps)))
+    elif args.op == "gemm_sweep":
+        for K in (2, 3, 4, 5, 8):
+            for m in (1, 4, 16, 64, 256, 2048):
+                print(json.dumps(gemm_point(m, 5120, 17408, K, args.reps)))
+    elif args.op == "attn":
+        r = np.random.default_rng(3)
+        bsz, nq, nkv, hd, q_len = args.seqs, 40, 8, 128, args.m
+        ctx_lens = np.exp(r.uniform(np.log(128), np.log(32768), bsz)).astype(np.int32)
+        need = (ctx_lens + q_len + 255) // 256
+        pages = int(need.sum()) + 1
+        perm = r.permutation(pages).astype(np.int32)
+        bt = np.zeros((bsz, int(need.max())), np.int32)
+        o = 0
+        for b in range(bsz):
+            bt[b, :need[b]] = perm[o:o + need[b]]; o += need[b]
+        kc = (torch.randn(pages, 256, nkv, hd, device="cuda", generator=g) * 0.5).to(torch.float16)
+        vc = (torch.randn(pages, 256, nkv, hd, device="cuda", generator=g) * 0.5).to(torch.float16)
+        q = torch.randn(bsz, q_len, nq, hd, device="cuda", generator=g).to(torch.float16)
+        kn = (torch.randn(bsz, q_len, nkv, hd, device="cuda", generator=g) * 0.5).to(torch.float16)
+        out = torch.empty_like(q)
+        dbt, dsl = torch.from_numpy(bt).cuda(), torch.from_numpy(ctx_lens).cuda()
+        t = time_calls([lambda: ctx.bighead_attn_paged(q, kn, kn, kc, vc, dbt, dsl, out)], args.reps)
+        byts = float((ctx_lens + q_len).sum()) * nkv * hd * 2 * 2
+        print(json.dumps({"op": "bighead_attn_paged", "seqs": bsz, "q_len": q_len, "mean_ctx": float(ctx_lens.mean()),
+                          "kv_bytes": byts, "us": t * 1e6, "GBps": byts / t / 1e9, "hbm_frac": byts / t / 1e9 / hbm_peak,
+                          "note": "KV pool %.1f GB" % (kc.numel() * 4 / 1e9), "peaks": which}))
+    ctx.poll_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default=None, choices=["gemm", "gemm_sweep", "attn"])
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--k", type=int, default=5120)
+    ap.add_argument("--n", type=int, default=17408)
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--seqs", type=int, default=64)
+    ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.op:
+        run_ops(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -33,6 +33,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread may sleep up to `ns` nanoseconds inside the instruction instead of
+// returning at once, which keeps waiting warps from eating issue slots.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+// Bounded wait with sleeping polls (about limit * ns nanoseconds at most).
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 20), uint32_t ns = 2000)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait_hint(bar, parity, ns)) return true;
+    return false;
+}
 // Bounded wait: false when the phase did not complete within `limit` polls.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22))
 {

@@ -9,9 +9,10 @@ using namespace exl3;
 // Each sequence gets ceil(total_k / chunk) splits per row block, with chunk sized so that the list has about
 // `target_items` entries; the reference sizes its splits from the padded block-table width instead
 // (kernels/attention.cu:1805), which launches empty CTAs for the short sequences of a ragged batch.
+// Only sequences whose packed row count ql*G lies in (rows_lo, rows_hi] get work items; the others are left to another pass.
 __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restrict__ seqlens,
                                                          const int32_t* __restrict__ cu_q, int bsz, int q_len,
-                                                         int kv_append, int G, int rows_per_cta, int target_items,
+                                                         int kv_append, int G, int rows_per_cta, int rows_lo, int rows_hi, int target_items,
                                                          int max_items, AttnPlan* plan, AttnItem* items, int* seq_base,
                                                          int* seq_splits)
 {
@@ -25,7 +26,8 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
     for (int b = tid; b < bsz; b += 1024) {
         const int ql = cu_q ? cu_q[b + 1] - cu_q[b] : q_len;
         const int tk = seqlens[b] + (cu_q ? ql : kv_append);
-        const int rb = (ql * G + rows_per_cta - 1) / rows_per_cta;
+        const int pr = ql * G;
+        const int rb = (pr > rows_lo && pr <= rows_hi) ? (pr + rows_per_cta - 1) / rows_per_cta : 0;
         local += (long long)tk * rb;
     }
     atomicAdd((unsigned long long*)&s_total, (unsigned long long)local);
@@ -45,8 +47,9 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
         if (b < bsz) {
             ql = cu_q ? cu_q[b + 1] - cu_q[b] : q_len;
             tk = seqlens[b] + (cu_q ? ql : kv_append);
-            rb = (ql * G + rows_per_cta - 1) / rows_per_cta;
-            sp = tk > 0 ? (tk + chunk - 1) / chunk : 1;
+            const int pr = ql * G;
+            rb = (pr > rows_lo && pr <= rows_hi) ? (pr + rows_per_cta - 1) / rows_per_cta : 0;
+            sp = (rb > 0 && tk > 0) ? (tk + chunk - 1) / chunk : 1;
         }
         const int cnt = rb * sp;
         s_scan[tid] = cnt;
@@ -134,13 +137,14 @@ cudaError_t launch_attn(const AttnParams& p, dim3 grid, cudaStream_t st)
     return cudaPeekAtLastError();
 }
 
-int attn_impl(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int max_q_len, bool quant)
+// One pass = plan + attention + combine over the sequences whose packed row count lies in (rows_lo, rows_hi].
+int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int max_rows, int rows_lo, int rows_hi,
+              bool decode_shape, bool quant)
 {
     const int D = 128;
     const int G = p.nq / p.nkv;
-    const bool decode_shape = max_q_len * G <= 16;            // one 16-row tile: spread the keys over the 4 warps
     const int rows_per_cta = decode_shape ? 16 : 64;
-    const int rb_max = (max_q_len * G + rows_per_cta - 1) / rows_per_cta;
+    const int rb_max = (max_rows + rows_per_cta - 1) / rows_per_cta;
     const int grid_x = (ctx->num_sms * 3 + p.nkv - 1) / p.nkv;    // about 3 resident CTAs per SM over all kv heads
     const int target_items = grid_x * 2;
     const int max_items = target_items + p.bsz * rb_max + 1;
@@ -155,8 +159,8 @@ int attn_impl(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
         return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "attention: context scratch too small for the split-KV partials");
     p.plan = plan; p.items = items; p.seq_base = seq_base; p.seq_splits = seq_splits; p.partial = partial;
 
-    attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, target_items,
-                                          max_items, plan, items, seq_base, seq_splits);
+    attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, rows_lo, rows_hi,
+                                          target_items, max_items, plan, items, seq_base, seq_splits);
     ctx->launches++;
     dim3 grid(grid_x, p.nkv);
     cudaError_t e;
@@ -168,6 +172,20 @@ int attn_impl(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     attn_combine_kernel<128><<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(p, rows_per_cta, total_rows);
     ctx->launches++;
     return exl3_check_launch(ctx, "attention");
+}
+
+// Sequences with at most 16 packed (query, head) rows (decode, short verify) take the kernel that spreads the keys of a
+// tile over the four warps; longer ones (verify with many heads, prefill chunks) the one with a 16-row tile per warp.
+// A ragged batch that holds both kinds runs one pass for each.
+int attn_impl(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int max_q_len, bool quant)
+{
+    const int G = p.nq / p.nkv;
+    const int max_rows = max_q_len * G;
+    if (max_rows <= 16) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 16, true, quant);
+    if (!p.cu_q) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 1 << 30, false, quant);
+    int rc = attn_pass(ctx, st, p, total_rows, 16, 0, 16, true, quant);
+    if (rc != EXL3_OK) return rc;
+    return attn_pass(ctx, st, p, total_rows, max_rows, 16, 1 << 30, false, quant);
 }
 
 int check_common(exl3_ctx* ctx, const void* q, const void* o, const int32_t* bt, const int32_t* sl, int bsz, int q_len,

@@ -133,6 +133,11 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
             lim[h] = rvalid[h] ? (p.causal ? min(total_k, total_k - ql + qi[h] + 1) : total_k) : 0;
         }
 
+        // smallest visibility limit among this warp's valid rows: tiles entirely below it need no masking
+        int wlim = min(rvalid[0] ? lim[0] : 0x7fffffff, rvalid[1] ? lim[1] : 0x7fffffff);
+        #pragma unroll
+        for (int o = 16; o > 0; o >>= 1) wlim = min(wlim, __shfl_xor_sync(0xffffffffu, wlim, o));
+
         // ---- Q fragments (A operand), straight from global memory
         uint32_t qf[KSTEPS][4];
         #pragma unroll
@@ -159,14 +164,23 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
             const int k0 = k_begin + tile * AT_TK;
             uint8_t* sbase = smem_raw + stage * SM::STAGE;
             if constexpr (!QUANT) {
-                constexpr int CPR = D / 8;                       // 16-byte chunks per key row
-                for (int c = tid; c < AT_TK * CPR; c += AT_THREADS) {
-                    const int key = c / CPR, ch = c % CPR;
-                    int kj = k0 + key; if (kj >= k_end) kj = k_end - 1;          // clamp: masked later
-                    const size_t tok = (size_t)bt[kj >> 8] * EXL3_PAGE + (kj & 255);
-                    const size_t off = (tok * p.nkv + kvh) * D + ch * 8;
-                    cp_async16(sbase + key * SM::ROWB + ch * 16, p.kc + off);
-                    cp_async16(sbase + SM::TILE + key * SM::ROWB + ch * 16, p.vc + off);
+                // A tile of 64 keys starts at a multiple of 64, so it lies inside one 256-token page: one block-table
+                // lookup per tile.  Thread layout: 16-byte chunk tid % 16 of keys tid / 16 + 8 i (D = 128: 16 chunks per
+                // key row).  Keys past the end of the split repeat the last valid key (masked later).
+                static_assert(D == 128, "loader assumes 16 chunks per key row");
+                const size_t tok0 = (size_t)bt[k0 >> 8] * EXL3_PAGE + (k0 & 255);
+                const int kmax = k_end - 1 - k0;
+                const int ch = tid & 15, key0 = tid >> 4;
+                const size_t rstride = (size_t)p.nkv * D;
+                const half* kb = p.kc + (tok0 * p.nkv + kvh) * D + ch * 8;
+                const half* vb = p.vc + (tok0 * p.nkv + kvh) * D + ch * 8;
+                uint8_t* dk = sbase + ch * 16;
+                #pragma unroll
+                for (int i = 0; i < AT_TK / 8; ++i) {
+                    const int key = key0 + 8 * i;
+                    const size_t so = (size_t)min(key, kmax) * rstride;
+                    cp_async16(dk + key * SM::ROWB, kb + so);
+                    cp_async16(dk + SM::TILE + key * SM::ROWB, vb + so);
                 }
             } else {
                 const int groups = p.nkv * (D / 32), gpk = D / 32;
@@ -248,18 +262,30 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                 }
             }
             // ---- scale, mask, online softmax (base 2)
+            const bool need_mask = kbase + KEYS_W > wlim || kbase + KEYS_W > k_end;      // warp-uniform
             float mx[2] = {-INFINITY, -INFINITY};
-            #pragma unroll
-            for (int nb = 0; nb < NBLK; ++nb)
+            if (need_mask) {
                 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int h = e >> 1;
-                    const int key = kbase + nb * 8 + 2 * t + (e & 1);
-                    float v = s_acc[nb][e] * p.scale_log2;
-                    v = (key < lim[h] && key < k_end) ? v : -INFINITY;
-                    s_acc[nb][e] = v;
-                    mx[h] = fmaxf(mx[h], v);
-                }
+                for (int nb = 0; nb < NBLK; ++nb)
+                    #pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int h = e >> 1;
+                        const int key = kbase + nb * 8 + 2 * t + (e & 1);
+                        float v = s_acc[nb][e] * p.scale_log2;
+                        v = (key < lim[h] && key < k_end) ? v : -INFINITY;
+                        s_acc[nb][e] = v;
+                        mx[h] = fmaxf(mx[h], v);
+                    }
+            } else {
+                #pragma unroll
+                for (int nb = 0; nb < NBLK; ++nb)
+                    #pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float v = s_acc[nb][e] * p.scale_log2;
+                        s_acc[nb][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+            }
             float corr[2];
             #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -270,15 +296,17 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                 m_run[h] = m_new;
                 l_run[h] *= corr[h];
             }
-            #pragma unroll
-            for (int i = 0; i < DBLK; ++i) { o_acc[i][0] *= corr[0]; o_acc[i][1] *= corr[0]; o_acc[i][2] *= corr[1]; o_acc[i][3] *= corr[1]; }
+            if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+                #pragma unroll
+                for (int i = 0; i < DBLK; ++i) { o_acc[i][0] *= corr[0]; o_acc[i][1] *= corr[0]; o_acc[i][2] *= corr[1]; o_acc[i][3] *= corr[1]; }
+            }
+            // rows that have seen no key yet keep m = -inf: use 0 as the reference so that exp2(-inf - 0) = 0
+            const float mref0 = (m_run[0] == -INFINITY) ? 0.f : m_run[0], mref1 = (m_run[1] == -INFINITY) ? 0.f : m_run[1];
             uint32_t pf[NBLK][2];
             #pragma unroll
             for (int nb = 0; nb < NBLK; ++nb) {
-                float e0 = (m_run[0] == -INFINITY) ? 0.f : exp2f(s_acc[nb][0] - m_run[0]);
-                float e1 = (m_run[0] == -INFINITY) ? 0.f : exp2f(s_acc[nb][1] - m_run[0]);
-                float e2 = (m_run[1] == -INFINITY) ? 0.f : exp2f(s_acc[nb][2] - m_run[1]);
-                float e3 = (m_run[1] == -INFINITY) ? 0.f : exp2f(s_acc[nb][3] - m_run[1]);
+                const float e0 = exp2f(s_acc[nb][0] - mref0), e1 = exp2f(s_acc[nb][1] - mref0);
+                const float e2 = exp2f(s_acc[nb][2] - mref1), e3 = exp2f(s_acc[nb][3] - mref1);
                 l_run[0] += e0 + e1; l_run[1] += e2 + e3;
                 pf[nb][0] = pack_h2(e0, e1); pf[nb][1] = pack_h2(e2, e3);
             }

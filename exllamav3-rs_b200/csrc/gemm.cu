@@ -57,53 +57,80 @@ __global__ void __launch_bounds__(256) gemm_prologue_kernel(const half* __restri
     }
 }
 
+// Launch geometry of the persistent kernel: one CTA per resident slot (SMs x occupancy), never more than work units.
+struct SmallPlan { int grid; int max_contrib; size_t partial_bytes; };
+
 template <int K, int CB, int MT>
-cudaError_t launch_small(const GemmSmallParams& p, dim3 grid, cudaStream_t st)
+cudaError_t launch_small(GemmSmallParams& p, int num_sms, size_t partial_room, float* partial_base, cudaStream_t st,
+                         SmallPlan* plan_out)
 {
     constexpr int bytes = GemmSmallSmem<K, MT>::BYTES;
-    static bool configured[64] = {};    // per (K, CB, MT) instantiation and device: the attribute is per device
+    static int occ[64] = {};            // per (K, CB, MT) instantiation and device; 0 = not configured yet
     auto kern = gemm_small_kernel<K, CB, MT>;
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
+    int ctas_per_sm = (dev >= 0 && dev < 64) ? occ[dev] : 0;
+    if (ctas_per_sm == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, 256, bytes);
+        if (e != cudaSuccess) return e;
+        if (ctas_per_sm < 1) ctas_per_sm = 1;
+        if (dev >= 0 && dev < 64) occ[dev] = ctas_per_sm;
     }
-    kern<<<grid, 256, bytes, st>>>(p);
+    const int NST = p.k / 128;
+    const long long total = (long long)(p.n / 128) * NST;
+    long long grid = (long long)num_sms * ctas_per_sm;
+    if (grid > total) grid = total;
+    // a column block is shared by at most ceil(NST / units-per-CTA) + 1 CTAs; shrink the grid until the partials fit
+    int max_contrib;
+    size_t need;
+    for (;;) {
+        const long long upc = total / grid;
+        max_contrib = (int)((NST + upc - 1) / upc) + 1;
+        need = (size_t)(p.n / 128) * max_contrib * p.m * 128 * 4;
+        if (need <= partial_room || grid <= 1) break;
+        grid = grid / 2 > 0 ? grid / 2 : 1;
+    }
+    if (need > partial_room && grid > 1) return cudaErrorMemoryAllocation;
+    if (grid == 1) { max_contrib = 1; need = 0; }
+    p.partial = partial_base;
+    p.max_contrib = max_contrib;
+    if (plan_out) { plan_out->grid = (int)grid; plan_out->max_contrib = max_contrib; plan_out->partial_bytes = need; }
+    kern<<<(unsigned)grid, 256, bytes, st>>>(p);
     return cudaPeekAtLastError();
 }
 
 template <int K, int CB>
-cudaError_t launch_small_mt(int mt, const GemmSmallParams& p, dim3 grid, cudaStream_t st)
+cudaError_t launch_small_mt(int mt, GemmSmallParams& p, int sms, size_t room, float* base, cudaStream_t st, SmallPlan* pl)
 {
-    if (mt == 1) return launch_small<K, CB, 1>(p, grid, st);
-    if (mt == 2) return launch_small<K, CB, 2>(p, grid, st);
-    return launch_small<K, CB, 4>(p, grid, st);
+    if (mt == 1) return launch_small<K, CB, 1>(p, sms, room, base, st, pl);
+    if (mt == 2) return launch_small<K, CB, 2>(p, sms, room, base, st, pl);
+    return launch_small<K, CB, 4>(p, sms, room, base, st, pl);
 }
 
 template <int K>
-cudaError_t launch_small_cb(int cb, int mt, const GemmSmallParams& p, dim3 grid, cudaStream_t st)
+cudaError_t launch_small_cb(int cb, int mt, GemmSmallParams& p, int sms, size_t room, float* base, cudaStream_t st, SmallPlan* pl)
 {
-    if (cb == 0) return launch_small_mt<K, 0>(mt, p, grid, st);
-    if (cb == 1) return launch_small_mt<K, 1>(mt, p, grid, st);
-    return launch_small_mt<K, 2>(mt, p, grid, st);
+    if (cb == 0) return launch_small_mt<K, 0>(mt, p, sms, room, base, st, pl);
+    if (cb == 1) return launch_small_mt<K, 1>(mt, p, sms, room, base, st, pl);
+    return launch_small_mt<K, 2>(mt, p, sms, room, base, st, pl);
 }
 
-cudaError_t launch_small_k(int K, int cb, int mt, const GemmSmallParams& p, dim3 grid, cudaStream_t st)
+cudaError_t launch_small_k(int K, int cb, int mt, GemmSmallParams& p, int sms, size_t room, float* base, cudaStream_t st,
+                           SmallPlan* pl)
 {
     switch (K) {
-        case 1: return launch_small_cb<1>(cb, mt, p, grid, st);
-        case 2: return launch_small_cb<2>(cb, mt, p, grid, st);
-        case 3: return launch_small_cb<3>(cb, mt, p, grid, st);
-        case 4: return launch_small_cb<4>(cb, mt, p, grid, st);
-        case 5: return launch_small_cb<5>(cb, mt, p, grid, st);
-        case 6: return launch_small_cb<6>(cb, mt, p, grid, st);
-        case 7: return launch_small_cb<7>(cb, mt, p, grid, st);
-        default: return launch_small_cb<8>(cb, mt, p, grid, st);
+        case 1: return launch_small_cb<1>(cb, mt, p, sms, room, base, st, pl);
+        case 2: return launch_small_cb<2>(cb, mt, p, sms, room, base, st, pl);
+        case 3: return launch_small_cb<3>(cb, mt, p, sms, room, base, st, pl);
+        case 4: return launch_small_cb<4>(cb, mt, p, sms, room, base, st, pl);
+        case 5: return launch_small_cb<5>(cb, mt, p, sms, room, base, st, pl);
+        case 6: return launch_small_cb<6>(cb, mt, p, sms, room, base, st, pl);
+        case 7: return launch_small_cb<7>(cb, mt, p, sms, room, base, st, pl);
+        default: return launch_small_cb<8>(cb, mt, p, sms, room, base, st, pl);
     }
 }
-
 
 // Input transform for the tensor-core path: plain fp16 A_had[row][k] (one CTA per row, as above without duplication).
 __global__ void __launch_bounds__(256) gemm_prologue_plain_kernel(const half* __restrict__ A, const half* __restrict__ suh,
@@ -242,12 +269,11 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
     const int NB = n / 128, NST = k / 128;
     EXL3_REQUIRE(NB <= ctx->n_counters, "exl3_gemm: n too large for the context's counters");
 
-    // Large M with n % 256 == 0: tcgen05 kernel over 256-row blocks; a remainder of up to 64 rows (the decode rows of a
-    // mixed step) goes through the small-M kernel instead of a mostly empty 256-row block.
+    // Large M with n % 256 == 0: tcgen05 kernel over 256-row blocks (the last block may be partial: its rows past m are
+    // zero-filled by TMA, and a block with at most 128 valid rows runs a single accumulator).
     int tc_rows = 0;
     if (m > 128 && n % TC_BN == 0 && ctx->use_tc) {
-        const int rem = m % TC_BM;
-        tc_rows = (rem != 0 && rem <= 64) ? m - rem : m;
+        tc_rows = m;
         int rc = gemm_tc_rows(ctx, st, (const half*)A, trellis, C, (const half*)suh, (const half*)svh, tc_rows, k, n, K, c_fp32, cb);
         if (rc != EXL3_OK) return rc;
     }
@@ -258,29 +284,17 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
         uint32_t* a_dup = (uint32_t*)exl3_ws_take(ctx, &off, (size_t)rows * k * 4);
         float* rowsum = (float*)exl3_ws_take(ctx, &off, (size_t)rows * 4);
         if (!a_dup || !rowsum) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the activations");
-        // split K so that the grid covers the SMs a few times over; partial sums must fit the remaining scratch
-        const int ctas_per_sm = mt == 1 ? 3 : (mt == 2 ? 2 : 1);
-        int splits = (ctx->num_sms * ctas_per_sm * 2 + NB - 1) / NB;
-        if (splits > NST / 2) splits = NST / 2;
-        if (splits < 1) splits = 1;
-        size_t part_off = off;
-        float* partial = nullptr;
-        while (splits > 1) {
-            part_off = off;
-            partial = (float*)exl3_ws_take(ctx, &part_off, (size_t)splits * rows * n * 4);
-            if (partial) break;
-            splits /= 2;
-        }
-        if (splits <= 1) { splits = 1; partial = nullptr; }
-
         gemm_prologue_kernel<<<rows, 256, 0, st>>>((const half*)A + (size_t)row0 * k, (const half*)suh, a_dup, rowsum, k);
         ctx->launches++;
+        // whatever scratch is left holds the partial sums of column blocks that several CTAs share
+        size_t part_off = (off + 255) & ~(size_t)255;
+        const size_t room = ctx->ws_bytes > part_off ? ctx->ws_bytes - part_off : 0;
         GemmSmallParams p;
-        p.a_dup = a_dup; p.rowsum = rowsum; p.trellis = (const uint32_t*)trellis; p.partial = partial;
+        p.a_dup = a_dup; p.rowsum = rowsum; p.trellis = (const uint32_t*)trellis; p.partial = nullptr;
         p.counters = ctx->counters; p.svh = (const half*)svh; p.status = ctx->status;
         p.C = c_fp32 ? (void*)((float*)C + (size_t)row0 * n) : (void*)((half*)C + (size_t)row0 * n);
-        p.m = rows; p.k = k; p.n = n; p.splits = splits; p.c_fp32 = c_fp32;
-        cudaError_t e = launch_small_k(K, cb, mt, p, dim3(NB, splits), st);
+        p.m = rows; p.k = k; p.n = n; p.max_contrib = 1; p.c_fp32 = c_fp32;
+        cudaError_t e = launch_small_k(K, cb, mt, p, ctx->num_sms, room, (float*)(ctx->ws + part_off), st, nullptr);
         ctx->launches++;
         if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
     }
@@ -308,7 +322,7 @@ constexpr size_t NA_OFF_STATUS = NA_OFF_CNT + (NA_MAX_N / 128) * 4;    // int st
 constexpr size_t NA_OFF_ROWSUM = NA_OFF_STATUS + 256;                  // float[NA_MAX_M]
 constexpr size_t NA_OFF_ADUP   = NA_OFF_ROWSUM + 256;                  // uint32[NA_MAX_M][k]
 constexpr size_t NA_ADUP_BYTES = (size_t)NA_MAX_M * NA_MAX_K * 4;
-constexpr size_t NA_OFF_PART   = NA_OFF_ADUP + NA_ADUP_BYTES;          // float[splits][m][n]
+constexpr size_t NA_OFF_PART   = NA_OFF_ADUP + NA_ADUP_BYTES;          // float[n/128][owners][m][128] partial sums
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NA_BYTES];
 
@@ -363,24 +377,16 @@ extern "C" int exl3_gemm_noalloc(exl3_stream stream, const void* A, const void* 
 
     cudaStream_t st = (cudaStream_t)stream;
     const int cb = mcg ? 1 : (mul1 ? 2 : 0);
-    const int NB = n / 128, NST = k / 128;
-    int splits = (d->num_sms * 3 * 2 + NB - 1) / NB;
-    if (splits > NST / 2) splits = NST / 2;
-    const size_t part_room = NA_BYTES - NA_OFF_PART;
-    while (splits > 1 && (size_t)splits * m * n * 4 > part_room) splits /= 2;
-    if (splits < 1) splits = 1;
-
     // the array keeps whatever the previous call left: counters and status must start at zero
     if (cudaMemsetAsync(d->base + NA_OFF_CNT, 0, NA_OFF_ROWSUM - NA_OFF_CNT, st) != cudaSuccess) { cudaGetLastError(); return EXL3_ERR_CUDA; }
     uint32_t* a_dup = (uint32_t*)(d->base + NA_OFF_ADUP);
     float* rowsum = (float*)(d->base + NA_OFF_ROWSUM);
     gemm_prologue_kernel<<<m, 256, 0, st>>>((const half*)A, (const half*)suh, a_dup, rowsum, k);
     GemmSmallParams p;
-    p.a_dup = a_dup; p.rowsum = rowsum; p.trellis = (const uint32_t*)trellis;
-    p.partial = splits > 1 ? (float*)(d->base + NA_OFF_PART) : nullptr;
+    p.a_dup = a_dup; p.rowsum = rowsum; p.trellis = (const uint32_t*)trellis; p.partial = nullptr;
     p.counters = (int*)(d->base + NA_OFF_CNT); p.svh = (const half*)svh; p.status = (int*)(d->base + NA_OFF_STATUS);
-    p.C = C; p.m = m; p.k = k; p.n = n; p.splits = splits; p.c_fp32 = c_fp32;
-    cudaError_t e = launch_small_k(K, cb, 1, p, dim3(NB, splits), st);
+    p.C = C; p.m = m; p.k = k; p.n = n; p.max_contrib = 1; p.c_fp32 = c_fp32;
+    cudaError_t e = launch_small_k(K, cb, 1, p, d->num_sms, NA_BYTES - NA_OFF_PART, (float*)(d->base + NA_OFF_PART), st, nullptr);
     if (e != cudaSuccess) {
         fprintf(stderr, "exl3_gemm_noalloc: launch failed: %s\n", cudaGetErrorString(e));
         cudaGetLastError();

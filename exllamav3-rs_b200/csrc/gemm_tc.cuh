@@ -124,6 +124,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     const int n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM;
     const int tiles_n = p.n >> 4;
     const int ksteps = p.k / TC_BK;
+    const bool two_tiles = p.m - m0 > 128;               // a block with at most 128 valid rows skips its second M tile
 
     if (tid == 0) {
         s_failed = 0;
@@ -175,7 +176,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                 for (int kk = 0; kk < TC_BK / 16; ++kk) {
                     const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
                     tc_mma_f16(tmem_base, adesc0 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);          // +32 bytes per K=16
-                    tc_mma_f16(tmem_base + TC_BN, adesc1 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);
+                    if (two_tiles) tc_mma_f16(tmem_base + TC_BN, adesc1 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);
                 }
                 tc_commit(&a_empty[sa]);      // arrive when the MMAs above have finished reading the stage
                 tc_commit(&b_empty[sb]);
@@ -227,7 +228,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             const int q = warp & 3, sel = (warp - 2) >> 2;            // TMEM lane quadrant, 128-column half of the tile
             const half* svh_s = reinterpret_cast<const half*>(smem + SM::OFF_SVH) + sel * 128;
             #pragma unroll 1
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < (two_tiles ? 2 : 1); ++mt) {
                 const int row = m0 + mt * 128 + q * 32 + lane;
                 float v[128];
                 #pragma unroll

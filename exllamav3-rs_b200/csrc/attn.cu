@@ -1,5 +1,6 @@
 // exl3_bighead_attn_paged / exl3_bighead_attn_paged_q: planning, launch and split-KV combine.
 #include "attn_paged.cuh"
+#include "attn_tc.cuh"
 
 namespace {
 
@@ -137,13 +138,63 @@ cudaError_t launch_attn(const AttnParams& p, dim3 grid, cudaStream_t st)
     return cudaPeekAtLastError();
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn attn_encode_tiled()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+// tcgen05 attention: one CTA per work item and kv head; K/V tiles come through 4-D tensor maps of the pools
+cudaError_t launch_attn_tc(exl3_ctx* ctx, const AttnParams& p, int max_items, cudaStream_t st)
+{
+    EncodeTiledFn enc = attn_encode_tiled();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap maps[2];
+    const void* pools[2] = {p.kc, p.vc};
+    for (int i = 0; i < 2; ++i) {
+        cuuint64_t dims[4] = {(cuuint64_t)ATC_D, (cuuint64_t)p.nkv, 256, (cuuint64_t)p.pages};
+        cuuint64_t strides[3] = {(cuuint64_t)ATC_D * 2, (cuuint64_t)p.nkv * ATC_D * 2, (cuuint64_t)256 * p.nkv * ATC_D * 2};
+        cuuint32_t box[4] = {64, 1, (cuuint32_t)ATC_TN, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        if (enc(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(pools[i]), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    (void)ctx;
+    attn_tc_kernel<<<dim3(max_items, p.nkv), ATC_THREADS, ATC_SMEM, st>>>(maps[0], maps[1], p);
+    return cudaPeekAtLastError();
+}
+
 // One pass = plan + attention + combine over the sequences whose packed row count lies in (rows_lo, rows_hi].
 int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int max_rows, int rows_lo, int rows_hi,
               bool decode_shape, bool quant)
 {
     const int D = 128;
     const int G = p.nq / p.nkv;
-    const int rows_per_cta = decode_shape ? 16 : 64;
+    // long class on fp16 pools: tcgen05 kernel (128-row blocks) unless the context was switched to the mma.sync kernels
+    const bool use_tc = !decode_shape && !quant && ctx->mma_attn != 0;
+    const int rows_per_cta = decode_shape ? 16 : (use_tc ? ATC_ROWS : 64);
     const int rb_max = (max_rows + rows_per_cta - 1) / rows_per_cta;
     const int grid_x = (ctx->num_sms * 3 + p.nkv - 1) / p.nkv;    // about 3 resident CTAs per SM over all kv heads
     const int target_items = grid_x * 2;
@@ -158,13 +209,15 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     if (!plan || !items || !seq_base || !seq_splits || !partial)
         return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "attention: context scratch too small for the split-KV partials");
     p.plan = plan; p.items = items; p.seq_base = seq_base; p.seq_splits = seq_splits; p.partial = partial;
+    p.status = ctx->status;
 
     attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, rows_lo, rows_hi,
                                           target_items, max_items, plan, items, seq_base, seq_splits);
     ctx->launches++;
     dim3 grid(grid_x, p.nkv);
     cudaError_t e;
-    if (quant) e = decode_shape ? launch_attn<128, 1, 4, true>(p, grid, st) : launch_attn<128, 4, 1, true>(p, grid, st);
+    if (use_tc) e = launch_attn_tc(ctx, p, max_items, st);
+    else if (quant) e = decode_shape ? launch_attn<128, 1, 4, true>(p, grid, st) : launch_attn<128, 4, 1, true>(p, grid, st);
     else       e = decode_shape ? launch_attn<128, 1, 4, false>(p, grid, st) : launch_attn<128, 4, 1, false>(p, grid, st);
     ctx->launches++;
     if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }

@@ -38,6 +38,7 @@ struct AttnParams {
     const int* seq_base;           // [bsz] first item of sequence b
     const int* seq_splits;         // [bsz]
     float* partial;                // [n_items][nkv][ROWS][D+2]
+    int* status;                   // context status word (bounded waits)
     int bsz, q_len, kv_append, nq, nkv, pps, pages, causal, k_bits, v_bits;
     float scale_log2;              // sm_scale * log2(e)
 };

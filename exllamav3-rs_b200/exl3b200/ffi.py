@@ -102,6 +102,10 @@ class Ctx:
     def poll_status(self, stream=None):
         self.check(lib().exl3_ctx_poll_status(self._h, self.stream(stream)), "device status")
 
+    def set_mma_attn(self, on):
+        """src/ffi.rs set_mma_attn: True = tcgen05 attention for long row blocks (default), False = mma.sync kernels."""
+        lib().exl3_set_mma_attn(self._h, int(bool(on)))
+
     def launch_count(self):
         return int(lib().exl3_ctx_launch_count(self._h))
 

@@ -216,7 +216,8 @@ EXL3_API int  exl3_sync_side_stream(exl3_ctx* ctx);
 EXL3_API void exl3_empty_cache(void);
 /* exl3_cuda_free_mib (src/ffi.rs:202, csrc/exl3_shim.cpp:308-312): free device memory in MiB, -1 on error */
 EXL3_API int64_t exl3_cuda_free_mib(void);
-/* exl3_shim_set_mma_attn (src/ffi.rs:201): 1 = tensor-core attention kernels (default), 0 = scalar kernels for A/B */
+/* exl3_shim_set_mma_attn (src/ffi.rs:201) selects the kernel family for sequences with more than 16 packed rows, for A/B
+ * runs: 1 = tcgen05/TMEM attention (default), 0 = the mma.sync kernels. */
 EXL3_API void exl3_set_mma_attn(exl3_ctx* ctx, int on);
 
 /* ------------------------------------------------------------------------------- step-level entry points

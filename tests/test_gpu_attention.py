@@ -104,6 +104,19 @@ def test_attention_shapes(ctx, ref, q_len, nq, nkv):
     assert e_or <= max(1.0, 1.1 * e_rr) and e_ref <= (1.0 if q_len == 1 else 1.25), (e_or, e_ref, e_rr)
 
 
+def test_attention_kernel_families_agree(ctx):
+    """set_mma_attn switches long row blocks between the tcgen05 kernel and the mma.sync kernel: same results"""
+    c = _make_case(4242, [0, 77, 1500, 6000], 96, 40, 8)
+    got_tc, _, _ = _run_fp16(ctx, c)
+    ctx.set_mma_attn(False)
+    try:
+        got_mma, _, _ = _run_fp16(ctx, c)
+    finally:
+        ctx.set_mma_attn(True)
+    assert np.isfinite(got_tc).all() and np.isfinite(got_mma).all()
+    assert _close(got_tc, got_mma, TOL_FP16, 2) <= 1.25
+
+
 def test_attention_long_context_split_kv(ctx, ref):
     """attention-alone benchmark shape at reduced batch: contexts log-uniform in [128, 32768], 40 q / 8 kv heads"""
     r = H.rng(77)

@@ -133,11 +133,14 @@ cudaError_t launch_small_k(int K, int cb, int mt, GemmSmallParams& p, int sms, s
 }
 
 // Input transform for the tensor-core path: plain fp16 A_had[row][k] (one CTA per row, as above without duplication).
-__global__ void __launch_bounds__(256) gemm_prologue_plain_kernel(const half* __restrict__ A, const half* __restrict__ suh,
-                                                                  half* __restrict__ a_had, int k)
+struct ProloguePlainArgs { const half* suh[TC_MAX_SEG]; half* a_had[TC_MAX_SEG]; };
+
+__global__ void __launch_bounds__(256) gemm_prologue_plain_kernel(const half* __restrict__ A, const ProloguePlainArgs args, int k)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t row = blockIdx.x;
+    const half* __restrict__ suh = args.suh[blockIdx.y];
+    half* __restrict__ a_had = args.a_had[blockIdx.y];
     for (int blk = warp; blk < k / 128; blk += 8) {
         uint2 raw = reinterpret_cast<const uint2*>(A + row * k + blk * 128)[lane];
         half2 a = *reinterpret_cast<half2*>(&raw.x), b = *reinterpret_cast<half2*>(&raw.y);
@@ -183,7 +186,7 @@ EncodeTiledFn get_encode_tiled()
 }
 
 template <int K, int CB>
-cudaError_t launch_tc(const CUtensorMap& amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
+cudaError_t launch_tc(const CUtensorMap* amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
 {
     constexpr int bytes = TcSmem<K>::BYTES;
     static bool configured[64] = {};
@@ -195,19 +198,19 @@ cudaError_t launch_tc(const CUtensorMap& amap, const GemmTcParams& p, dim3 grid,
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kern<<<grid, TC_THREADS, bytes, st>>>(amap, p);
+    kern<<<grid, TC_THREADS, bytes, st>>>(amap[0], amap[1], amap[2], p);
     return cudaPeekAtLastError();
 }
 
 template <int K>
-cudaError_t launch_tc_cb(int cb, const CUtensorMap& amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
+cudaError_t launch_tc_cb(int cb, const CUtensorMap* amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
 {
     if (cb == 0) return launch_tc<K, 0>(amap, p, grid, st);
     if (cb == 1) return launch_tc<K, 1>(amap, p, grid, st);
     return launch_tc<K, 2>(amap, p, grid, st);
 }
 
-cudaError_t launch_tc_k(int K, int cb, const CUtensorMap& amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
+cudaError_t launch_tc_k(int K, int cb, const CUtensorMap* amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
 {
     switch (K) {
         case 1: return launch_tc_cb<1>(cb, amap, p, grid, st);
@@ -221,29 +224,44 @@ cudaError_t launch_tc_k(int K, int cb, const CUtensorMap& amap, const GemmTcPara
     }
 }
 
-// Tensor-core path for rows [0, m): one launch of the input transform and one of the tcgen05 kernel.
-int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, const void* trellis, void* C, const half* suh,
-                 const half* svh, int m, int k, int n, int K, int c_fp32, int cb)
+// Tensor-core path for rows [0, m) and `nseg` weight tensors that share the activations, k, bits and codebook:
+// one launch of the input transforms (each tensor has its own suh) and one of the tcgen05 kernel.
+int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const void* const* trellis, void* const* C,
+                 const half* const* suh, const half* const* svh, const int* n, int m, int k, int K, int c_fp32, int cb)
 {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled is not available from this driver");
     size_t off = 0;
-    half* a_had = (half*)exl3_ws_take(ctx, &off, (size_t)m * k * 2);
-    if (!a_had) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the activations");
-    gemm_prologue_plain_kernel<<<m, 256, 0, st>>>(A, suh, a_had, k);
-    ctx->launches++;
-    CUtensorMap amap;
-    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
-    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a_had, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled failed");
+    ProloguePlainArgs pa;
+    CUtensorMap amap[TC_MAX_SEG];
     GemmTcParams p;
-    p.trellis = (const uint32_t*)trellis; p.C = C; p.svh = svh; p.status = ctx->status;
-    p.m = m; p.k = k; p.n = n; p.c_fp32 = c_fp32;
-    cudaError_t e = launch_tc_k(K, cb, amap, p, dim3(n / TC_BN, (m + TC_BM - 1) / TC_BM), st);
+    memset(&p, 0, sizeof(p));
+    int blocks = 0;
+    for (int i = 0; i < TC_MAX_SEG; ++i) {
+        const int j = i < nseg ? i : nseg - 1;              // unused slots repeat the last tensor (never selected)
+        if (i < nseg) {
+            pa.a_had[i] = (half*)exl3_ws_take(ctx, &off, (size_t)m * k * 2);
+            if (!pa.a_had[i]) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the activations");
+            pa.suh[i] = suh[i];
+            blocks += n[i] / TC_BN;
+            cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
+            cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+            cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
+            cuuint32_t estr[2] = {1, 1};
+            CUresult r = enc(&amap[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pa.a_had[i], dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled failed");
+        } else {
+            pa.a_had[i] = pa.a_had[j]; pa.suh[i] = pa.suh[j]; amap[i] = amap[j];
+        }
+        p.trellis[i] = (const uint32_t*)trellis[j]; p.C[i] = C[j]; p.svh[i] = svh[j]; p.n[i] = n[j];
+        p.blk_end[i] = i < nseg ? blocks : 0x7fffffff;
+    }
+    gemm_prologue_plain_kernel<<<dim3(m, nseg), 256, 0, st>>>(A, pa, k);
+    ctx->launches++;
+    p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
+    cudaError_t e = launch_tc_k(K, cb, amap, p, dim3(blocks, (m + TC_BM - 1) / TC_BM), st);
     ctx->launches++;
     if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
     return EXL3_OK;
@@ -274,7 +292,8 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
     int tc_rows = 0;
     if (m > 128 && n % TC_BN == 0 && ctx->use_tc) {
         tc_rows = m;
-        int rc = gemm_tc_rows(ctx, st, (const half*)A, trellis, C, (const half*)suh, (const half*)svh, tc_rows, k, n, K, c_fp32, cb);
+        const half* suh1 = (const half*)suh; const half* svh1 = (const half*)svh;
+        int rc = gemm_tc_rows(ctx, st, (const half*)A, 1, &trellis, &C, &suh1, &svh1, &n, tc_rows, k, K, c_fp32, cb);
         if (rc != EXL3_OK) return rc;
     }
     for (int row0 = tc_rows; row0 < m; row0 += 64) {
@@ -297,6 +316,33 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
         cudaError_t e = launch_small_k(K, cb, mt, p, ctx->num_sms, room, (float*)(ctx->ws + part_off), st, nullptr);
         ctx->launches++;
         if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
+    }
+    return EXL3_OK;
+}
+
+// exl3_gemm_fanout: the same activations through several EXL3 tensors (q/k/v, gate/up).  With many rows and tensors that
+// agree in k, bits and codebook this is one tensor-core launch over all their column blocks; otherwise one exl3_gemm
+// per tensor.
+extern "C" int exl3_gemm_fanout(exl3_ctx* ctx, exl3_stream stream, const void* A, int count, const exl3_linear* const* w,
+                                void* const* C, int m, int c_fp32)
+{
+    EXL3_REQUIRE(ctx && A && w && C && count >= 1 && count <= TC_MAX_SEG, "exl3_gemm_fanout: 1..3 tensors required");
+    bool same = true;
+    for (int i = 0; i < count; ++i) {
+        EXL3_REQUIRE(w[i] && C[i] && w[i]->trellis, "exl3_gemm_fanout: null tensor");
+        same = same && w[i]->k == w[0]->k && w[i]->K == w[0]->K && w[i]->cb == w[0]->cb && w[i]->n % TC_BN == 0 &&
+               w[i]->k % 128 == 0 && w[i]->K >= 1 && w[i]->K <= 8 && aligned16(w[i]->trellis) && aligned16(C[i]) &&
+               aligned16(w[i]->suh) && aligned16(w[i]->svh) && (w[i]->suh != nullptr) == (w[0]->suh != nullptr);
+    }
+    if (count > 1 && same && m > 128 && ctx->use_tc && aligned16(A)) {
+        const void* tr[TC_MAX_SEG]; const half* suh[TC_MAX_SEG]; const half* svh[TC_MAX_SEG]; int n[TC_MAX_SEG];
+        for (int i = 0; i < count; ++i) { tr[i] = w[i]->trellis; suh[i] = (const half*)w[i]->suh; svh[i] = (const half*)w[i]->svh; n[i] = w[i]->n; }
+        return gemm_tc_rows(ctx, (cudaStream_t)stream, (const half*)A, count, tr, C, suh, svh, n, m, w[0]->k, w[0]->K, c_fp32, w[0]->cb);
+    }
+    for (int i = 0; i < count; ++i) {
+        int rc = exl3_gemm(ctx, stream, A, w[i]->trellis, C[i], w[i]->suh, nullptr, w[i]->svh, m, w[i]->k, w[i]->n, w[i]->K, c_fp32,
+                           w[i]->cb == 1, w[i]->cb == 2);
+        if (rc != EXL3_OK) return rc;
     }
     return EXL3_OK;
 }

@@ -146,9 +146,11 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
         const exl3_layer& L = m->layers[l];
         if (pending) STEP_TRY(exl3_rms_norm_res_in(ctx, stream, pending, 0, L.attn_norm, s.a_in, 0, s.resid, m->norm_eps, 0.f, 1.f, rows, hidden));
         else         STEP_TRY(exl3_rms_norm(ctx, stream, s.resid, 1, L.attn_norm, s.a_in, 0, m->norm_eps, 0.f, 1.f, rows, hidden));
-        STEP_TRY(linear(ctx, stream, L.q_proj, s.a_in, s.q, rows, 0));
-        STEP_TRY(linear(ctx, stream, L.k_proj, s.a_in, s.k, rows, 0));
-        STEP_TRY(linear(ctx, stream, L.v_proj, s.a_in, s.v, rows, 0));
+        {
+            const exl3_linear* w[3] = {&L.q_proj, &L.k_proj, &L.v_proj};
+            void* out[3] = {s.q, s.k, s.v};
+            STEP_TRY(exl3_gemm_fanout(ctx, stream, s.a_in, 3, w, out, rows, 0));
+        }
         STEP_TRY(exl3_rope(ctx, stream, s.q, s.k, m->inv_freq, m->n_freq, 0, nullptr, s.row_pos, L.q_norm, L.k_norm,
                            m->norm_eps, 0.f, m->rope_mode, m->attn_factor, 1, rows, m->nq, m->nkv, m->hd));
         if (m->kv_bits == 0)
@@ -162,8 +164,11 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
                                                0.f, 0.f));
         STEP_TRY(linear(ctx, stream, L.o_proj, s.attn_o, s.proj, rows, 0));
         STEP_TRY(exl3_rms_norm_res_in(ctx, stream, s.proj, 0, L.mlp_norm, s.a_in, 0, s.resid, m->norm_eps, 0.f, 1.f, rows, hidden));
-        STEP_TRY(linear(ctx, stream, L.gate_proj, s.a_in, s.gate, rows, 0));
-        STEP_TRY(linear(ctx, stream, L.up_proj, s.a_in, s.up, rows, 0));
+        {
+            const exl3_linear* w[2] = {&L.gate_proj, &L.up_proj};
+            void* out[2] = {s.gate, s.up};
+            STEP_TRY(exl3_gemm_fanout(ctx, stream, s.a_in, 2, w, out, rows, 0));
+        }
         STEP_TRY(exl3_silu_mul(ctx, stream, s.gate, s.up, s.act, 0.f, (int64_t)rows * m->inter));
         STEP_TRY(linear(ctx, stream, L.down_proj, s.act, s.proj, rows, 0));
         pending = s.proj;

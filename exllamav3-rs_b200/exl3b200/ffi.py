@@ -18,6 +18,12 @@ class Exl3Error(RuntimeError):
     pass
 
 
+class Linear(C.Structure):
+    """exl3_linear (include/exl3_abi.h): one EXL3 tensor of a step-level call."""
+    _fields_ = [("trellis", C.c_void_p), ("suh", C.c_void_p), ("svh", C.c_void_p),
+                ("k", C.c_int), ("n", C.c_int), ("K", C.c_int), ("cb", C.c_int)]
+
+
 _lib = None
 
 
@@ -123,6 +129,29 @@ class Ctx:
         rc = lib().exl3_gemm(self._h, self.stream(stream), _ptr(a), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had),
                              _ptr(svh), m, k, n, K, int(c.dtype == torch.float32), int(mcg), int(mul1))
         self.check(rc, "exl3_gemm")
+
+    def gemm_fanout(self, a, weights, outs, stream=None):
+        """The same activations through up to three EXL3 tensors (the reference's back-to-back exl3_gemm calls for
+        q/k/v, src/modules.rs:646-648, and gate/up, src/modules.rs:933-934).  `weights` is a list of
+        (trellis, suh, svh, cb) tuples, `outs` the matching output tensors."""
+        _chk(a, torch.float16, "a")
+        k = a.shape[-1]
+        m = a.numel() // k
+        structs, keep = [], []
+        for (trellis, suh, svh, cb), c in zip(weights, outs):
+            _chk(trellis, torch.int16, "trellis"); _chk(suh, torch.float16, "suh"); _chk(svh, torch.float16, "svh")
+            _chk(c, (torch.float16, torch.float32), "c")
+            n = trellis.shape[1] * 16
+            if trellis.shape[0] * 16 != k or c.shape[-1] != n or c.numel() // n != m or c.dtype != outs[0].dtype:
+                raise Exl3Error("gemm_fanout: shape mismatch")
+            structs.append(Linear(_ptr(trellis), _ptr(suh), _ptr(svh), k, n, trellis.shape[2] // 16, int(cb)))
+        cnt = len(structs)
+        if cnt != len(outs) or not 1 <= cnt <= 3:
+            raise Exl3Error("gemm_fanout: 1..3 tensors and as many outputs")
+        wp = (C.POINTER(Linear) * cnt)(*[C.pointer(x) for x in structs])
+        cp = (C.c_void_p * cnt)(*[_ptr(c) for c in outs])
+        rc = lib().exl3_gemm_fanout(self._h, self.stream(stream), _ptr(a), cnt, wp, cp, m, int(outs[0].dtype == torch.float32))
+        self.check(rc, "exl3_gemm_fanout")
 
     def reconstruct(self, unpacked, packed, K, mcg=False, mul1=False, stream=None):
         """src/ffi.rs:611-613."""

@@ -6,12 +6,7 @@ import ctypes as C
 import numpy as np
 import torch
 
-from .ffi import Exl3Error, lib
-
-
-class Linear(C.Structure):
-    _fields_ = [("trellis", C.c_void_p), ("suh", C.c_void_p), ("svh", C.c_void_p),
-                ("k", C.c_int), ("n", C.c_int), ("K", C.c_int), ("cb", C.c_int)]
+from .ffi import Exl3Error, Linear, lib
 
 
 class Layer(C.Structure):

@@ -271,6 +271,12 @@ typedef struct {
     int bsz, rows, max_q_len, pages_per_seq, advance;
 } exl3_batch;
 
+/* The same activations A [m,k] through `count` (1..3) EXL3 tensors, C[i] [m, w[i]->n]: what the reference issues as
+ * separate exl3_shim_gemm calls for q/k/v (src/modules.rs:646-648) and gate/up (src/modules.rs:933-934).  Results are
+ * those of `count` exl3_gemm calls; tensors that agree in k, bits and codebook share one tensor-core launch. */
+EXL3_API int exl3_gemm_fanout(exl3_ctx* ctx, exl3_stream stream, const void* A, int count, const exl3_linear* const* w,
+                              void* const* C, int m, int c_fp32);
+
 /* bytes of device scratch exl3_step_forward needs for up to `max_rows` packed rows and `max_bsz` sequences */
 EXL3_API size_t exl3_step_scratch_bytes(const exl3_model* model, int max_rows, int max_bsz);
 

@@ -285,3 +285,30 @@ def test_gemm_tc_row_counts(ctx, ctx_small_only, ref, m):
 def test_gemm_tc_step_shape(ctx, ctx_small_only):
     """the benchmark step's row count on the 5120 x 17408 projection"""
     _tc_case(ctx, ctx_small_only, None, 1052, 5120, 17408, 4, 1, False, 1200)
+
+
+@pytest.mark.parametrize("m,ns,K,c_fp32", [(200, (512, 256, 256), 4, False), (1052, (1024, 256, 256), 4, False),
+                                            (300, (768, 768), 3, True), (40, (512, 256), 4, False),
+                                            (260, (512, 384), 4, False)])
+def test_gemm_fanout_equals_separate_calls(ctx, m, ns, K, c_fp32):
+    """q/k/v and gate/up style fan-out: one grouped launch must give what separate exl3_gemm calls give, bit for bit
+    (each tensor keeps its own sign vectors); small m and a column count that is no multiple of 256 take the
+    per-tensor route"""
+    torch = _torch()
+    r = H.rng(1300 + m)
+    k = 1024
+    A = H.to_dev(r.standard_normal((m, k)).astype(np.float16))
+    ws, outs, wants = [], [], []
+    dt = torch.float32 if c_fp32 else torch.float16
+    for n in ns:
+        tr, suh, svh = H.to_dev(H.rand_trellis(r, k, n, K)), H.to_dev(H.rand_signs(r, k)), H.to_dev(H.rand_signs(r, n))
+        ws.append((tr, suh, svh, 1))
+        outs.append(torch.full((m, n), float("nan"), dtype=dt, device="cuda"))
+        want = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+        ctx.exl3_gemm(A, tr, want, suh, None, svh, mcg=True)
+        wants.append(want)
+    ctx.gemm_fanout(A, ws, outs)
+    ctx.poll_status()
+    for got, want in zip(outs, wants):
+        assert torch.isfinite(got).all()
+        assert torch.equal(got, want)

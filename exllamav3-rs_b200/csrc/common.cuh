@@ -25,6 +25,7 @@ struct exl3_ctx {
     uint64_t launches;
     int mma_attn;
     int use_tc;             // 1: tcgen05 GEMM for large M (default), 0: small-M kernel in passes (for A/B runs)
+    int use_pair;           // 1: the tcgen05 GEMM runs on CTA pairs (cta_group::2, default), 0: one CTA per tile
     char err[256];
 };
 

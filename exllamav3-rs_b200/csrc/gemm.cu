@@ -185,12 +185,12 @@ EncodeTiledFn get_encode_tiled()
     return fn;
 }
 
-template <int K, int CB>
-cudaError_t launch_tc(const CUtensorMap* amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
+template <int K, int CB, int CTAS>
+cudaError_t launch_tc(const CUtensorMap* amap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
-    constexpr int bytes = TcSmem<K>::BYTES;
+    constexpr int bytes = TcSmem<K, CTAS>::BYTES;
     static bool configured[64] = {};
-    auto kern = gemm_tc_kernel<K, CB>;
+    auto kern = gemm_tc_kernel<K, CB, CTAS>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -198,29 +198,44 @@ cudaError_t launch_tc(const CUtensorMap* amap, const GemmTcParams& p, dim3 grid,
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kern<<<grid, TC_THREADS, bytes, st>>>(amap[0], amap[1], amap[2], p);
-    return cudaPeekAtLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(slabs * CTAS, (p.m + TC_BM * CTAS - 1) / (TC_BM * CTAS));
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, amap[0], amap[1], amap[2], p);
+}
+
+template <int K, int CB>
+cudaError_t launch_tc_ctas(bool pair, const CUtensorMap* amap, const GemmTcParams& p, int slabs, cudaStream_t st)
+{
+    return pair ? launch_tc<K, CB, 2>(amap, p, slabs, st) : launch_tc<K, CB, 1>(amap, p, slabs, st);
 }
 
 template <int K>
-cudaError_t launch_tc_cb(int cb, const CUtensorMap* amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
+cudaError_t launch_tc_cb(int cb, bool pair, const CUtensorMap* amap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
-    if (cb == 0) return launch_tc<K, 0>(amap, p, grid, st);
-    if (cb == 1) return launch_tc<K, 1>(amap, p, grid, st);
-    return launch_tc<K, 2>(amap, p, grid, st);
+    if (cb == 0) return launch_tc_ctas<K, 0>(pair, amap, p, slabs, st);
+    if (cb == 1) return launch_tc_ctas<K, 1>(pair, amap, p, slabs, st);
+    return launch_tc_ctas<K, 2>(pair, amap, p, slabs, st);
 }
 
-cudaError_t launch_tc_k(int K, int cb, const CUtensorMap* amap, const GemmTcParams& p, dim3 grid, cudaStream_t st)
+cudaError_t launch_tc_k(int K, int cb, bool pair, const CUtensorMap* amap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
     switch (K) {
-        case 1: return launch_tc_cb<1>(cb, amap, p, grid, st);
-        case 2: return launch_tc_cb<2>(cb, amap, p, grid, st);
-        case 3: return launch_tc_cb<3>(cb, amap, p, grid, st);
-        case 4: return launch_tc_cb<4>(cb, amap, p, grid, st);
-        case 5: return launch_tc_cb<5>(cb, amap, p, grid, st);
-        case 6: return launch_tc_cb<6>(cb, amap, p, grid, st);
-        case 7: return launch_tc_cb<7>(cb, amap, p, grid, st);
-        default: return launch_tc_cb<8>(cb, amap, p, grid, st);
+        case 1: return launch_tc_cb<1>(cb, pair, amap, p, slabs, st);
+        case 2: return launch_tc_cb<2>(cb, pair, amap, p, slabs, st);
+        case 3: return launch_tc_cb<3>(cb, pair, amap, p, slabs, st);
+        case 4: return launch_tc_cb<4>(cb, pair, amap, p, slabs, st);
+        case 5: return launch_tc_cb<5>(cb, pair, amap, p, slabs, st);
+        case 6: return launch_tc_cb<6>(cb, pair, amap, p, slabs, st);
+        case 7: return launch_tc_cb<7>(cb, pair, amap, p, slabs, st);
+        default: return launch_tc_cb<8>(cb, pair, amap, p, slabs, st);
     }
 }
 
@@ -246,7 +261,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
             blocks += n[i] / TC_BN;
             cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
             cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-            cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
+            cuuint32_t box[2] = {(cuuint32_t)TC_BK, 128u};
             cuuint32_t estr[2] = {1, 1};
             CUresult r = enc(&amap[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pa.a_had[i], dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -261,7 +276,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
     gemm_prologue_plain_kernel<<<dim3(m, nseg), 256, 0, st>>>(A, pa, k);
     ctx->launches++;
     p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
-    cudaError_t e = launch_tc_k(K, cb, amap, p, dim3(blocks, (m + TC_BM - 1) / TC_BM), st);
+    cudaError_t e = launch_tc_k(K, cb, ctx->use_pair != 0, amap, p, blocks, st);
     ctx->launches++;
     if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
     return EXL3_OK;

@@ -1,11 +1,17 @@
 // EXL3 GEMM for large M (prefill chunks, verify batches, big packed steps): a real contraction on the 5th-generation
-// tensor cores.  Activations arrive by TMA (tiled, 128-byte swizzle), trellis codes by bulk copies; eight decoder
+// tensor cores.  Activations arrive by TMA (tiled, 128-byte swizzle), trellis codes by bulk copies; sixteen decoder
 // warps turn codes into fp16 weights and write them straight into the K-major swizzled B operand tile in shared memory;
 // one thread issues tcgen05.mma with both accumulators (2 x 128 rows x 256 columns, all 512 TMEM columns) resident in
-// tensor memory; the epilogue reads TMEM, applies the 128-wide output Hadamard in registers and stores fp16/fp32.
+// tensor memory; the epilogue reads TMEM, applies the 128-wide output Hadamard and stores fp16/fp32.
 //
-// CTA tile: 256 rows x 256 columns, K step 64.  Roles: warp 0 = producer (TMA + bulk copies), warp 1 = MMA issuer and
-// TMEM owner, warps 2..17 = decoders, then epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+// Two forms of the same kernel (template parameter CTAS):
+//   CTAS = 1  one CTA owns 256 rows x 256 columns and decodes all 256 columns of the weight slab.
+//   CTAS = 2  a cluster of two CTAs (one SM pair) owns 512 rows x 256 columns.  Each CTA decodes only its 128-column half
+//             of the slab and holds the accumulators of its own 2 x 128 rows; the leader CTA issues
+//             tcgen05.mma.cta_group::2 (M = 256 across the pair), which reads each CTA's half of B from that CTA's shared
+//             memory.  The decode work per multiply is halved, which is what bounds the CTAS = 1 form.
+// K step 64.  Roles: warp 0 = producer (TMA + bulk copies), warp 1 = MMA issuer (leader CTA only) and TMEM owner,
+// warps 2..17 = decoders, then epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
 // Every mbarrier wait is bounded; a wait that runs out makes the CTA skip to the tear-down (TMEM is always freed) and
 // sets the status word.
 #pragma once
@@ -16,23 +22,28 @@
 
 namespace exl3 {
 
-constexpr int TC_BM = 256, TC_BN = 256, TC_BK = 64;
-constexpr int TC_SA = 3, TC_SR = 3, TC_SB = 2;          // stages: activations, raw codes, decoded weights
-constexpr int TC_DECODERS = 16;                          // decoder warps (one 16-column tile strip each)
+constexpr int TC_BM = 256, TC_BN = 256, TC_BK = 64;     // rows per CTA, columns per slab, K step
+constexpr int TC_DECODERS = 16;                          // decoder warps
 constexpr int TC_THREADS = (2 + TC_DECODERS) * 32;       // 18 warps
 constexpr int TC_MAX_SEG = 3;                            // weight tensors that may share one launch
-constexpr int TC_A_STAGE = TC_BM * TC_BK * 2;            // 32 KB
-constexpr int TC_B_STAGE = TC_BN * TC_BK * 2;            // 32 KB
+constexpr int TC_A_TILE = 128 * TC_BK * 2;               // one 128-row activation tile of a stage: 16 KB
+constexpr int TC_A_STAGE = 2 * TC_A_TILE;                // 32 KB
 constexpr float TC_R128 = 0.088388347648f;
 
-template <int K> struct TcSmem {
-    static constexpr int RAW_STAGE = (TC_BK / 16) * (TC_BN / 16) * 32 * K;      // 4 tile rows x 16 tiles x 32K bytes
+template <int K, int CTAS> struct TcSmem {
+    static constexpr int SA = CTAS == 2 ? 4 : 3;         // stages: activations,
+    static constexpr int SB = CTAS == 2 ? 4 : 2;         //         decoded weights,
+    static constexpr int SR = 3;                         //         raw codes
+    static constexpr int NB = TC_BN / CTAS;              // columns this CTA decodes
+    static constexpr int B_STAGE = NB * TC_BK * 2;
+    static constexpr int RAW_ROW = (NB / 16) * 32 * K;   // one tile row of codes: NB/16 tiles x 32K bytes
+    static constexpr int RAW_STAGE = (TC_BK / 16) * RAW_ROW;
     static constexpr int OFF_A = 0;
-    static constexpr int OFF_B = OFF_A + TC_SA * TC_A_STAGE;
-    static constexpr int OFF_RAW = OFF_B + TC_SB * TC_B_STAGE;
-    static constexpr int OFF_SVH = OFF_RAW + TC_SR * RAW_STAGE;
+    static constexpr int OFF_B = OFF_A + SA * TC_A_STAGE;
+    static constexpr int OFF_RAW = OFF_B + SB * B_STAGE;
+    static constexpr int OFF_SVH = OFF_RAW + SR * RAW_STAGE;
     static constexpr int OFF_BAR = OFF_SVH + TC_BN * 2;
-    static constexpr int N_BARS = 2 * TC_SA + 2 * TC_SR + 2 * TC_SB + 1;
+    static constexpr int N_BARS = 2 * SA + 2 * SR + 2 * SB + 2;
     static constexpr int OFF_TMEM = OFF_BAR + N_BARS * 8;
     static constexpr int BYTES = OFF_TMEM + 16 + 1024;      // + slack to align the base to 1024 bytes
 };
@@ -44,7 +55,7 @@ struct GemmTcParams {
     void* C[TC_MAX_SEG];                   // [m][n] fp16 or fp32
     const half* svh[TC_MAX_SEG];           // [n] or NULL
     int n[TC_MAX_SEG];
-    int blk_end[TC_MAX_SEG];               // running count of 256-column blocks
+    int blk_end[TC_MAX_SEG];               // running count of 256-column slabs
     int* status;
     int m, k, c_fp32;
 };
@@ -68,6 +79,57 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// ---- the same operations for a CTA pair (cta_group::2)
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// all threads of both CTAs
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// tile lands in this CTA's shared memory, its bytes are counted on the leader CTA's barrier (rank bit of the address cleared)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar) & 0xFEFFFFFFu) : "memory");
+}
+// arrive on the barrier at the same offset in CTA `cta` of the cluster.  The data this signals lies in the arriving CTA's own
+// shared memory and was fenced into the async proxy by each writing lane; a cluster-scope release on top of that was
+// measured to cost a quarter of the kernel's time and is what no 2-CTA pipeline needs for SM-local shared memory.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta)
+{
+    asm volatile("{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\t"
+                 "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}" ::"r"(smem_u32(bar)), "r"(cta) : "memory");
+}
+// bounded wait that acquires at cluster scope (the arrivals or bytes may come from the other CTA)
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22))
+{
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// arrive on the barrier at this offset in both CTAs of the pair when the MMAs issued so far have completed
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32])
 {
     uint32_t* r = reinterpret_cast<uint32_t*>(v);
@@ -108,8 +170,9 @@ __device__ __forceinline__ uint64_t tc_smem_desc(const void* p)
     return d;
 }
 
-// instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = 256
+// instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 128 (one CTA) or 256 (a CTA pair)
 constexpr uint32_t TC_IDESC = (1u << 4) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+constexpr uint32_t TC_IDESC_PAIR = (1u << 4) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 
 
 // in-register unnormalised 32-point Walsh-Hadamard transform (Sylvester order)
@@ -125,49 +188,65 @@ __device__ __forceinline__ void fwht32(float (&v)[32])
     }
 }
 
-// grid (n / 256, ceil(m / 256)); the activations come through `amap` (A_had [m][k] fp16, box 64 x 256, 128B swizzle)
-template <int K, int CB>
+
+// CTAS = 1: grid (slabs, ceil(m / 256)).  CTAS = 2: grid (2 * slabs, ceil(m / 512)), cluster (2,1,1).
+// The activations come through `amap*` (A_had [m][k] fp16, box 64 x 128, 128-byte swizzle), one map per weight tensor.
+template <int K, int CB, int CTAS>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap amap0,
                                                                const __grid_constant__ CUtensorMap amap1,
                                                                const __grid_constant__ CUtensorMap amap2, const GemmTcParams p)
 {
-    using SM = TcSmem<K>;
+    using SM = TcSmem<K, CTAS>;
+    constexpr bool PAIR = CTAS == 2;
+    constexpr int NT = SM::NB / 16;                       // tile columns this CTA decodes (16 or 8)
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
-    uint64_t* a_full = bars;                 uint64_t* a_empty = a_full + TC_SA;
-    uint64_t* r_full = a_empty + TC_SA;      uint64_t* r_empty = r_full + TC_SR;
-    uint64_t* b_full = r_empty + TC_SR;      uint64_t* b_empty = b_full + TC_SB;
-    uint64_t* acc_full = b_empty + TC_SB;
+    uint64_t* a_full = bars;                  uint64_t* a_empty = a_full + SM::SA;
+    uint64_t* r_full = a_empty + SM::SA;      uint64_t* r_empty = r_full + SM::SR;
+    uint64_t* b_full = r_empty + SM::SR;      uint64_t* b_empty = b_full + SM::SB;
+    uint64_t* acc_full = b_empty + SM::SB;    uint64_t* drain = acc_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::OFF_TMEM);
     __shared__ int s_failed;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int seg = (blockIdx.x >= p.blk_end[0]) + (blockIdx.x >= p.blk_end[1]);
-    const int n0 = (blockIdx.x - (seg ? p.blk_end[seg - 1] : 0)) * TC_BN, m0 = blockIdx.y * TC_BM;
+    const int rank = PAIR ? (int)cluster_ctarank() : 0;                  // 0 = leader of the pair
+    const int slab = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int seg = (slab >= p.blk_end[0]) + (slab >= p.blk_end[1]);
+    const int n0 = (slab - (seg ? p.blk_end[seg - 1] : 0)) * TC_BN;     // first column of the slab
+    const int nd0 = n0 + rank * SM::NB;                                  // first column this CTA decodes
+    const int m0 = blockIdx.y * (TC_BM * CTAS);
+    const int row_t0 = m0 + rank * 128, row_t1 = row_t0 + 128 * CTAS;    // first rows of this CTA's two M tiles
     const CUtensorMap* amap = seg == 0 ? &amap0 : (seg == 1 ? &amap1 : &amap2);
     const uint32_t* trellis = p.trellis[seg];
     const half* svh = p.svh[seg];
     const int n = p.n[seg];
     const int tiles_n = n >> 4;
     const int ksteps = p.k / TC_BK;
-    const bool two_tiles = p.m - m0 > 128;               // a block with at most 128 valid rows skips its second M tile
+    const bool two_tiles = p.m - m0 > 128 * CTAS;          // otherwise the second M tile (of both CTAs) has no valid row
 
     if (tid == 0) {
         s_failed = 0;
-        for (int i = 0; i < TC_SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
-        for (int i = 0; i < TC_SR; ++i) { mbar_init(&r_full[i], 1); mbar_init(&r_empty[i], TC_DECODERS); }
-        for (int i = 0; i < TC_SB; ++i) { mbar_init(&b_full[i], TC_DECODERS); mbar_init(&b_empty[i], 1); }
+        for (int i = 0; i < SM::SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < SM::SR; ++i) { mbar_init(&r_full[i], 1); mbar_init(&r_empty[i], TC_DECODERS); }
+        for (int i = 0; i < SM::SB; ++i) { mbar_init(&b_full[i], TC_DECODERS * CTAS); mbar_init(&b_empty[i], 1); }
         mbar_init(acc_full, 1);
+        mbar_init(drain, 1);
         mbar_fence_init();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     if (svh) for (int i = tid; i < TC_BN; i += TC_THREADS) reinterpret_cast<half*>(smem + SM::OFF_SVH)[i] = svh[n0 + i];
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();               // the other CTA's barriers are initialised before anything arrives
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
@@ -175,77 +254,102 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     if (warp == 0) {
         // ===== producer: activations by TMA, trellis codes by bulk copies
         if (lane == 0) {
+            const uint32_t a_bytes = (two_tiles ? 2u : 1u) * TC_A_TILE * CTAS;     // what lands on the leader's barrier
             for (int ks = 0; ks < ksteps; ++ks) {
-                const int sa = ks % TC_SA, sr = ks % TC_SR;
-                if (ks >= TC_SA && !mbar_wait(&a_empty[sa], ((ks / TC_SA) - 1) & 1)) { failed = true; break; }
-                mbar_expect_tx(&a_full[sa], TC_A_STAGE);
-                tma_load_2d(smem + SM::OFF_A + sa * TC_A_STAGE, amap, ks * TC_BK, m0, &a_full[sa]);
-                if (ks >= TC_SR && !mbar_wait(&r_empty[sr], ((ks / TC_SR) - 1) & 1)) { failed = true; break; }
+                const int sa = ks % SM::SA, sr = ks % SM::SR;
+                if (ks >= SM::SA && !mbar_wait(&a_empty[sa], ((ks / SM::SA) - 1) & 1)) { failed = true; break; }
+                uint8_t* at = smem + SM::OFF_A + sa * TC_A_STAGE;
+                if constexpr (PAIR) {
+                    if (rank == 0) mbar_expect_tx(&a_full[sa], a_bytes);
+                    tma_load_2d_pair(at, amap, ks * TC_BK, row_t0, &a_full[sa]);
+                    if (two_tiles) tma_load_2d_pair(at + TC_A_TILE, amap, ks * TC_BK, row_t1, &a_full[sa]);
+                } else {
+                    mbar_expect_tx(&a_full[sa], a_bytes);
+                    tma_load_2d(at, amap, ks * TC_BK, row_t0, &a_full[sa]);
+                    if (two_tiles) tma_load_2d(at + TC_A_TILE, amap, ks * TC_BK, row_t1, &a_full[sa]);
+                }
+                if (ks >= SM::SR && !mbar_wait(&r_empty[sr], ((ks / SM::SR) - 1) & 1)) { failed = true; break; }
                 mbar_expect_tx(&r_full[sr], SM::RAW_STAGE);
                 #pragma unroll
                 for (int r = 0; r < TC_BK / 16; ++r)
-                    bulk_g2s(smem + SM::OFF_RAW + sr * SM::RAW_STAGE + r * (TC_BN / 16) * 32 * K,
-                             trellis + ((size_t)(ks * (TC_BK / 16) + r) * tiles_n + (n0 >> 4)) * 8 * K,
-                             (TC_BN / 16) * 32 * K, &r_full[sr]);
+                    bulk_g2s(smem + SM::OFF_RAW + sr * SM::RAW_STAGE + r * SM::RAW_ROW,
+                             trellis + ((size_t)(ks * (TC_BK / 16) + r) * tiles_n + (nd0 >> 4)) * 8 * K, SM::RAW_ROW, &r_full[sr]);
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer
-        if (lane == 0) {
+        // ===== MMA issuer (one thread of the leader CTA)
+        if (lane == 0 && rank == 0) {
             for (int ks = 0; ks < ksteps; ++ks) {
-                const int sa = ks % TC_SA, sb = ks % TC_SB;
-                if (!mbar_wait(&a_full[sa], (ks / TC_SA) & 1) || !mbar_wait(&b_full[sb], (ks / TC_SB) & 1)) { failed = true; break; }
+                const int sa = ks % SM::SA, sb = ks % SM::SB;
+                const bool ok = PAIR ? (mbar_wait_cluster(&a_full[sa], (ks / SM::SA) & 1) && mbar_wait_cluster(&b_full[sb], (ks / SM::SB) & 1))
+                                     : (mbar_wait(&a_full[sa], (ks / SM::SA) & 1) && mbar_wait(&b_full[sb], (ks / SM::SB) & 1));
+                if (!ok) { failed = true; break; }
                 tc_fence_after();
                 const uint64_t adesc0 = tc_smem_desc(smem + SM::OFF_A + sa * TC_A_STAGE);
-                const uint64_t adesc1 = tc_smem_desc(smem + SM::OFF_A + sa * TC_A_STAGE + 128 * 128);
-                const uint64_t bdesc = tc_smem_desc(smem + SM::OFF_B + sb * TC_B_STAGE);
+                const uint64_t adesc1 = tc_smem_desc(smem + SM::OFF_A + sa * TC_A_STAGE + TC_A_TILE);
+                const uint64_t bdesc = tc_smem_desc(smem + SM::OFF_B + sb * SM::B_STAGE);
                 #pragma unroll
                 for (int kk = 0; kk < TC_BK / 16; ++kk) {
                     const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
-                    tc_mma_f16(tmem_base, adesc0 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);          // +32 bytes per K=16
-                    if (two_tiles) tc_mma_f16(tmem_base + TC_BN, adesc1 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);
+                    if constexpr (PAIR) {
+                        tc_mma_f16_pair(tmem_base, adesc0 + 2 * kk, bdesc + 2 * kk, TC_IDESC_PAIR, acc);      // +32 bytes per K=16
+                        if (two_tiles) tc_mma_f16_pair(tmem_base + TC_BN, adesc1 + 2 * kk, bdesc + 2 * kk, TC_IDESC_PAIR, acc);
+                    } else {
+                        tc_mma_f16(tmem_base, adesc0 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);
+                        if (two_tiles) tc_mma_f16(tmem_base + TC_BN, adesc1 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);
+                    }
                 }
-                tc_commit(&a_empty[sa]);      // arrive when the MMAs above have finished reading the stage
-                tc_commit(&b_empty[sb]);
+                // arrive when the MMAs above have finished reading the stage (in both CTAs of a pair)
+                if constexpr (PAIR) { tc_commit_pair(&a_empty[sa]); tc_commit_pair(&b_empty[sb]); }
+                else { tc_commit(&a_empty[sa]); tc_commit(&b_empty[sb]); }
             }
-            if (!failed) tc_commit(acc_full);
+            if (!failed) {
+                if constexpr (PAIR) tc_commit_pair(acc_full); else tc_commit(acc_full);
+            } else {
+                // leave no MMA in flight behind: the tear-down lets the other CTA go, whose shared memory they read
+                if constexpr (PAIR) tc_commit_pair(drain); else tc_commit(drain);
+                mbar_wait(drain, 0);
+            }
         }
     } else {
         // ===== decoders: raw codes -> fp16 weights in the K-major swizzled B tile
-        const int nt = warp - 2;                                   // 0..15: owns tile column nt of every tile row
+        const int nt = (warp - 2) % NT;                            // tile column of this CTA's part of the slab
+        const int r0 = (warp - 2) / NT;                            // first tile row; the warp takes every (16 / NT)-th
         const int g = lane >> 2, t = lane & 3;
         for (int ks = 0; ks < ksteps; ++ks) {
-            const int sr = ks % TC_SR, sb = ks % TC_SB;
-            if (!mbar_wait_warp(&r_full[sr], (ks / TC_SR) & 1)) { failed = true; break; }
-            if (ks >= TC_SB && !mbar_wait_warp(&b_empty[sb], ((ks / TC_SB) - 1) & 1)) { failed = true; break; }
+            const int sr = ks % SM::SR, sb = ks % SM::SB;
+            if (!mbar_wait_warp(&r_full[sr], (ks / SM::SR) & 1)) { failed = true; break; }
+            if (ks >= SM::SB && !mbar_wait_warp(&b_empty[sb], ((ks / SM::SB) - 1) & 1)) { failed = true; break; }
             const uint32_t* raw = reinterpret_cast<const uint32_t*>(smem + SM::OFF_RAW + sr * SM::RAW_STAGE);
-            uint8_t* bt = smem + SM::OFF_B + sb * TC_B_STAGE;
+            uint8_t* bt = smem + SM::OFF_B + sb * SM::B_STAGE;
             #pragma unroll
-            for (int r = 0; r < TC_BK / 16; ++r) {
-                {
-                    uint32_t st[8];
-                    lane_states<K>(raw + (r * (TC_BN / 16) + nt) * 8 * K, lane, st);
-                    const half2 w0 = decode_pair<CB>(st[0], st[1]);      // rows 2t, 2t+1   col g
-                    const half2 w1 = decode_pair<CB>(st[2], st[3]);      // rows 2t+8, +9   col g
-                    const half2 w2 = decode_pair<CB>(st[4], st[5]);      // rows 2t, 2t+1   col g+8
-                    const half2 w3 = decode_pair<CB>(st[6], st[7]);      // rows 2t+8, +9   col g+8
-                    // B tile row = n (128 bytes = 64 k), 16-byte chunk index XOR (n & 7)
-                    const int na = nt * 16 + g, nb = na + 8;
-                    const int c0 = 2 * r, c1 = 2 * r + 1;                 // chunks of k = 16r + [0,8) and [8,16)
-                    uint8_t* ra = bt + na * 128; uint8_t* rb = bt + nb * 128;
-                    *reinterpret_cast<half2*>(ra + ((c0 ^ (na & 7)) << 4) + 4 * t) = w0;
-                    *reinterpret_cast<half2*>(ra + ((c1 ^ (na & 7)) << 4) + 4 * t) = w1;
-                    *reinterpret_cast<half2*>(rb + ((c0 ^ (nb & 7)) << 4) + 4 * t) = w2;
-                    *reinterpret_cast<half2*>(rb + ((c1 ^ (nb & 7)) << 4) + 4 * t) = w3;
-                }
+            for (int r = r0; r < TC_BK / 16; r += TC_DECODERS / NT) {
+                uint32_t st[8];
+                lane_states<K>(raw + (r * NT + nt) * 8 * K, lane, st);
+                const half2 w0 = decode_pair<CB>(st[0], st[1]);      // rows 2t, 2t+1   col g
+                const half2 w1 = decode_pair<CB>(st[2], st[3]);      // rows 2t+8, +9   col g
+                const half2 w2 = decode_pair<CB>(st[4], st[5]);      // rows 2t, 2t+1   col g+8
+                const half2 w3 = decode_pair<CB>(st[6], st[7]);      // rows 2t+8, +9   col g+8
+                // B tile row = n (128 bytes = 64 k), 16-byte chunk index XOR (n & 7)
+                const int na = nt * 16 + g, nb = na + 8;
+                const int c0 = 2 * r, c1 = 2 * r + 1;                 // chunks of k = 16r + [0,8) and [8,16)
+                uint8_t* ra = bt + na * 128; uint8_t* rb = bt + nb * 128;
+                *reinterpret_cast<half2*>(ra + ((c0 ^ (na & 7)) << 4) + 4 * t) = w0;
+                *reinterpret_cast<half2*>(ra + ((c1 ^ (na & 7)) << 4) + 4 * t) = w1;
+                *reinterpret_cast<half2*>(rb + ((c0 ^ (nb & 7)) << 4) + 4 * t) = w2;
+                *reinterpret_cast<half2*>(rb + ((c1 ^ (nb & 7)) << 4) + 4 * t) = w3;
             }
-            fence_proxy_async();                 // make the generic-proxy stores visible to the tensor core's reads
+            // make the generic-proxy stores visible to the tensor core's reads, then tell the issuer
+            fence_proxy_async();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&b_full[sb]); mbar_arrive(&r_empty[sr]); }
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(&b_full[sb], 0); else mbar_arrive(&b_full[sb]);
+                mbar_arrive(&r_empty[sr]);
+            }
         }
     }
 
-    // ===== epilogue (warps 2..17): TMEM -> registers -> output transform -> global
+    // ===== epilogue (warps 2..17): TMEM -> registers -> output transform -> global.  Each CTA stores its own rows.
     if (warp >= 2 && !failed) {
         if (!mbar_wait_warp(acc_full, 0)) failed = true;
         if (!failed) {
@@ -254,7 +358,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             const int q = warp & 3, mt = (warp - 2) >> 3, sel = ((warp - 2) >> 2) & 1;
             const half* svh_s = reinterpret_cast<const half*>(smem + SM::OFF_SVH) + sel * 128;
             if (mt == 0 || two_tiles) {
-                const int row = m0 + mt * 128 + q * 32 + lane;
+                const int row = (mt ? row_t1 : row_t0) + q * 32 + lane;
                 const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + mt * TC_BN + sel * 128;
                 // The 128-point transform of a row is split so that a thread never holds more than 32 accumulators:
                 // the two outer butterfly levels (strides 32 and 64) run on 8-column slices and go back to TMEM, the five
@@ -320,13 +424,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         }
     }
 
-    // ===== tear-down: every path arrives here; TMEM is released by the warp that allocated it
+    // ===== tear-down: every path arrives here; TMEM is released by the warp that allocated it, and in a pair only after
+    // both CTAs are done with their accumulators and with each other's barriers and shared memory
     if (failed) s_failed = 1;
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }
     if (tid == 0 && s_failed) atomicExch(p.status, 2);
 }

@@ -312,3 +312,36 @@ def test_gemm_fanout_equals_separate_calls(ctx, m, ns, K, c_fp32):
     for got, want in zip(outs, wants):
         assert torch.isfinite(got).all()
         assert torch.equal(got, want)
+
+
+@pytest.fixture(scope="module")
+def ctx_one_cta():
+    """A context whose tcgen05 GEMM runs one CTA per tile instead of CTA pairs (cta_group::2)."""
+    import os
+    import exl3b200
+    os.environ["EXL3_B200_NO_PAIR"] = "1"
+    try:
+        c = exl3b200.Ctx(0)
+    finally:
+        del os.environ["EXL3_B200_NO_PAIR"]
+    yield c
+    c.close()
+
+
+@pytest.mark.parametrize("m", [129, 256, 257, 300, 384, 385, 512, 513, 700, 1052])
+def test_gemm_tc_pair_equals_one_cta(ctx, ctx_one_cta, m):
+    """the CTA-pair form and the one-CTA form run the same multiplies in the same order: equal bit for bit, at every
+    split of the rows over the pair's four 128-row tiles"""
+    torch = _torch()
+    r = H.rng(1400 + m)
+    k, n, K = 1024, 768, 4
+    A = H.to_dev(r.standard_normal((m, k)).astype(np.float16))
+    tr, suh, svh = H.to_dev(H.rand_trellis(r, k, n, K)), H.to_dev(H.rand_signs(r, k)), H.to_dev(H.rand_signs(r, n))
+    outs = []
+    for c in (ctx, ctx_one_cta):
+        out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+        c.exl3_gemm(A, tr, out, suh, None, svh, mcg=True)
+        c.poll_status()
+        outs.append(out)
+    assert torch.isfinite(outs[0]).all()
+    assert torch.equal(outs[0], outs[1])

@@ -67,6 +67,12 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, u
     const bool ok = mbar_wait(bar, parity, limit);
     return __all_sync(0xffffffffu, ok);
 }
+// Warp-uniform form of mbar_wait_sleep.
+__device__ __forceinline__ bool mbar_wait_sleep_warp(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 20), uint32_t ns = 2000)
+{
+    const bool ok = mbar_wait_sleep(bar, parity, limit, ns);
+    return __all_sync(0xffffffffu, ok);
+}
 // global -> shared bulk copy; dst/src 16-byte aligned, bytes % 16 == 0; completion counted on `bar`
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
 {

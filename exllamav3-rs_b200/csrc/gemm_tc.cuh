@@ -33,11 +33,14 @@ constexpr float TC_R128 = 0.088388347648f;
 template <int K, int CTAS> struct TcSmem {
     static constexpr int SA = CTAS == 2 ? 4 : 3;         // stages: activations,
     static constexpr int SB = CTAS == 2 ? 4 : 2;         //         decoded weights,
-    static constexpr int SR = 3;                         //         raw codes
     static constexpr int NB = TC_BN / CTAS;              // columns this CTA decodes
     static constexpr int B_STAGE = NB * TC_BK * 2;
     static constexpr int RAW_ROW = (NB / 16) * 32 * K;   // one tile row of codes: NB/16 tiles x 32K bytes
     static constexpr int RAW_STAGE = (TC_BK / 16) * RAW_ROW;
+    // raw codes come from HBM with the longest latency of the three rings and are the smallest: a deep ring keeps
+    // enough bytes in flight (a pair CTA has about 32 KB left for it, one CTA alone 24 KB)
+    static constexpr int SR_ROOM = (CTAS == 2 ? 32 : 24) * 1024 / RAW_STAGE;
+    static constexpr int SR = SR_ROOM > 8 ? 8 : (SR_ROOM < 3 ? 3 : SR_ROOM);
     static constexpr int OFF_A = 0;
     static constexpr int OFF_B = OFF_A + SA * TC_A_STAGE;
     static constexpr int OFF_RAW = OFF_B + SB * B_STAGE;
@@ -105,14 +108,15 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta)
     asm volatile("{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\t"
                  "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}" ::"r"(smem_u32(bar)), "r"(cta) : "memory");
 }
-// bounded wait that acquires at cluster scope (the arrivals or bytes may come from the other CTA)
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22))
+// bounded wait that acquires at cluster scope (the arrivals or bytes may come from the other CTA); each poll may sleep
+// up to `ns` nanoseconds inside the instruction and returns early when the phase completes
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 20), uint32_t ns = 2000)
 {
     for (uint32_t i = 0; i < limit; ++i) {
         uint32_t ok;
         asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+                     "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
         if (ok) return true;
     }
     return false;
@@ -213,14 +217,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     const int rank = PAIR ? (int)cluster_ctarank() : 0;                  // 0 = leader of the pair
     const int slab = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int seg = (slab >= p.blk_end[0]) + (slab >= p.blk_end[1]);
-    const int n0 = (slab - (seg ? p.blk_end[seg - 1] : 0)) * TC_BN;     // first column of the slab
+    const int n0 = (slab - (seg == 0 ? 0 : (seg == 1 ? p.blk_end[0] : p.blk_end[1]))) * TC_BN;     // first column of the slab
     const int nd0 = n0 + rank * SM::NB;                                  // first column this CTA decodes
     const int m0 = blockIdx.y * (TC_BM * CTAS);
     const int row_t0 = m0 + rank * 128, row_t1 = row_t0 + 128 * CTAS;    // first rows of this CTA's two M tiles
     const CUtensorMap* amap = seg == 0 ? &amap0 : (seg == 1 ? &amap1 : &amap2);
-    const uint32_t* trellis = p.trellis[seg];
-    const half* svh = p.svh[seg];
-    const int n = p.n[seg];
+    // (selected with compares: indexing the parameter arrays with `seg` would put a copy of them in local memory)
+    const uint32_t* trellis = seg == 0 ? p.trellis[0] : (seg == 1 ? p.trellis[1] : p.trellis[2]);
+    const half* svh = seg == 0 ? p.svh[0] : (seg == 1 ? p.svh[1] : p.svh[2]);
+    void* Cout = seg == 0 ? p.C[0] : (seg == 1 ? p.C[1] : p.C[2]);
+    const int n = seg == 0 ? p.n[0] : (seg == 1 ? p.n[1] : p.n[2]);
     const int tiles_n = n >> 4;
     const int ksteps = p.k / TC_BK;
     const bool two_tiles = p.m - m0 > 128 * CTAS;          // otherwise the second M tile (of both CTAs) has no valid row
@@ -255,9 +261,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         // ===== producer: activations by TMA, trellis codes by bulk copies
         if (lane == 0) {
             const uint32_t a_bytes = (two_tiles ? 2u : 1u) * TC_A_TILE * CTAS;     // what lands on the leader's barrier
+            constexpr int AHEAD = SM::SR > SM::SA ? SM::SR - SM::SA : 0;          // the code ring runs this far ahead of A
+            auto load_raw = [&](int kr) {
+                const int sr = kr % SM::SR;
+                mbar_expect_tx(&r_full[sr], SM::RAW_STAGE);
+                #pragma unroll
+                for (int r = 0; r < TC_BK / 16; ++r)
+                    bulk_g2s(smem + SM::OFF_RAW + sr * SM::RAW_STAGE + r * SM::RAW_ROW,
+                             trellis + ((size_t)(kr * (TC_BK / 16) + r) * tiles_n + (nd0 >> 4)) * 8 * K, SM::RAW_ROW, &r_full[sr]);
+            };
+            for (int kr = 0; kr < AHEAD && kr < ksteps; ++kr) load_raw(kr);
             for (int ks = 0; ks < ksteps; ++ks) {
-                const int sa = ks % SM::SA, sr = ks % SM::SR;
-                if (ks >= SM::SA && !mbar_wait(&a_empty[sa], ((ks / SM::SA) - 1) & 1)) { failed = true; break; }
+                const int kr = ks + AHEAD;
+                if (kr < ksteps) {
+                    if (kr >= SM::SR && !mbar_wait_sleep(&r_empty[kr % SM::SR], ((kr / SM::SR) - 1) & 1)) { failed = true; break; }
+                    load_raw(kr);
+                }
+                const int sa = ks % SM::SA;
+                if (ks >= SM::SA && !mbar_wait_sleep(&a_empty[sa], ((ks / SM::SA) - 1) & 1)) { failed = true; break; }
                 uint8_t* at = smem + SM::OFF_A + sa * TC_A_STAGE;
                 if constexpr (PAIR) {
                     if (rank == 0) mbar_expect_tx(&a_full[sa], a_bytes);
@@ -268,12 +289,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                     tma_load_2d(at, amap, ks * TC_BK, row_t0, &a_full[sa]);
                     if (two_tiles) tma_load_2d(at + TC_A_TILE, amap, ks * TC_BK, row_t1, &a_full[sa]);
                 }
-                if (ks >= SM::SR && !mbar_wait(&r_empty[sr], ((ks / SM::SR) - 1) & 1)) { failed = true; break; }
-                mbar_expect_tx(&r_full[sr], SM::RAW_STAGE);
-                #pragma unroll
-                for (int r = 0; r < TC_BK / 16; ++r)
-                    bulk_g2s(smem + SM::OFF_RAW + sr * SM::RAW_STAGE + r * SM::RAW_ROW,
-                             trellis + ((size_t)(ks * (TC_BK / 16) + r) * tiles_n + (nd0 >> 4)) * 8 * K, SM::RAW_ROW, &r_full[sr]);
             }
         }
     } else if (warp == 1) {
@@ -282,7 +297,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             for (int ks = 0; ks < ksteps; ++ks) {
                 const int sa = ks % SM::SA, sb = ks % SM::SB;
                 const bool ok = PAIR ? (mbar_wait_cluster(&a_full[sa], (ks / SM::SA) & 1) && mbar_wait_cluster(&b_full[sb], (ks / SM::SB) & 1))
-                                     : (mbar_wait(&a_full[sa], (ks / SM::SA) & 1) && mbar_wait(&b_full[sb], (ks / SM::SB) & 1));
+                                     : (mbar_wait_sleep(&a_full[sa], (ks / SM::SA) & 1) && mbar_wait_sleep(&b_full[sb], (ks / SM::SB) & 1));
                 if (!ok) { failed = true; break; }
                 tc_fence_after();
                 const uint64_t adesc0 = tc_smem_desc(smem + SM::OFF_A + sa * TC_A_STAGE);
@@ -313,39 +328,53 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         }
     } else {
         // ===== decoders: raw codes -> fp16 weights in the K-major swizzled B tile
+        constexpr int RSTEP = TC_DECODERS / NT;                    // a warp takes every RSTEP-th tile row (1 or 2)
+        constexpr int TPW = (TC_BK / 16) / RSTEP;                  // tiles per warp and stage (4 or 2)
         const int nt = (warp - 2) % NT;                            // tile column of this CTA's part of the slab
-        const int r0 = (warp - 2) / NT;                            // first tile row; the warp takes every (16 / NT)-th
+        const int r0 = (warp - 2) / NT;                            // first tile row
         const int g = lane >> 2, t = lane & 3;
+        // Tile row r covers k = 16r..16r+15 of the stage: 16-byte chunks 2r and 2r+1 of a 128-byte B row.  B row = column
+        // na = 16nt + g (and na + 8, 1024 bytes further on); the chunk index is XORed with (row & 7) = g for both.
+        uint32_t raw_off[TPW], st_off[TPW][2];
+        #pragma unroll
+        for (int i = 0; i < TPW; ++i) {
+            const int r = r0 + i * RSTEP;
+            raw_off[i] = (r * NT + nt) * 8 * K;
+            st_off[i][0] = (nt * 16 + g) * 128 + (((2 * r) ^ g) << 4) + 4 * t;
+            st_off[i][1] = (nt * 16 + g) * 128 + (((2 * r + 1) ^ g) << 4) + 4 * t;
+        }
+        uint32_t bfull_addr = smem_u32(&b_full[0]);
+        if constexpr (PAIR) asm volatile("mapa.shared::cluster.u32 %0, %0, 0;" : "+r"(bfull_addr));
+        int sr = 0, sb = 0;
+        uint32_t par_r = 0, par_b = 1;                             // b_empty is waited from the second round on
         for (int ks = 0; ks < ksteps; ++ks) {
-            const int sr = ks % SM::SR, sb = ks % SM::SB;
-            if (!mbar_wait_warp(&r_full[sr], (ks / SM::SR) & 1)) { failed = true; break; }
-            if (ks >= SM::SB && !mbar_wait_warp(&b_empty[sb], ((ks / SM::SB) - 1) & 1)) { failed = true; break; }
+            if (!mbar_wait_sleep_warp(&r_full[sr], par_r)) { failed = true; break; }
+            if (ks >= SM::SB && !mbar_wait_sleep_warp(&b_empty[sb], par_b)) { failed = true; break; }
             const uint32_t* raw = reinterpret_cast<const uint32_t*>(smem + SM::OFF_RAW + sr * SM::RAW_STAGE);
             uint8_t* bt = smem + SM::OFF_B + sb * SM::B_STAGE;
+            uint32_t st[TPW][8];
             #pragma unroll
-            for (int r = r0; r < TC_BK / 16; r += TC_DECODERS / NT) {
-                uint32_t st[8];
-                lane_states<K>(raw + (r * NT + nt) * 8 * K, lane, st);
-                const half2 w0 = decode_pair<CB>(st[0], st[1]);      // rows 2t, 2t+1   col g
-                const half2 w1 = decode_pair<CB>(st[2], st[3]);      // rows 2t+8, +9   col g
-                const half2 w2 = decode_pair<CB>(st[4], st[5]);      // rows 2t, 2t+1   col g+8
-                const half2 w3 = decode_pair<CB>(st[6], st[7]);      // rows 2t+8, +9   col g+8
-                // B tile row = n (128 bytes = 64 k), 16-byte chunk index XOR (n & 7)
-                const int na = nt * 16 + g, nb = na + 8;
-                const int c0 = 2 * r, c1 = 2 * r + 1;                 // chunks of k = 16r + [0,8) and [8,16)
-                uint8_t* ra = bt + na * 128; uint8_t* rb = bt + nb * 128;
-                *reinterpret_cast<half2*>(ra + ((c0 ^ (na & 7)) << 4) + 4 * t) = w0;
-                *reinterpret_cast<half2*>(ra + ((c1 ^ (na & 7)) << 4) + 4 * t) = w1;
-                *reinterpret_cast<half2*>(rb + ((c0 ^ (nb & 7)) << 4) + 4 * t) = w2;
-                *reinterpret_cast<half2*>(rb + ((c1 ^ (nb & 7)) << 4) + 4 * t) = w3;
+            for (int i = 0; i < TPW; ++i) lane_states<K>(raw + raw_off[i], lane, st[i]);
+            #pragma unroll
+            for (int i = 0; i < TPW; ++i) {
+                const half2 w0 = decode_pair<CB>(st[i][0], st[i][1]);      // rows 2t, 2t+1   col g
+                const half2 w1 = decode_pair<CB>(st[i][2], st[i][3]);      // rows 2t+8, +9   col g
+                const half2 w2 = decode_pair<CB>(st[i][4], st[i][5]);      // rows 2t, 2t+1   col g+8
+                const half2 w3 = decode_pair<CB>(st[i][6], st[i][7]);      // rows 2t+8, +9   col g+8
+                *reinterpret_cast<half2*>(bt + st_off[i][0]) = w0;
+                *reinterpret_cast<half2*>(bt + st_off[i][1]) = w1;
+                *reinterpret_cast<half2*>(bt + st_off[i][0] + 1024) = w2;
+                *reinterpret_cast<half2*>(bt + st_off[i][1] + 1024) = w3;
             }
             // make the generic-proxy stores visible to the tensor core's reads, then tell the issuer
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-                if constexpr (PAIR) mbar_arrive_cluster(&b_full[sb], 0); else mbar_arrive(&b_full[sb]);
+                asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bfull_addr + 8u * sb) : "memory");
                 mbar_arrive(&r_empty[sr]);
             }
+            if (++sr == SM::SR) { sr = 0; par_r ^= 1; }
+            if (++sb == SM::SB) { sb = 0; par_b ^= 1; }
         }
     }
 
@@ -394,7 +423,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                         const size_t off = (size_t)row * n + n0 + sel * 128 + j * 32;
                         const half* sv = svh_s + j * 32;
                         if (p.c_fp32) {
-                            float4* dst = reinterpret_cast<float4*>((float*)p.C[seg] + off);
+                            float4* dst = reinterpret_cast<float4*>((float*)Cout + off);
                             #pragma unroll
                             for (int e = 0; e < 32; e += 4) {
                                 float4 o = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
@@ -405,7 +434,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                                 dst[e >> 2] = o;
                             }
                         } else {
-                            uint4* dst = reinterpret_cast<uint4*>((half*)p.C[seg] + off);
+                            uint4* dst = reinterpret_cast<uint4*>((half*)Cout + off);
                             #pragma unroll
                             for (int e = 0; e < 32; e += 8) {
                                 uint32_t w[4];

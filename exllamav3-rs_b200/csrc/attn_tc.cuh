@@ -68,7 +68,9 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attn_tc_kernel(const __grid_co
     const int item_idx = blockIdx.x;
     if (item_idx >= p.plan->n_items) return;
     extern __shared__ uint8_t smem_unaligned[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    // aligned to 1024 bytes by an offset from the array, not through an integer, so that the compiler still knows the
+    // pointer is in shared memory (32-bit addresses, ld/st.shared) instead of falling back to generic accesses
+    uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATC_OFF_BAR);
     uint64_t* q_full = bars;
     uint64_t* k_full = q_full + 1;                 uint64_t* v_full = k_full + ATC_KV_STAGES;

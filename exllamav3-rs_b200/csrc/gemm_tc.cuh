@@ -204,7 +204,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     constexpr bool PAIR = CTAS == 2;
     constexpr int NT = SM::NB / 16;                       // tile columns this CTA decodes (16 or 8)
     extern __shared__ uint8_t smem_unaligned[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    // aligned to 1024 bytes by an offset from the array, not through an integer, so that the compiler still knows the
+    // pointer is in shared memory (32-bit addresses, ld/st.shared) instead of falling back to generic accesses
+    uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
     uint64_t* a_full = bars;                  uint64_t* a_empty = a_full + SM::SA;
     uint64_t* r_full = a_empty + SM::SA;      uint64_t* r_empty = r_full + SM::SR;

@@ -355,8 +355,10 @@ def run_ops(args):
         dbt, dsl = torch.from_numpy(bt).cuda(), torch.from_numpy(ctx_lens).cuda()
         t = time_calls([lambda st: ctx.bighead_attn_paged(q, kn, kn, kc, vc, dbt, dsl, out, stream=st)], args.reps)
         byts = float((ctx_lens + q_len).sum()) * nkv * hd * 2 * 2
+        flops = float((4.0 * q_len * nq * hd * (ctx_lens + (q_len + 1) / 2)).sum())       # QK^T and PV under the causal mask
         print(json.dumps({"op": "bighead_attn_paged", "seqs": bsz, "q_len": q_len, "mean_ctx": float(ctx_lens.mean()),
                           "kv_bytes": byts, "us": t * 1e6, "GBps": byts / t / 1e9, "hbm_frac": byts / t / 1e9 / hbm_peak,
+                          "TFLOPs": flops / t / 1e12,
                           "note": "KV pool %.1f GB" % (kc.numel() * 4 / 1e9), "peaks": which}))
     ctx.poll_status()
 

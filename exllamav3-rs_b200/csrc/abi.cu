@@ -34,7 +34,7 @@ extern "C" int exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** ou
         return EXL3_ERR_UNSUPPORTED;
     }
     ctx->num_sms = prop.multiProcessorCount;
-    ctx->ws_bytes = workspace_bytes ? workspace_bytes : ((size_t)256 << 20);
+    ctx->ws_bytes = workspace_bytes ? workspace_bytes : ((size_t)512 << 20);
     ctx->n_counters = 1 << 16;
     bool ok = cudaMalloc(&ctx->ws, ctx->ws_bytes) == cudaSuccess &&
               cudaMalloc(&ctx->counters, ctx->n_counters * sizeof(int)) == cudaSuccess &&

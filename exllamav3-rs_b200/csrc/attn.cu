@@ -13,7 +13,7 @@ using namespace exl3;
 // Only sequences whose packed row count ql*G lies in (rows_lo, rows_hi] get work items; the others are left to another pass.
 __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restrict__ seqlens,
                                                          const int32_t* __restrict__ cu_q, int bsz, int q_len,
-                                                         int kv_append, int G, int rows_per_cta, int rows_lo, int rows_hi, int target_items,
+                                                         int kv_append, int G, int rows_per_cta, int rows_lo, int rows_hi, int chunk_mult, int target_items,
                                                          int max_items, AttnPlan* plan, AttnItem* items, int* seq_base,
                                                          int* seq_splits)
 {
@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
     __syncthreads();
     if (tid == 0) {
         long long c = (s_total + target_items - 1) / target_items;
-        c = (c + AT_TK - 1) / AT_TK * AT_TK;
+        c = (c + chunk_mult - 1) / chunk_mult * chunk_mult;       // splits start on a key-tile boundary of the kernel
         if (c < 256) c = 256;
         if (c > (1 << 30)) c = 1 << 30;
         s_chunk = (int)c;
@@ -166,7 +166,7 @@ cudaError_t launch_attn_tc(exl3_ctx* ctx, const AttnParams& p, int max_items, cu
     for (int i = 0; i < 2; ++i) {
         cuuint64_t dims[4] = {(cuuint64_t)ATC_D, (cuuint64_t)p.nkv, 256, (cuuint64_t)p.pages};
         cuuint64_t strides[3] = {(cuuint64_t)ATC_D * 2, (cuuint64_t)p.nkv * ATC_D * 2, (cuuint64_t)256 * p.nkv * ATC_D * 2};
-        cuuint32_t box[4] = {64, 1, (cuuint32_t)ATC_TN, 1};
+        cuuint32_t box[4] = {64, 1, (cuuint32_t)ATC_TN, 1};           // 128 tokens of one page, one 64-wide d block
         cuuint32_t estr[4] = {1, 1, 1, 1};
         if (enc(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(pools[i]), dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -192,11 +192,13 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
 {
     const int D = 128;
     const int G = p.nq / p.nkv;
-    // long class on fp16 pools: tcgen05 kernel (128-row blocks) unless the context was switched to the mma.sync kernels
-    const bool use_tc = !decode_shape && !quant && ctx->mma_attn != 0;
-    const int rows_per_cta = decode_shape ? 16 : (use_tc ? ATC_ROWS : 64);
+    // long class on fp16 pools: tcgen05 kernel (256-row items) unless the context was switched to the mma.sync kernels
+    // (its row maximum is taken on the raw scores, which needs a positive scale)
+    const bool use_tc = !decode_shape && !quant && ctx->mma_attn != 0 && p.scale_log2 > 0.f;
+    const int rows_per_cta = decode_shape ? 16 : (use_tc ? ATC_CTA_ROWS : 64);
     const int rb_max = (max_rows + rows_per_cta - 1) / rows_per_cta;
-    const int grid_x = (ctx->num_sms * 3 + p.nkv - 1) / p.nkv;    // about 3 resident CTAs per SM over all kv heads
+    // resident CTAs per SM over all kv heads: about 3 for the mma.sync kernels, 1 for the tcgen05 kernel (all of TMEM)
+    const int grid_x = (ctx->num_sms * (use_tc ? 1 : 3) + p.nkv - 1) / p.nkv;
     const int target_items = grid_x * 2;
     const int max_items = target_items + p.bsz * rb_max + 1;
 
@@ -212,7 +214,7 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     p.status = ctx->status;
 
     attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, rows_lo, rows_hi,
-                                          target_items, max_items, plan, items, seq_base, seq_splits);
+                                          use_tc ? ATC_TN : AT_TK, target_items, max_items, plan, items, seq_base, seq_splits);
     ctx->launches++;
     dim3 grid(grid_x, p.nkv);
     cudaError_t e;

@@ -55,7 +55,7 @@ enum { EXL3_ROPE_NONE = 0, EXL3_ROPE_GPTJ = 1, EXL3_ROPE_NEOX = 2 };
 /* ------------------------------------------------------------------------------------------------ context */
 
 /* Create the per-device context (allocates scratch with cudaMalloc on `device`).  `workspace_bytes` = 0 picks the
- * default (256 MiB).  Replaces the reference's DevCtx singleton (kernels/quant/exl3_devctx.cuh:18-40). */
+ * default (512 MiB).  Replaces the reference's DevCtx singleton (kernels/quant/exl3_devctx.cuh:18-40). */
 EXL3_API int  exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** out);
 EXL3_API void exl3_ctx_destroy(exl3_ctx* ctx);
 /* host string describing the last error on this context (never NULL) */

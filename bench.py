@@ -47,6 +47,23 @@ def shard_batch(rank, seed=1234):
     return q_lens, ctx, bt, pages, ids
 
 
+def reduce_max_ms(ms_local, world, device="cpu"):
+    """Device time of a multi-rank run: the slowest rank's.  One all_reduce(MAX) over the job's process group (NCCL on
+    GPUs, gloo in the CPU tests); the data path itself has no collective: sequences never leave their rank."""
+    if world <= 1:
+        return float(ms_local)
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([float(ms_local)], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_value(rows_per_rank, world, ms_per_step):
+    """Tokens/s of the whole job under weak scaling: every rank processes `rows_per_rank` rows per step."""
+    return rows_per_rank * world / (ms_per_step * 1e-3)
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
 
@@ -204,10 +221,7 @@ def run_ours(args):
             fn()
         e1.record(stream)
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        return reduce_max_ms(e0.elapsed_time(e1), world, dev)
 
     for _ in range(max(args.warmup, 3)):
         step_resident()
@@ -215,7 +229,10 @@ def run_ours(args):
     sampler = ClockSampler(local)
     sampler.start()
     l0 = ctx.launch_count()
+    # a profiler started with `--profile-from-start off` sees exactly the timed steps (no effect otherwise)
+    torch.cuda.cudart().cudaProfilerStart()
     ms_total = timed(step_resident, args.steps)
+    torch.cuda.cudart().cudaProfilerStop()
     launches = (ctx.launch_count() - l0) // max(args.steps, 1)
     clocks = sampler.stop()
     step_e2e()
@@ -223,9 +240,8 @@ def run_ours(args):
     ctx.poll_status()
 
     ms_step = ms_total / args.steps
-    total_rows = rows * world
-    value = total_rows / (ms_step * 1e-3)
-    e2e_value = total_rows / (ms_e2e / args.steps * 1e-3)
+    value = whole_job_value(rows, world, ms_step)
+    e2e_value = whole_job_value(rows, world, ms_e2e / args.steps)
     h2d = int(ids.nbytes + q_lens.nbytes + ctx_lens.nbytes + bt.nbytes)
 
     # ---- roofline of the dominant kernel: the EXL3 GEMM at the step's row count, timed on L2-cold weights (the 64

@@ -271,6 +271,11 @@ typedef struct {
     int bsz, rows, max_q_len, pages_per_seq, advance;
 } exl3_batch;
 
+/* exl3_shim_hgemm (src/ffi.rs:66, csrc/exl3_shim.cpp:93 -> kernels/hgemm.cu:19-78): C[m,n] = A[m,k] . B[k,n],
+ * fp16 inputs, fp32 accumulation, C fp16 or fp32.  k % 64 == 0, n % 8 == 0. */
+EXL3_API int exl3_hgemm(exl3_ctx* ctx, exl3_stream stream, const void* a, const void* b, void* c, int m, int k, int n,
+               int c_fp32);
+
 /* The same activations A [m,k] through `count` (1..3) EXL3 tensors, C[i] [m, w[i]->n]: what the reference issues as
  * separate exl3_shim_gemm calls for q/k/v (src/modules.rs:646-648) and gate/up (src/modules.rs:933-934).  Results are
  * those of `count` exl3_gemm calls; tensors that agree in k, bits and codebook share one tensor-core launch. */

@@ -345,3 +345,42 @@ def test_gemm_tc_pair_equals_one_cta(ctx, ctx_one_cta, m):
         outs.append(out)
     assert torch.isfinite(outs[0]).all()
     assert torch.equal(outs[0], outs[1])
+
+
+# ------------------------------------------------------------------------------------------ dense fp16 GEMM (tcgen05)
+
+@pytest.mark.parametrize("m,k,n,c_fp32", [(1, 64, 8, False), (128, 128, 256, False), (129, 192, 264, True),
+                                          (300, 1024, 776, False), (1052, 5120, 1024, False), (77, 17408, 5120, True)])
+def test_hgemm_vs_oracle_and_reference(ctx, ref, m, k, n, c_fp32):
+    """C = A.B with fp32 accumulation against the CPU oracle (exact fp32-accumulate product rounded once) and, where the
+    reference library is present, its cuBLAS call; covers row/column tails and a K far longer than the tile"""
+    torch = _torch()
+    from oracle import oracle as O
+    r = H.rng(1500 + m + n)
+    A = (r.standard_normal((m, k)) * 0.5).astype(np.float16)
+    B = (r.standard_normal((k, n)) * 0.5).astype(np.float16)
+    dA, dB = H.to_dev(A), H.to_dev(B)
+    dt = torch.float32 if c_fp32 else torch.float16
+    out = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+    ctx.hgemm(dA, dB, out)
+    ctx.poll_status()
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    small = m * k * n <= 300 * 1024 * 776
+    want = O.hgemm(A, B, c_fp32=c_fp32).astype(np.float32) if small else (A.astype(np.float32) @ B.astype(np.float32))
+    assert H.gemm_mismatch(got, want, GEMM_TOL, not c_fp32) <= 1.0
+    if ref is not None:
+        C2 = torch.zeros_like(out)
+        ref.ref_hgemm(H.ptr(dA), H.ptr(dB), H.ptr(C2), m, k, n, int(c_fp32))
+        torch.cuda.synchronize()
+        assert H.gemm_mismatch(got, C2.float().cpu().numpy(), GEMM_TOL, not c_fp32) <= 1.0
+
+
+def test_hgemm_rejects_bad_shapes(ctx):
+    torch = _torch()
+    import exl3b200
+    a = torch.zeros(4, 96, dtype=torch.float16, device="cuda")
+    b = torch.zeros(96, 16, dtype=torch.float16, device="cuda")
+    c = torch.zeros(4, 16, dtype=torch.float16, device="cuda")
+    with pytest.raises(exl3b200.Exl3Error):
+        ctx.hgemm(a, b, c)                       # k = 96 is no multiple of 64

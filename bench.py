@@ -198,14 +198,34 @@ def run_ours(args):
     max_q = int(q_lens.max())
     stream = torch.cuda.current_stream()
 
+    # The step is captured once into a CUDA graph on the context's side stream (the reference's CudaGraph,
+    # src/ffi.rs:403-451, does the same for its decode loop) and replayed: the device buffers the step reads are
+    # fixed, their contents change per step.  --no-graph launches the ~1200 kernels of a step one by one instead.
+    for _ in range(2):
+        model.step(ctx, d_ids, d_q, d_sl, d_bt, max_q)
+    torch.cuda.synchronize()
+    graph, tok_static, launches_captured = None, torch.empty(bsz, dtype=torch.int64, device=dev), None
+    if not args.no_graph:
+        graph = exl3b200.CudaGraph(ctx)
+        stream = torch.cuda.ExternalStream(graph.side_stream(), device=dev)
+        l0 = ctx.launch_count()
+        graph.capture_begin()
+        model.step(ctx, d_ids, d_q, d_sl, d_bt, max_q, stream=graph.side_stream(), tokens_out=tok_static)
+        graph.capture_end()
+        launches_captured = ctx.launch_count() - l0
+
     def step_resident():
-        return model.step(ctx, d_ids, d_q, d_sl, d_bt, max_q)[0]
+        if graph is not None:
+            graph.replay()
+            return tok_static
+        return model.step(ctx, d_ids, d_q, d_sl, d_bt, max_q, tokens_out=tok_static)[0]
 
     def step_e2e():
-        d_ids.copy_(h_ids, non_blocking=True); d_q.copy_(h_q, non_blocking=True)
-        d_sl.copy_(h_sl, non_blocking=True); d_bt.copy_(h_bt, non_blocking=True)
-        tok = model.step(ctx, d_ids, d_q, d_sl, d_bt, max_q)[0]
-        return tok.cpu()                       # device -> host read of the sampled tokens (synchronises)
+        with torch.cuda.stream(stream):
+            d_ids.copy_(h_ids, non_blocking=True); d_q.copy_(h_q, non_blocking=True)
+            d_sl.copy_(h_sl, non_blocking=True); d_bt.copy_(h_bt, non_blocking=True)
+            tok = step_resident()
+            return tok.cpu()                   # device -> host read of the sampled tokens (synchronises)
 
     def barrier():
         torch.cuda.synchronize()
@@ -233,7 +253,7 @@ def run_ours(args):
     torch.cuda.cudart().cudaProfilerStart()
     ms_total = timed(step_resident, args.steps)
     torch.cuda.cudart().cudaProfilerStop()
-    launches = (ctx.launch_count() - l0) // max(args.steps, 1)
+    launches = launches_captured if graph is not None else (ctx.launch_count() - l0) // max(args.steps, 1)
     clocks = sampler.stop()
     step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
@@ -257,10 +277,11 @@ def run_ours(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         g0 = ctx.launch_count()
-        e0.record(stream)
+        cur = torch.cuda.current_stream()
+        e0.record(cur)
         for l in lins:
             ctx.exl3_gemm(x, l.trellis, y, l.suh, None, l.svh, mcg=True)
-        e1.record(stream)
+        e1.record(cur)
         torch.cuda.synchronize()
         t_op = e0.elapsed_time(e1) * 1e-3 / len(lins)
         flops = 2.0 * rows * CFG["hidden"] * CFG["inter"]
@@ -287,7 +308,8 @@ def run_ours(args):
                            "l2": "inputs larger than L2 (11 GB of weights and the KV pool are streamed every step)"},
                 "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": bsz * 8},
-                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
+                "gpu_launches": int(launches), "launch_mode": "cuda graph replay" if graph is not None else "stream launches",
+                "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -393,6 +415,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the step's kernels one by one instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.op:
         run_ops(args)

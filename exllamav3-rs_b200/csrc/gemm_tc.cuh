@@ -243,8 +243,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     if (tid == 0) {
         s_failed = 0;
         for (int i = 0; i < SM::SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
-        for (int i = 0; i < SM::SR; ++i) { mbar_init(&r_full[i], 1); mbar_init(&r_empty[i], TC_DECODERS); }
-        for (int i = 0; i < SM::SB; ++i) { mbar_init(&b_full[i], TC_DECODERS * CTAS); mbar_init(&b_empty[i], 1); }
+        for (int i = 0; i < SM::SR; ++i) { mbar_init(&r_full[i], 1); mbar_init(&r_empty[i], TC_DECODERS / 2); }
+        for (int i = 0; i < SM::SB; ++i) { mbar_init(&b_full[i], TC_DECODERS / 2 * CTAS); mbar_init(&b_empty[i], 1); }
         mbar_init(acc_full, 1);
         mbar_init(drain, 1);
         mbar_fence_init();
@@ -301,79 +301,100 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer (one thread of the leader CTA)
-        if (lane == 0 && rank == 0) {
+        // ===== MMA issuer (leader CTA).  The whole warp runs the loop with warp-uniform values, so that descriptors and
+        // addresses stay in uniform registers (where tcgen05.mma takes them from); one elected lane issues.
+        if (rank == 0) {
+            const bool leader = elect_one();
+            constexpr uint32_t HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);     // SBO 1024, version 1, SWIZZLE_128B
+            const uint32_t a_lo = (smem_u32(smem + SM::OFF_A) >> 4) | (1u << 16);
+            const uint32_t b_lo = (smem_u32(smem + SM::OFF_B) >> 4) | (1u << 16);
+            auto mk = [](uint32_t lo) { return ((uint64_t)HI << 32) | lo; };
+            int sa = 0, sb = 0;
+            uint32_t par_a = 0, par_b = 0;
             for (int ks = 0; ks < ksteps; ++ks) {
-                const int sa = ks % SM::SA, sb = ks % SM::SB;
-                const bool ok = PAIR ? (mbar_wait_cluster(&a_full[sa], (ks / SM::SA) & 1) && mbar_wait_cluster(&b_full[sb], (ks / SM::SB) & 1))
-                                     : (mbar_wait_sleep(&a_full[sa], (ks / SM::SA) & 1) && mbar_wait_sleep(&b_full[sb], (ks / SM::SB) & 1));
-                if (!ok) { failed = true; break; }
+                const bool ok = PAIR ? (mbar_wait_cluster(&a_full[sa], par_a) && mbar_wait_cluster(&b_full[sb], par_b))
+                                     : (mbar_wait_sleep(&a_full[sa], par_a) && mbar_wait_sleep(&b_full[sb], par_b));
+                if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
                 tc_fence_after();
-                const uint64_t adesc0 = tc_smem_desc(smem + SM::OFF_A + sa * TC_A_STAGE);
-                const uint64_t adesc1 = tc_smem_desc(smem + SM::OFF_A + sa * TC_A_STAGE + TC_A_TILE);
-                const uint64_t bdesc = tc_smem_desc(smem + SM::OFF_B + sb * SM::B_STAGE);
-                #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk) {
-                    const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
-                    if constexpr (PAIR) {
-                        tc_mma_f16_pair(tmem_base, adesc0 + 2 * kk, bdesc + 2 * kk, TC_IDESC_PAIR, acc);      // +32 bytes per K=16
-                        if (two_tiles) tc_mma_f16_pair(tmem_base + TC_BN, adesc1 + 2 * kk, bdesc + 2 * kk, TC_IDESC_PAIR, acc);
-                    } else {
-                        tc_mma_f16(tmem_base, adesc0 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);
-                        if (two_tiles) tc_mma_f16(tmem_base + TC_BN, adesc1 + 2 * kk, bdesc + 2 * kk, TC_IDESC, acc);
+                const uint32_t a0 = a_lo + sa * (TC_A_STAGE >> 4), b0 = b_lo + sb * (SM::B_STAGE >> 4);
+                if (leader) {
+                    #pragma unroll
+                    for (int kk = 0; kk < TC_BK / 16; ++kk) {
+                        const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+                        if constexpr (PAIR) {
+                            tc_mma_f16_pair(tmem_base, mk(a0 + 2 * kk), mk(b0 + 2 * kk), TC_IDESC_PAIR, acc);      // +32 bytes per K=16
+                            if (two_tiles) tc_mma_f16_pair(tmem_base + TC_BN, mk(a0 + (TC_A_TILE >> 4) + 2 * kk), mk(b0 + 2 * kk), TC_IDESC_PAIR, acc);
+                        } else {
+                            tc_mma_f16(tmem_base, mk(a0 + 2 * kk), mk(b0 + 2 * kk), TC_IDESC, acc);
+                            if (two_tiles) tc_mma_f16(tmem_base + TC_BN, mk(a0 + (TC_A_TILE >> 4) + 2 * kk), mk(b0 + 2 * kk), TC_IDESC, acc);
+                        }
                     }
+                    // arrive when the MMAs above have finished reading the stage (in both CTAs of a pair)
+                    if constexpr (PAIR) { tc_commit_pair(&a_empty[sa]); tc_commit_pair(&b_empty[sb]); }
+                    else { tc_commit(&a_empty[sa]); tc_commit(&b_empty[sb]); }
                 }
-                // arrive when the MMAs above have finished reading the stage (in both CTAs of a pair)
-                if constexpr (PAIR) { tc_commit_pair(&a_empty[sa]); tc_commit_pair(&b_empty[sb]); }
-                else { tc_commit(&a_empty[sa]); tc_commit(&b_empty[sb]); }
+                __syncwarp();
+                if (++sa == SM::SA) { sa = 0; par_a ^= 1; }
+                if (++sb == SM::SB) { sb = 0; par_b ^= 1; }
             }
-            if (!failed) {
-                if constexpr (PAIR) tc_commit_pair(acc_full); else tc_commit(acc_full);
-            } else {
-                // leave no MMA in flight behind: the tear-down lets the other CTA go, whose shared memory they read
-                if constexpr (PAIR) tc_commit_pair(drain); else tc_commit(drain);
-                mbar_wait(drain, 0);
+            if (leader) {
+                if (!failed) {
+                    if constexpr (PAIR) tc_commit_pair(acc_full); else tc_commit(acc_full);
+                } else {
+                    // leave no MMA in flight behind: the tear-down lets the other CTA go, whose shared memory they read
+                    if constexpr (PAIR) tc_commit_pair(drain); else tc_commit(drain);
+                    mbar_wait(drain, 0);
+                }
             }
+            __syncwarp();
         }
     } else {
-        // ===== decoders: raw codes -> fp16 weights in the K-major swizzled B tile
-        constexpr int RSTEP = TC_DECODERS / NT;                    // a warp takes every RSTEP-th tile row (1 or 2)
-        constexpr int TPW = (TC_BK / 16) / RSTEP;                  // tiles per warp and stage (4 or 2)
-        const int nt = (warp - 2) % NT;                            // tile column of this CTA's part of the slab
-        const int r0 = (warp - 2) / NT;                            // first tile row
+        // ===== decoders: raw codes -> fp16 weights in the K-major swizzled B tile.
+        // The 16 warps form two groups of 8 (two warps per scheduler each) that take alternate K steps: while one group
+        // waits on its barriers, fences and arrives, the other decodes, so the schedulers stay busy (with all 16 warps
+        // in lockstep on every stage, the waits of a stage cost as much as its decode work).
+        constexpr int GW = TC_DECODERS / 2;                        // warps per group
+        constexpr int TPW = (TC_BK / 16) * NT / GW;                // tiles per warp and stage: 4 (pair) or 8
+        constexpr int TB = 4;                                      // tiles decoded together (register budget)
+        const int dw = warp - 2;
+        const int grp = (dw >> 2) & 1;
+        const int wi = (dw & 3) + 4 * (dw >> 3);                   // 0..7 inside the group
         const int g = lane >> 2, t = lane & 3;
-        // Tile row r covers k = 16r..16r+15 of the stage: 16-byte chunks 2r and 2r+1 of a 128-byte B row.  B row = column
-        // na = 16nt + g (and na + 8, 1024 bytes further on); the chunk index is XORed with (row & 7) = g for both.
+        // Tile (r, nt) of a stage: tile row r covers k = 16r..16r+15, i.e. 16-byte chunks 2r and 2r+1 of a 128-byte B
+        // row; B row = column 16nt + g (and + 8, 1024 bytes further on); the chunk index is XORed with (row & 7) = g.
         uint32_t raw_off[TPW], st_off[TPW][2];
         #pragma unroll
         for (int i = 0; i < TPW; ++i) {
-            const int r = r0 + i * RSTEP;
+            const int idx = wi + GW * i, r = idx / NT, nt = idx % NT;
             raw_off[i] = (r * NT + nt) * 8 * K;
             st_off[i][0] = (nt * 16 + g) * 128 + (((2 * r) ^ g) << 4) + 4 * t;
             st_off[i][1] = (nt * 16 + g) * 128 + (((2 * r + 1) ^ g) << 4) + 4 * t;
         }
         uint32_t bfull_addr = smem_u32(&b_full[0]);
         if constexpr (PAIR) asm volatile("mapa.shared::cluster.u32 %0, %0, 0;" : "+r"(bfull_addr));
-        int sr = 0, sb = 0;
+        int sr = grp % SM::SR, sb = grp % SM::SB;
         uint32_t par_r = 0, par_b = 1;                             // b_empty is waited from the second round on
-        for (int ks = 0; ks < ksteps; ++ks) {
+        for (int ks = grp; ks < ksteps; ks += 2) {
             if (!mbar_wait_sleep_warp(&r_full[sr], par_r)) { failed = true; break; }
             if (ks >= SM::SB && !mbar_wait_sleep_warp(&b_empty[sb], par_b)) { failed = true; break; }
             const uint32_t* raw = reinterpret_cast<const uint32_t*>(smem + SM::OFF_RAW + sr * SM::RAW_STAGE);
             uint8_t* bt = smem + SM::OFF_B + sb * SM::B_STAGE;
-            uint32_t st[TPW][8];
             #pragma unroll
-            for (int i = 0; i < TPW; ++i) lane_states<K>(raw + raw_off[i], lane, st[i]);
-            #pragma unroll
-            for (int i = 0; i < TPW; ++i) {
-                const half2 w0 = decode_pair<CB>(st[i][0], st[i][1]);      // rows 2t, 2t+1   col g
-                const half2 w1 = decode_pair<CB>(st[i][2], st[i][3]);      // rows 2t+8, +9   col g
-                const half2 w2 = decode_pair<CB>(st[i][4], st[i][5]);      // rows 2t, 2t+1   col g+8
-                const half2 w3 = decode_pair<CB>(st[i][6], st[i][7]);      // rows 2t+8, +9   col g+8
-                *reinterpret_cast<half2*>(bt + st_off[i][0]) = w0;
-                *reinterpret_cast<half2*>(bt + st_off[i][1]) = w1;
-                *reinterpret_cast<half2*>(bt + st_off[i][0] + 1024) = w2;
-                *reinterpret_cast<half2*>(bt + st_off[i][1] + 1024) = w3;
+            for (int h = 0; h < TPW; h += TB) {
+                uint32_t st[TB][8];
+                #pragma unroll
+                for (int i = 0; i < TB; ++i) lane_states<K>(raw + raw_off[h + i], lane, st[i]);
+                #pragma unroll
+                for (int i = 0; i < TB; ++i) {
+                    const half2 w0 = decode_pair<CB>(st[i][0], st[i][1]);      // rows 2t, 2t+1   col g
+                    const half2 w1 = decode_pair<CB>(st[i][2], st[i][3]);      // rows 2t+8, +9   col g
+                    const half2 w2 = decode_pair<CB>(st[i][4], st[i][5]);      // rows 2t, 2t+1   col g+8
+                    const half2 w3 = decode_pair<CB>(st[i][6], st[i][7]);      // rows 2t+8, +9   col g+8
+                    *reinterpret_cast<half2*>(bt + st_off[h + i][0]) = w0;
+                    *reinterpret_cast<half2*>(bt + st_off[h + i][1]) = w1;
+                    *reinterpret_cast<half2*>(bt + st_off[h + i][0] + 1024) = w2;
+                    *reinterpret_cast<half2*>(bt + st_off[h + i][1] + 1024) = w3;
+                }
             }
             // make the generic-proxy stores visible to the tensor core's reads, then tell the issuer
             fence_proxy_async();
@@ -382,8 +403,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                 asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bfull_addr + 8u * sb) : "memory");
                 mbar_arrive(&r_empty[sr]);
             }
-            if (++sr == SM::SR) { sr = 0; par_r ^= 1; }
-            if (++sb == SM::SB) { sb = 0; par_b ^= 1; }
+            sr += 2; if (sr >= SM::SR) { sr -= SM::SR; par_r ^= 1; }
+            sb += 2; if (sb >= SM::SB) { sb -= SM::SB; par_b ^= 1; }
         }
     }
 

@@ -121,9 +121,11 @@ class SyntheticModel:
                 b += L[n].trellis.numel() * 2
         return b
 
-    def step(self, ctx, ids, q_lens, cache_seqlens, block_table, max_q_len, advance=False, want_logits=False, stream=None):
+    def step(self, ctx, ids, q_lens, cache_seqlens, block_table, max_q_len, advance=False, want_logits=False, stream=None,
+             tokens_out=None):
         """ids int64 [rows], q_lens/cache_seqlens int32 [bsz], block_table int32 [bsz,pps] (device).  Returns tokens
-        (int64 [bsz]) and, if asked, fp32 logits [bsz, vocab]."""
+        (int64 [bsz]) and, if asked, fp32 logits [bsz, vocab].  `tokens_out` (int64 [bsz], device) makes the call
+        allocation-free once the scratch exists, which is what a CUDA-graph capture of the step needs."""
         L = lib()
         L.exl3_step_scratch_bytes.restype = C.c_size_t
         L.exl3_step_scratch_bytes.argtypes = [C.POINTER(Model), C.c_int, C.c_int]
@@ -131,7 +133,7 @@ class SyntheticModel:
         need = L.exl3_step_scratch_bytes(C.byref(self.struct), rows, bsz)
         if self._scratch is None or self._scratch.numel() < need:
             self._scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
-        tokens = torch.empty(bsz, dtype=torch.int64, device=self.device)
+        tokens = tokens_out if tokens_out is not None else torch.empty(bsz, dtype=torch.int64, device=self.device)
         logits = torch.empty(bsz, self.cfg["vocab"], dtype=torch.float32, device=self.device) if want_logits else None
         batch = Batch(ids.data_ptr(), q_lens.data_ptr(), cache_seqlens.data_ptr(), block_table.data_ptr(), bsz, rows,
                       max_q_len, block_table.shape[1], int(advance))

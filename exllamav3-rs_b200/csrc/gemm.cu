@@ -185,8 +185,10 @@ EncodeTiledFn get_encode_tiled()
     return fn;
 }
 
+constexpr int TC_MAX_SMALL_M = 16;          // row counts up to this stay on the mma.sync small-M kernel
+
 template <int K, int CB, int CTAS>
-cudaError_t launch_tc(const CUtensorMap* amap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc(const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
     constexpr int bytes = TcSmem<K, CTAS>::BYTES;
     static bool configured[64] = {};
@@ -208,34 +210,34 @@ cudaError_t launch_tc(const CUtensorMap* amap, const GemmTcParams& p, int slabs,
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, amap[0], amap[1], amap[2], p);
+    return cudaLaunchKernelEx(&cfg, kern, amap[0], amap[1], amap[2], rmap[0], rmap[1], rmap[2], p);
 }
 
 template <int K, int CB>
-cudaError_t launch_tc_ctas(bool pair, const CUtensorMap* amap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc_ctas(bool pair, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
-    return pair ? launch_tc<K, CB, 2>(amap, p, slabs, st) : launch_tc<K, CB, 1>(amap, p, slabs, st);
+    return pair ? launch_tc<K, CB, 2>(amap, rmap, p, slabs, st) : launch_tc<K, CB, 1>(amap, rmap, p, slabs, st);
 }
 
 template <int K>
-cudaError_t launch_tc_cb(int cb, bool pair, const CUtensorMap* amap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc_cb(int cb, bool pair, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
-    if (cb == 0) return launch_tc_ctas<K, 0>(pair, amap, p, slabs, st);
-    if (cb == 1) return launch_tc_ctas<K, 1>(pair, amap, p, slabs, st);
-    return launch_tc_ctas<K, 2>(pair, amap, p, slabs, st);
+    if (cb == 0) return launch_tc_ctas<K, 0>(pair, amap, rmap, p, slabs, st);
+    if (cb == 1) return launch_tc_ctas<K, 1>(pair, amap, rmap, p, slabs, st);
+    return launch_tc_ctas<K, 2>(pair, amap, rmap, p, slabs, st);
 }
 
-cudaError_t launch_tc_k(int K, int cb, bool pair, const CUtensorMap* amap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc_k(int K, int cb, bool pair, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
     switch (K) {
-        case 1: return launch_tc_cb<1>(cb, pair, amap, p, slabs, st);
-        case 2: return launch_tc_cb<2>(cb, pair, amap, p, slabs, st);
-        case 3: return launch_tc_cb<3>(cb, pair, amap, p, slabs, st);
-        case 4: return launch_tc_cb<4>(cb, pair, amap, p, slabs, st);
-        case 5: return launch_tc_cb<5>(cb, pair, amap, p, slabs, st);
-        case 6: return launch_tc_cb<6>(cb, pair, amap, p, slabs, st);
-        case 7: return launch_tc_cb<7>(cb, pair, amap, p, slabs, st);
-        default: return launch_tc_cb<8>(cb, pair, amap, p, slabs, st);
+        case 1: return launch_tc_cb<1>(cb, pair, amap, rmap, p, slabs, st);
+        case 2: return launch_tc_cb<2>(cb, pair, amap, rmap, p, slabs, st);
+        case 3: return launch_tc_cb<3>(cb, pair, amap, rmap, p, slabs, st);
+        case 4: return launch_tc_cb<4>(cb, pair, amap, rmap, p, slabs, st);
+        case 5: return launch_tc_cb<5>(cb, pair, amap, rmap, p, slabs, st);
+        case 6: return launch_tc_cb<6>(cb, pair, amap, rmap, p, slabs, st);
+        case 7: return launch_tc_cb<7>(cb, pair, amap, rmap, p, slabs, st);
+        default: return launch_tc_cb<8>(cb, pair, amap, rmap, p, slabs, st);
     }
 }
 
@@ -248,7 +250,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
     if (!enc) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled is not available from this driver");
     size_t off = 0;
     ProloguePlainArgs pa;
-    CUtensorMap amap[TC_MAX_SEG];
+    CUtensorMap amap[TC_MAX_SEG], rmap[TC_MAX_SEG];
     GemmTcParams p;
     memset(&p, 0, sizeof(p));
     int blocks = 0;
@@ -267,8 +269,17 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled failed");
+            // the trellis as a matrix of 64-bit words, one row per tile row (16 k); a CTA of a pair fetches a stage of its
+            // half slab (4 tile rows x 8 tiles x 32K bytes) as one box
+            cuuint64_t rdims[2] = {(cuuint64_t)(n[i] / 16) * 4 * K, (cuuint64_t)(k / 16)};
+            cuuint64_t rstrides[1] = {(cuuint64_t)(n[i] / 16) * 32 * K};
+            cuuint32_t rbox[2] = {(cuuint32_t)(TC_BN / 2 / 16) * 4 * K, (cuuint32_t)(TC_BK / 16)};
+            r = enc(&rmap[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(trellis[i]), rdims, rstrides, rbox, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled failed for the trellis");
         } else {
-            pa.a_had[i] = pa.a_had[j]; pa.suh[i] = pa.suh[j]; amap[i] = amap[j];
+            pa.a_had[i] = pa.a_had[j]; pa.suh[i] = pa.suh[j]; amap[i] = amap[j]; rmap[i] = rmap[j];
         }
         p.trellis[i] = (const uint32_t*)trellis[j]; p.C[i] = C[j]; p.svh[i] = svh[j]; p.n[i] = n[j];
         p.blk_end[i] = i < nseg ? blocks : 0x7fffffff;
@@ -276,7 +287,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
     gemm_prologue_plain_kernel<<<dim3(m, nseg), 256, 0, st>>>(A, pa, k);
     ctx->launches++;
     p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
-    cudaError_t e = launch_tc_k(K, cb, ctx->use_pair != 0, amap, p, blocks, st);
+    cudaError_t e = launch_tc_k(K, cb, ctx->use_pair != 0, amap, rmap, p, blocks, st);
     ctx->launches++;
     if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
     return EXL3_OK;
@@ -302,10 +313,12 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
     const int NB = n / 128, NST = k / 128;
     EXL3_REQUIRE(NB <= ctx->n_counters, "exl3_gemm: n too large for the context's counters");
 
-    // Large M with n % 256 == 0: tcgen05 kernel over 256-row blocks (the last block may be partial: its rows past m are
-    // zero-filled by TMA, and a block with at most 128 valid rows runs a single accumulator).
+    // More than TC_MAX_SMALL_M rows with n % 256 == 0: tcgen05 kernel over 512-row blocks per CTA pair (the last block may
+    // be partial: its rows past m are zero-filled by TMA, and a block with at most 256 valid rows runs a single MMA per K
+    // step).  Measured on 5120 x 17408: the small-M kernel takes 55 us at m = 1, 72 us at m = 16 and 209 us at m = 64,
+    // the tcgen05 kernel about 60 us for any m <= 256.
     int tc_rows = 0;
-    if (m > 128 && n % TC_BN == 0 && ctx->use_tc) {
+    if (m > TC_MAX_SMALL_M && n % TC_BN == 0 && ctx->use_tc) {
         tc_rows = m;
         const half* suh1 = (const half*)suh; const half* svh1 = (const half*)svh;
         int rc = gemm_tc_rows(ctx, st, (const half*)A, 1, &trellis, &C, &suh1, &svh1, &n, tc_rows, k, K, c_fp32, cb);
@@ -349,7 +362,7 @@ extern "C" int exl3_gemm_fanout(exl3_ctx* ctx, exl3_stream stream, const void* A
                w[i]->k % 128 == 0 && w[i]->K >= 1 && w[i]->K <= 8 && aligned16(w[i]->trellis) && aligned16(C[i]) &&
                aligned16(w[i]->suh) && aligned16(w[i]->svh) && (w[i]->suh != nullptr) == (w[0]->suh != nullptr);
     }
-    if (count > 1 && same && m > 128 && ctx->use_tc && aligned16(A)) {
+    if (count > 1 && same && m > TC_MAX_SMALL_M && ctx->use_tc && aligned16(A)) {
         const void* tr[TC_MAX_SEG]; const half* suh[TC_MAX_SEG]; const half* svh[TC_MAX_SEG]; int n[TC_MAX_SEG];
         for (int i = 0; i < count; ++i) { tr[i] = w[i]->trellis; suh[i] = (const half*)w[i]->suh; svh[i] = (const half*)w[i]->svh; n[i] = w[i]->n; }
         return gemm_tc_rows(ctx, (cudaStream_t)stream, (const half*)A, count, tr, C, suh, svh, n, m, w[0]->k, w[0]->K, c_fp32, w[0]->cb);

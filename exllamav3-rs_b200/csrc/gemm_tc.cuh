@@ -10,8 +10,8 @@
 //             of the slab and holds the accumulators of its own 2 x 128 rows; the leader CTA issues
 //             tcgen05.mma.cta_group::2 (M = 256 across the pair), which reads each CTA's half of B from that CTA's shared
 //             memory.  The decode work per multiply is halved, which is what bounds the CTAS = 1 form.
-// K step 64.  Roles: warp 0 = producer (TMA + bulk copies), warp 1 = MMA issuer (leader CTA only) and TMEM owner,
-// warps 2..17 = decoders, then epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+// K step 64.  Roles: warp 0 = activation producer (TMA), warp 1 = MMA issuer (leader CTA only) and TMEM owner,
+// warps 2..17 = decoders, then epilogue (warp w reads TMEM lanes 32*(w%4)..+31), warp 18 = trellis-code producer.
 // Every mbarrier wait is bounded; a wait that runs out makes the CTA skip to the tear-down (TMEM is always freed) and
 // sets the status word.
 #pragma once
@@ -24,7 +24,7 @@ namespace exl3 {
 
 constexpr int TC_BM = 256, TC_BN = 256, TC_BK = 64;     // rows per CTA, columns per slab, K step
 constexpr int TC_DECODERS = 16;                          // decoder warps
-constexpr int TC_THREADS = (2 + TC_DECODERS) * 32;       // 18 warps
+constexpr int TC_THREADS = (3 + TC_DECODERS) * 32;       // 19 warps: two producers, the MMA issuer, the decoders
 constexpr int TC_MAX_SEG = 3;                            // weight tensors that may share one launch
 constexpr int TC_A_TILE = 128 * TC_BK * 2;               // one 128-row activation tile of a stage: 16 KB
 constexpr int TC_A_STAGE = 2 * TC_A_TILE;                // 32 KB
@@ -46,7 +46,7 @@ template <int K, int CTAS> struct TcSmem {
     static constexpr int OFF_RAW = OFF_B + SB * B_STAGE;
     static constexpr int OFF_SVH = OFF_RAW + SR * RAW_STAGE;
     static constexpr int OFF_BAR = OFF_SVH + TC_BN * 2;
-    static constexpr int N_BARS = 2 * SA + 2 * SR + 2 * SB + 2;
+    static constexpr int N_BARS = 4 * SA + 2 * SR + 2 * SB + 2;      // the A ring has 2 * SA slots for one-tile blocks
     static constexpr int OFF_TMEM = OFF_BAR + N_BARS * 8;
     static constexpr int BYTES = OFF_TMEM + 16 + 1024;      // + slack to align the base to 1024 bytes
 };
@@ -128,6 +128,18 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
     }
     return false;
 }
+// the same with plain polls: for the one thread whose wake-up latency is on the critical path
+__device__ __forceinline__ bool mbar_spin_cluster(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 24))
+{
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
 // arrive on the barrier at this offset in both CTAs of the pair when the MMAs issued so far have completed
 __device__ __forceinline__ void tc_commit_pair(uint64_t* bar)
 {
@@ -205,7 +217,10 @@ __device__ __forceinline__ void fwht32(float (&v)[32])
 template <int K, int CB, int CTAS>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap amap0,
                                                                const __grid_constant__ CUtensorMap amap1,
-                                                               const __grid_constant__ CUtensorMap amap2, const GemmTcParams p)
+                                                               const __grid_constant__ CUtensorMap amap2,
+                                                               const __grid_constant__ CUtensorMap rmap0,
+                                                               const __grid_constant__ CUtensorMap rmap1,
+                                                               const __grid_constant__ CUtensorMap rmap2, const GemmTcParams p)
 {
     using SM = TcSmem<K, CTAS>;
     constexpr bool PAIR = CTAS == 2;
@@ -215,8 +230,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     // pointer is in shared memory (32-bit addresses, ld/st.shared) instead of falling back to generic accesses
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
-    uint64_t* a_full = bars;                  uint64_t* a_empty = a_full + SM::SA;
-    uint64_t* r_full = a_empty + SM::SA;      uint64_t* r_empty = r_full + SM::SR;
+    uint64_t* a_full = bars;                  uint64_t* a_empty = a_full + 2 * SM::SA;
+    uint64_t* r_full = a_empty + 2 * SM::SA;      uint64_t* r_empty = r_full + SM::SR;
     uint64_t* b_full = r_empty + SM::SR;      uint64_t* b_empty = b_full + SM::SB;
     uint64_t* acc_full = b_empty + SM::SB;    uint64_t* drain = acc_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::OFF_TMEM);
@@ -231,6 +246,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     const int m0 = blockIdx.y * (TC_BM * CTAS);
     const int row_t0 = m0 + rank * 128, row_t1 = row_t0 + 128 * CTAS;    // first rows of this CTA's two M tiles
     const CUtensorMap* amap = seg == 0 ? &amap0 : (seg == 1 ? &amap1 : &amap2);
+    const CUtensorMap* rmap = seg == 0 ? &rmap0 : (seg == 1 ? &rmap1 : &rmap2);       // trellis as [k/16][row of uint64]
     // (selected with compares: indexing the parameter arrays with `seg` would put a copy of them in local memory)
     const uint32_t* trellis = seg == 0 ? p.trellis[0] : (seg == 1 ? p.trellis[1] : p.trellis[2]);
     const half* svh = seg == 0 ? p.svh[0] : (seg == 1 ? p.svh[1] : p.svh[2]);
@@ -239,10 +255,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     const int tiles_n = n >> 4;
     const int ksteps = p.k / TC_BK;
     const bool two_tiles = p.m - m0 > 128 * CTAS;          // otherwise the second M tile (of both CTAs) has no valid row
+    // The activation ring holds SA steps of two tiles, or twice as many steps of one tile: a block with one tile spends half
+    // the tensor-core time per step, and the TMA round trip (about 2000 cycles) must still be covered by the steps in flight.
+    const int a_slots = two_tiles ? SM::SA : 2 * SM::SA;
+    const uint32_t a_slot_bytes = two_tiles ? TC_A_STAGE : TC_A_TILE;
 
     if (tid == 0) {
         s_failed = 0;
-        for (int i = 0; i < SM::SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < 2 * SM::SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
         for (int i = 0; i < SM::SR; ++i) { mbar_init(&r_full[i], 1); mbar_init(&r_empty[i], TC_DECODERS / 2); }
         for (int i = 0; i < SM::SB; ++i) { mbar_init(&b_full[i], TC_DECODERS / 2 * CTAS); mbar_init(&b_empty[i], 1); }
         mbar_init(acc_full, 1);
@@ -266,29 +286,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
 
+    // The two producers are single threads on different schedulers (warps 0 and 18).  One thread doing both jobs took
+    // about 1000 cycles per K step (some fifty dependent instructions, each arbitrated against four decoder warps) and
+    // was what the tensor core ended up waiting for.
     if (warp == 0) {
-        // ===== producer: activations by TMA, trellis codes by bulk copies
+        // ===== activation producer: one or two tiled TMA loads per K step
         if (lane == 0) {
             const uint32_t a_bytes = (two_tiles ? 2u : 1u) * TC_A_TILE * CTAS;     // what lands on the leader's barrier
-            constexpr int AHEAD = SM::SR > SM::SA ? SM::SR - SM::SA : 0;          // the code ring runs this far ahead of A
-            auto load_raw = [&](int kr) {
-                const int sr = kr % SM::SR;
-                mbar_expect_tx(&r_full[sr], SM::RAW_STAGE);
-                #pragma unroll
-                for (int r = 0; r < TC_BK / 16; ++r)
-                    bulk_g2s(smem + SM::OFF_RAW + sr * SM::RAW_STAGE + r * SM::RAW_ROW,
-                             trellis + ((size_t)(kr * (TC_BK / 16) + r) * tiles_n + (nd0 >> 4)) * 8 * K, SM::RAW_ROW, &r_full[sr]);
-            };
-            for (int kr = 0; kr < AHEAD && kr < ksteps; ++kr) load_raw(kr);
+            int sa = 0;
+            uint32_t par_ae = 1;                                  // a_empty is waited from the second round on
             for (int ks = 0; ks < ksteps; ++ks) {
-                const int kr = ks + AHEAD;
-                if (kr < ksteps) {
-                    if (kr >= SM::SR && !mbar_wait_sleep(&r_empty[kr % SM::SR], ((kr / SM::SR) - 1) & 1)) { failed = true; break; }
-                    load_raw(kr);
-                }
-                const int sa = ks % SM::SA;
-                if (ks >= SM::SA && !mbar_wait_sleep(&a_empty[sa], ((ks / SM::SA) - 1) & 1)) { failed = true; break; }
-                uint8_t* at = smem + SM::OFF_A + sa * TC_A_STAGE;
+                if (ks >= a_slots && !mbar_wait(&a_empty[sa], par_ae)) { failed = true; break; }
+                uint8_t* at = smem + SM::OFF_A + sa * a_slot_bytes;
                 if constexpr (PAIR) {
                     if (rank == 0) mbar_expect_tx(&a_full[sa], a_bytes);
                     tma_load_2d_pair(at, amap, ks * TC_BK, row_t0, &a_full[sa]);
@@ -298,6 +307,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                     tma_load_2d(at, amap, ks * TC_BK, row_t0, &a_full[sa]);
                     if (two_tiles) tma_load_2d(at + TC_A_TILE, amap, ks * TC_BK, row_t1, &a_full[sa]);
                 }
+                if (++sa == a_slots) { sa = 0; par_ae ^= 1; }
+            }
+        }
+    } else if (warp == 2 + TC_DECODERS) {
+        // ===== code producer: a stage of trellis codes = 4 tile rows x RAW_ROW bytes.  The pair form fetches it with one
+        // tiled TMA load (box of 4 rows), the one-CTA form with four bulk copies issued by four lanes at once.
+        const size_t row_words = (size_t)tiles_n * 8 * K;                      // one tile row of the whole tensor
+        const uint32_t* src_lane = trellis + (size_t)(lane & 3) * row_words + (size_t)(nd0 >> 4) * 8 * K;
+        const uint32_t dst_lane = smem_u32(smem + SM::OFF_RAW) + (lane & 3) * SM::RAW_ROW;
+        if (PAIR ? lane == 0 : lane < TC_BK / 16) {
+            int sr = 0;
+            uint32_t par_re = 1;                                  // r_empty is waited from the second round on
+            for (int kr = 0; kr < ksteps; ++kr) {
+                if (kr >= SM::SR && !mbar_wait(&r_empty[sr], par_re)) { failed = true; break; }
+                if (lane == 0) mbar_expect_tx(&r_full[sr], SM::RAW_STAGE);
+                if constexpr (PAIR) {
+                    tma_load_2d(smem + SM::OFF_RAW + sr * SM::RAW_STAGE, rmap, (nd0 >> 4) * 4 * K, kr * (TC_BK / 16), &r_full[sr]);
+                } else {
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(dst_lane + sr * SM::RAW_STAGE), "l"(src_lane + (size_t)kr * (TC_BK / 16) * row_words),
+                                   "r"((uint32_t)SM::RAW_ROW), "r"(smem_u32(&r_full[sr])) : "memory");
+                }
+                if (++sr == SM::SR) { sr = 0; par_re ^= 1; }
             }
         }
     } else if (warp == 1) {
@@ -312,11 +344,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             int sa = 0, sb = 0;
             uint32_t par_a = 0, par_b = 0;
             for (int ks = 0; ks < ksteps; ++ks) {
-                const bool ok = PAIR ? (mbar_wait_cluster(&a_full[sa], par_a) && mbar_wait_cluster(&b_full[sb], par_b))
-                                     : (mbar_wait_sleep(&a_full[sa], par_a) && mbar_wait_sleep(&b_full[sb], par_b));
+                bool ok = PAIR ? mbar_spin_cluster(&a_full[sa], par_a) : mbar_wait(&a_full[sa], par_a);
+                ok = ok && (PAIR ? mbar_spin_cluster(&b_full[sb], par_b) : mbar_wait(&b_full[sb], par_b));
                 if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
                 tc_fence_after();
-                const uint32_t a0 = a_lo + sa * (TC_A_STAGE >> 4), b0 = b_lo + sb * (SM::B_STAGE >> 4);
+                const uint32_t a0 = a_lo + sa * (a_slot_bytes >> 4), b0 = b_lo + sb * (SM::B_STAGE >> 4);
                 if (leader) {
                     #pragma unroll
                     for (int kk = 0; kk < TC_BK / 16; ++kk) {
@@ -334,7 +366,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                     else { tc_commit(&a_empty[sa]); tc_commit(&b_empty[sb]); }
                 }
                 __syncwarp();
-                if (++sa == SM::SA) { sa = 0; par_a ^= 1; }
+                if (++sa == a_slots) { sa = 0; par_a ^= 1; }
                 if (++sb == SM::SB) { sb = 0; par_b ^= 1; }
             }
             if (leader) {
@@ -348,7 +380,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             }
             __syncwarp();
         }
-    } else {
+    } else if (warp < 2 + TC_DECODERS) {
         // ===== decoders: raw codes -> fp16 weights in the K-major swizzled B tile.
         // The 16 warps form two groups of 8 (two warps per scheduler each) that take alternate K steps: while one group
         // waits on its barriers, fences and arrives, the other decodes, so the schedulers stay busy (with all 16 warps
@@ -409,7 +441,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     }
 
     // ===== epilogue (warps 2..17): TMEM -> registers -> output transform -> global.  Each CTA stores its own rows.
-    if (warp >= 2 && !failed) {
+    if (warp >= 2 && warp < 2 + TC_DECODERS && !failed) {
         if (!mbar_wait_warp(acc_full, 0)) failed = true;
         if (!failed) {
             tc_fence_after();

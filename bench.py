@@ -289,7 +289,11 @@ def run_ours(args):
         kv_bytes = float((ctx_lens + q_lens).sum()) * CFG["nkv"] * CFG["hd"] * 2 * 2 * CFG["n_layers"]
         step_bytes = model.weight_bytes() + kv_bytes
         roof = {"bound": "tensor", "kernel": "exl3_gemm (gate_proj 5120x17408, M=%d)" % rows, "achieved": ach,
-                "peak": tf_peak, "unit": "TFLOP/s", "frac": ach / tf_peak, "traffic": None, "peak_source": which,
+                "peak": tf_peak, "unit": "TFLOP/s", "frac": ach / tf_peak,
+                # DRAM bytes of one gemm_tc_kernel launch at this shape (dram__bytes_read.sum + dram__bytes_write.sum of the
+                # ncu capture summarised in profiles/gemm_tc_kernel_m1052_k5120_n17408_4bpw.md): the 44.6 MB of codes once,
+                # the transformed activations, and the part of the output that leaves L2
+                "traffic": 57940224 + 10788096, "peak_source": which,
                 "launches_per_op": (ctx.launch_count() - g0) // len(lins), "op_ms": t_op * 1e3,
                 "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9, "step_hbm_frac": step_bytes / (ms_step * 1e-3) / 1e9 / hbm_peak}
 

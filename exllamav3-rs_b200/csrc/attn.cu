@@ -1,4 +1,5 @@
 // exl3_bighead_attn_paged / exl3_bighead_attn_paged_q: planning, launch and split-KV combine.
+#include <algorithm>
 #include "attn_paged.cuh"
 #include "attn_tc.cuh"
 
@@ -198,7 +199,10 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     const int rows_per_cta = decode_shape ? 16 : (use_tc ? ATC_CTA_ROWS : 64);
     const int rb_max = (max_rows + rows_per_cta - 1) / rows_per_cta;
     // resident CTAs per SM over all kv heads: about 3 for the mma.sync kernels, 1 for the tcgen05 kernel (all of TMEM)
-    const int grid_x = (ctx->num_sms * (use_tc ? 1 : 3) + p.nkv - 1) / p.nkv;
+    // (rounded down: one CTA more than fits would run alone in a second wave after all the others have finished)
+    const int grid_x = std::max(1, ctx->num_sms * (use_tc ? 1 : 3) / p.nkv);
+    // two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs a 133 KB
+    // partial per kv head written and read back (4 per slot was measured 20 % slower, 1 per slot 2 % slower)
     const int target_items = grid_x * 2;
     const int max_items = target_items + p.bsz * rb_max + 1;
 

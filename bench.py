@@ -98,27 +98,34 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
-def cpu_sample(steps=10, warmup=1):
-    """Bounded CPU sample of the same step: ONE layer of the model (full widths) over 8 decode rows with contexts in
-    [512, 2048], composed from the oracle's ops; a whole step is 64 such layers plus the head, so tokens/s is
-    rows / (64 * t_layer).  Returns (tokens_per_s, seconds_per_layer, threads)."""
+CPU_SAMPLE = ("one layer of the 64 (full widths, 4 bpw) over a 1/16-scale cut of a GPU's shard: 2 decode sequences + one "
+              "prefill chunk of 64 rows (66 packed rows, 3 sequences), contexts in [512, 2048], composed from oracle/ ops; "
+              "step time extrapolated as 64 x layer time")
+
+
+def cpu_sample(steps=3, warmup=1):
+    """Bounded CPU sample of the same step: ONE layer of the model (full widths) over 2 decode sequences and one prefill
+    chunk of 64 rows (the shard's 28 : 1024 row mix at 1/16 scale) with contexts in [512, 2048], composed from the
+    oracle's ops; a whole step is 64 such layers plus the head, so tokens/s is rows / (64 * t_layer).
+    Returns (tokens_per_s, seconds_per_layer, threads)."""
     from oracle import oracle as O
     from oracle import oracle_model
     r = np.random.default_rng(7)
     c = CFG
-    rows = 8
+    q_lens = np.array([1, 1, 64], np.int32)
+    nseq, rows = len(q_lens), int(q_lens.sum())
 
     def lin(k, n):
         return dict(trellis=r.integers(-32768, 32768, size=(k // 16, n // 16, 16 * c["K"]), dtype=np.int16),
                     suh=(r.integers(0, 2, k) * 2 - 1).astype(np.float16),
                     svh=((r.integers(0, 2, n) * 2 - 1) / np.sqrt(k)).astype(np.float16), K=c["K"], cb=c["cb"])
 
-    ctx = r.integers(512, 2049, rows).astype(np.int32)
-    need = (ctx + 1 + 255) // 256
+    ctx = r.integers(512, 2049, nseq).astype(np.int32)
+    need = (ctx + q_lens + 255) // 256
     pages = int(need.sum()) + 1
-    bt = np.zeros((rows, int(need.max())), np.int32)
+    bt = np.zeros((nseq, int(need.max())), np.int32)
     o = 0
-    for b in range(rows):
+    for b in range(nseq):
         bt[b, :need[b]] = np.arange(o, o + need[b]); o += need[b]
     hid, nq, nkv, hd = c["hidden"], c["nq"], c["nkv"], c["hd"]
     layer = dict(q_proj=lin(hid, nq * hd), k_proj=lin(hid, nkv * hd), v_proj=lin(hid, nkv * hd), o_proj=lin(nq * hd, hid),
@@ -132,7 +139,6 @@ def cpu_sample(steps=10, warmup=1):
              final_norm=np.ones(hid, np.float16), inv_freq=(1.0 / (1e6 ** (np.arange(0, hd, 2) / hd))).astype(np.float32),
              lm_head=dict(lin(hid, small_vocab)), layers=[layer])
     ids = r.integers(0, small_vocab, rows).astype(np.int64)
-    q_lens = np.ones(rows, np.int32)
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
@@ -147,9 +153,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    tps, t_layer, threads = cpu_sample(steps=max(1, args.steps), warmup=min(args.warmup, 1))
-    sample = ("one layer of the 64 (full widths, 4 bpw) over 8 decode rows, contexts in [512, 2048], composed from "
-              "oracle/ ops; step time extrapolated as 64 x layer time")
+    tps, t_layer, threads = cpu_sample(steps=max(1, min(args.steps, 5)), warmup=min(args.warmup, 1))
+    sample = CPU_SAMPLE
     line = {"impl": "reference", "metric": "ragged decode-step tokens/s", "value": tps, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 64e3 * t_layer,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
@@ -301,8 +306,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         tps, t_layer, threads = cpu_sample()
         cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-               "sample": "one layer of the 64 (full widths) over 8 decode rows, contexts in [512, 2048], oracle/ ops; "
-                         "step time extrapolated as 64 x layer time (%.2f s per layer)" % t_layer}
+               "sample": CPU_SAMPLE + " (%.2f s per layer)" % t_layer}
     if rank == 0:
         line = {"metric": "ragged decode-step tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,

@@ -200,7 +200,13 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     const int rb_max = (max_rows + rows_per_cta - 1) / rows_per_cta;
     // resident CTAs per SM over all kv heads: about 3 for the mma.sync kernels, 1 for the tcgen05 kernel (all of TMEM)
     // (rounded down: one CTA more than fits would run alone in a second wave after all the others have finished)
-    const int grid_x = std::max(1, ctx->num_sms * (use_tc ? 1 : 3) / p.nkv);
+    int per_sm = 1;
+    if (!use_tc) {
+        // CTAs of the mma.sync kernel that fit on an SM (bounded by shared memory: stages x 34.8 KB for fp16 pools)
+        const size_t smem = quant ? AttnSmem<128, true>::BYTES : AttnSmem<128, false>::BYTES;
+        per_sm = std::max(1, std::min(3, (int)((227 * 1024) / (smem + 1024))));
+    }
+    const int grid_x = std::max(1, ctx->num_sms * per_sm / p.nkv);
     // two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs a 133 KB
     // partial per kv head written and read back (4 per slot was measured 20 % slower, 1 per slot 2 % slower)
     const int target_items = grid_x * 2;

@@ -224,3 +224,20 @@ def test_attention_rejects_unsupported(ctx):
     sl = torch.zeros(1, dtype=torch.int32, device="cuda")
     with pytest.raises(exl3b200.Exl3Error):
         ctx.bighead_attn_paged(q, None, None, kc, kc.clone(), bt, sl, torch.zeros_like(q))
+
+
+@pytest.mark.parametrize("q_len,ctx_len,nq,nkv", [(64, 1500, 16, 2), (9, 600, 8, 8)])
+def test_attention_reference_check_shapes(ctx, ref, q_len, ctx_len, nq, nkv):
+    """the two head_dim-128 cases of the reference's own differential check (src/bin/attn_check.rs:438-439): one
+    sequence, a context that is no multiple of the page, GQA ratios 8 and 1"""
+    c = _make_case(5000 + q_len, [ctx_len], q_len, nq, nkv)
+    got, _, _ = _run_fp16(ctx, c)
+    want, _, _ = _oracle_fp16(c)
+    assert np.isfinite(got).all()
+    e_or = _close(got, want, TOL_FP16, 2)
+    e_ref = e_rr = 0.0
+    if ref is not None:
+        rgot = _ref_fp16(ref, c, 1)
+        e_ref = _close(got, rgot, TOL_FP16, 2)
+        e_rr = _close(rgot, want, TOL_FP16, 2)
+    assert e_or <= max(1.0, 1.1 * e_rr) and e_ref <= 1.25, (e_or, e_ref, e_rr)

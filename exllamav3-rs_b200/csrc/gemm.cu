@@ -185,7 +185,7 @@ EncodeTiledFn get_encode_tiled()
     return fn;
 }
 
-constexpr int TC_MAX_SMALL_M = 16;          // row counts up to this stay on the mma.sync small-M kernel
+constexpr int TC_MAX_SMALL_M = 0;           // row counts up to this stay on the mma.sync small-M kernel (0: none do)
 
 template <int K, int CB, int CTAS>
 cudaError_t launch_tc(const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
@@ -313,10 +313,11 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
     const int NB = n / 128, NST = k / 128;
     EXL3_REQUIRE(NB <= ctx->n_counters, "exl3_gemm: n too large for the context's counters");
 
-    // More than TC_MAX_SMALL_M rows with n % 256 == 0: tcgen05 kernel over 512-row blocks per CTA pair (the last block may
-    // be partial: its rows past m are zero-filled by TMA, and a block with at most 256 valid rows runs a single MMA per K
-    // step).  Measured on 5120 x 17408: the small-M kernel takes 55 us at m = 1, 72 us at m = 16 and 209 us at m = 64,
-    // the tcgen05 kernel about 60 us for any m <= 256.
+    // n % 256 == 0: tcgen05 kernel over 512-row blocks per CTA pair (the last block may be partial: its rows past m are
+    // zero-filled by TMA, and a block with at most 256 valid rows runs a single MMA per K step).  Measured on 5120 x 17408
+    // at 4 bpw: the tcgen05 kernel takes 47-52 us for any m <= 256 (its decoders set the pace), the mma.sync small-M
+    // kernel 54 us at m = 1, 73 us at m = 16 and 209 us at m = 64, so every row count goes to the former.  The small-M
+    // kernel serves the shapes with n % 256 == 128 (e.g. a 151936-column head), exl3_gemm_noalloc and EXL3_B200_NO_TC.
     int tc_rows = 0;
     if (m > TC_MAX_SMALL_M && n % TC_BN == 0 && ctx->use_tc) {
         tc_rows = m;

@@ -152,15 +152,22 @@ def _gemm_case(ctx, ref, m, k, n, K, cb, c_fp32, seed, check_oracle=True):
     return got
 
 
+@pytest.fixture(params=["tcgen05", "small-m"])
+def gemm_ctx(request):
+    """Both GEMM kernels behind exl3_gemm: the default context (tcgen05 kernel whenever n % 256 == 0) and one with that
+    path switched off (mma.sync small-M kernel in 64-row passes)."""
+    return request.getfixturevalue("ctx" if request.param == "tcgen05" else "ctx_small_only")
+
+
 @pytest.mark.parametrize("cb", [0, 1, 2])
 @pytest.mark.parametrize("K", [1, 2, 3, 4, 5, 6, 7, 8])
-def test_gemm_formats(ctx, ref, K, cb):
-    _gemm_case(ctx, ref, 5, 1024, 1024, K, cb, False, 400 + K * 3 + cb)
+def test_gemm_formats(gemm_ctx, ref, K, cb):
+    _gemm_case(gemm_ctx, ref, 5, 1024, 1024, K, cb, False, 400 + K * 3 + cb)
 
 
 @pytest.mark.parametrize("m", [1, 2, 8, 16, 17, 32, 33, 64, 65, 100, 150])
-def test_gemm_row_counts(ctx, ref, m):
-    _gemm_case(ctx, ref, m, 2048, 1024, 4, 1, False, 500 + m)
+def test_gemm_row_counts(gemm_ctx, ref, m):
+    _gemm_case(gemm_ctx, ref, m, 2048, 1024, 4, 1, False, 500 + m)
 
 
 @pytest.mark.parametrize("c_fp32", [False, True])
@@ -171,13 +178,14 @@ def test_gemm_shapes(ctx, ref, k, n, c_fp32):
 
 @pytest.mark.parametrize("K", [2, 3, 4, 5, 8])
 @pytest.mark.parametrize("m", [1, 4, 16, 64])
-def test_gemm_sweep_shape(ctx, ref, m, K):
+def test_gemm_sweep_shape(gemm_ctx, ref, m, K):
     """K=5120, N=17408 sweep of the benchmark configs at the small-M sizes, against oracle and reference op."""
-    _gemm_case(ctx, ref, m, 5120, 17408, K, 1, False, 700 + m + K, check_oracle=(m <= 16))
+    _gemm_case(gemm_ctx, ref, m, 5120, 17408, K, 1, False, 700 + m + K, check_oracle=(m <= 16))
 
 
-def test_gemm_deterministic_and_reusable(ctx):
+def test_gemm_deterministic_and_reusable(gemm_ctx):
     """Two calls in a row give identical bits (fixed-order split-K reduction, counters return to zero)."""
+    ctx = gemm_ctx
     torch = _torch()
     r = H.rng(9)
     m, k, n, K = 3, 5120, 1024, 4

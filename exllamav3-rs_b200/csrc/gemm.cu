@@ -260,7 +260,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
             pa.a_had[i] = (half*)exl3_ws_take(ctx, &off, (size_t)m * k * 2);
             if (!pa.a_had[i]) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the activations");
             pa.suh[i] = suh[i];
-            blocks += n[i] / TC_BN;
+            blocks += (n[i] + TC_BN - 1) / TC_BN;          // a trailing 128-column half slab counts (CTA pairs only)
             cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
             cuuint64_t strides[1] = {(cuuint64_t)k * 2};
             cuuint32_t box[2] = {(cuuint32_t)TC_BK, 128u};
@@ -313,13 +313,14 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
     const int NB = n / 128, NST = k / 128;
     EXL3_REQUIRE(NB <= ctx->n_counters, "exl3_gemm: n too large for the context's counters");
 
-    // n % 256 == 0: tcgen05 kernel over 512-row blocks per CTA pair (the last block may be partial: its rows past m are
+    // tcgen05 kernel over 512-row blocks per CTA pair and 256-column slabs (with CTA pairs a last slab of 128 columns is
+    // allowed: its missing half reads zero-filled codes and is never stored) (the last block may be partial: its rows past m are
     // zero-filled by TMA, and a block with at most 256 valid rows runs a single MMA per K step).  Measured on 5120 x 17408
     // at 4 bpw: the tcgen05 kernel takes 47-52 us for any m <= 256 (its decoders set the pace), the mma.sync small-M
     // kernel 54 us at m = 1, 73 us at m = 16 and 209 us at m = 64, so every row count goes to the former.  The small-M
-    // kernel serves the shapes with n % 256 == 128 (e.g. a 151936-column head), exl3_gemm_noalloc and EXL3_B200_NO_TC.
+    // kernel serves exl3_gemm_noalloc, EXL3_B200_NO_TC, and n % 256 == 128 under EXL3_B200_NO_PAIR.
     int tc_rows = 0;
-    if (m > TC_MAX_SMALL_M && n % TC_BN == 0 && ctx->use_tc) {
+    if (m > TC_MAX_SMALL_M && (n % TC_BN == 0 || ctx->use_pair) && ctx->use_tc) {
         tc_rows = m;
         const half* suh1 = (const half*)suh; const half* svh1 = (const half*)svh;
         int rc = gemm_tc_rows(ctx, st, (const half*)A, 1, &trellis, &C, &suh1, &svh1, &n, tc_rows, k, K, c_fp32, cb);

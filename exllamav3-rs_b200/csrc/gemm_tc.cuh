@@ -278,7 +278,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         }
     }
-    if (svh) for (int i = tid; i < TC_BN; i += TC_THREADS) reinterpret_cast<half*>(smem + SM::OFF_SVH)[i] = svh[n0 + i];
+    // (the last slab of a tensor with n % 256 == 128 has one valid half: its other half decodes zero-filled codes into
+    // columns that are never stored)
+    if (svh) for (int i = tid; i < TC_BN; i += TC_THREADS)
+        reinterpret_cast<half*>(smem + SM::OFF_SVH)[i] = n0 + i < n ? svh[n0 + i] : __float2half(0.f);
     tc_fence_before();
     __syncthreads();
     if constexpr (PAIR) cluster_sync_all();               // the other CTA's barriers are initialised before anything arrives
@@ -448,7 +451,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             // TMEM lane quadrant q; each of the four warps of a quadrant takes one (M tile, 128-column half) pair
             const int q = warp & 3, mt = (warp - 2) >> 3, sel = ((warp - 2) >> 2) & 1;
             const half* svh_s = reinterpret_cast<const half*>(smem + SM::OFF_SVH) + sel * 128;
-            if (mt == 0 || two_tiles) {
+            if ((mt == 0 || two_tiles) && n0 + sel * 128 < n) {
                 const int row = (mt ? row_t1 : row_t0) + q * 32 + lane;
                 const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + mt * TC_BN + sel * 128;
                 // The 128-point transform of a row is split so that a thread never holds more than 32 accumulators:

@@ -399,10 +399,22 @@ def run_ops(args):
         kn = (torch.randn(bsz, q_len, nkv, hd, device="cuda", generator=g) * 0.5).to(torch.float16)
         out = torch.empty_like(q)
         dbt, dsl = torch.from_numpy(bt).cuda(), torch.from_numpy(ctx_lens).cuda()
-        t = time_calls([lambda st: ctx.bighead_attn_paged(q, kn, kn, kc, vc, dbt, dsl, out, stream=st)], args.reps)
-        byts = float((ctx_lens + q_len).sum()) * nkv * hd * 2 * 2
+        if args.kv_bits:
+            # quantised pools with random codes and small positive scales (timing only: every bit pattern is a valid code)
+            del kc, vc
+            groups, bits = nkv * hd // 32, args.kv_bits
+            qk = torch.randint(-2 ** 31, 2 ** 31 - 1, (pages, 256, groups * bits), dtype=torch.int32, device="cuda", generator=g)
+            qv = torch.randint(-2 ** 31, 2 ** 31 - 1, (pages, 256, groups * bits), dtype=torch.int32, device="cuda", generator=g)
+            sk = (torch.rand(pages, 256, groups, device="cuda", generator=g) * 0.05 + 0.01).to(torch.float16)
+            sv = (torch.rand(pages, 256, groups, device="cuda", generator=g) * 0.05 + 0.01).to(torch.float16)
+            t = time_calls([lambda st: ctx.bighead_attn_paged_q(q, kn, kn, qk, sk, qv, sv, dbt, dsl, out, nkv, stream=st)], args.reps)
+            byts = float((ctx_lens + q_len).sum()) * nkv * hd * 2 * (bits / 8 + 2 / 32)
+            kc = qk
+        else:
+            t = time_calls([lambda st: ctx.bighead_attn_paged(q, kn, kn, kc, vc, dbt, dsl, out, stream=st)], args.reps)
+            byts = float((ctx_lens + q_len).sum()) * nkv * hd * 2 * 2
         flops = float((4.0 * q_len * nq * hd * (ctx_lens + (q_len + 1) / 2)).sum())       # QK^T and PV under the causal mask
-        print(json.dumps({"op": "bighead_attn_paged", "seqs": bsz, "q_len": q_len, "mean_ctx": float(ctx_lens.mean()),
+        print(json.dumps({"op": "bighead_attn_paged_q" if args.kv_bits else "bighead_attn_paged", "kv_bits": args.kv_bits or 16, "seqs": bsz, "q_len": q_len, "mean_ctx": float(ctx_lens.mean()),
                           "kv_bytes": byts, "us": t * 1e6, "GBps": byts / t / 1e9, "hbm_frac": byts / t / 1e9 / hbm_peak,
                           "TFLOPs": flops / t / 1e12,
                           "note": "KV pool %.1f GB" % (kc.numel() * 4 / 1e9), "peaks": which}))
@@ -417,6 +429,7 @@ def main():
     ap.add_argument("--n", type=int, default=17408)
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--seqs", type=int, default=64)
+    ap.add_argument("--kv-bits", type=int, default=0, help="--op attn: quantised KV pools with this many bits (0 = fp16 pools)")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)

@@ -153,6 +153,28 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
             }
         }
 
+        if constexpr (QUANT) {
+            // Quantised pools hold codes of the rotated vectors H(k), H(v) (H = H32 / sqrt(32) per group of 32 dims).
+            // Instead of rotating every key and value back, the query is rotated once here (q . H(c) = H(q) . c) and the
+            // output row once at the end; the tiles below then hold the scaled codes as they are.
+            #pragma unroll
+            for (int gq = 0; gq < D / 32; ++gq) {
+                #pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float v[4][2];
+                    #pragma unroll
+                    for (int b4 = 0; b4 < 4; ++b4) {
+                        const half2 x = *reinterpret_cast<const half2*>(&qf[2 * gq + (b4 >> 1)][h + 2 * (b4 & 1)]);
+                        v[b4][0] = __low2float(x); v[b4][1] = __high2float(x);
+                    }
+                    had32_quad(v, t);
+                    #pragma unroll
+                    for (int b4 = 0; b4 < 4; ++b4)
+                        qf[2 * gq + (b4 >> 1)][h + 2 * (b4 & 1)] = pack_h2(v[b4][0] * R32, v[b4][1] * R32);
+                }
+            }
+        }
+
         float o_acc[DBLK][4];
         #pragma unroll
         for (int i = 0; i < DBLK; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
@@ -225,7 +247,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
 
             const uint8_t* ktile; const uint8_t* vtile;
             if constexpr (QUANT) {
-                // decode the staged codes into fp16 tiles: one warp-op = 4 groups = the D=128 values of one key
+                // scale the staged codes into fp16 tiles (rotated domain): one warp-op = 4 groups = the D=128 values of one key
                 uint8_t* dk = smem_raw + AT_STAGES * SM::STAGE;
                 uint8_t* dv = dk + SM::TILE;
                 const uint8_t* raw = smem_raw + stage * SM::STAGE;
@@ -234,12 +256,12 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                     for (int part = 0; part < D / 128; ++part) {
                         const uint8_t* rk = raw + key * SM::RAW_ROW;
                         const uint8_t* rv = raw + SM::RAW + key * SM::RAW_ROW;
-                        dequant_x4(reinterpret_cast<const uint32_t*>(rk) + part * 4 * p.k_bits,
-                                   reinterpret_cast<const half*>(rk + (D / 32) * 32) + part * 4,
-                                   reinterpret_cast<half*>(dk + key * SM::ROWB) + part * 128, 4, p.k_bits);
-                        dequant_x4(reinterpret_cast<const uint32_t*>(rv) + part * 4 * p.v_bits,
-                                   reinterpret_cast<const half*>(rv + (D / 32) * 32) + part * 4,
-                                   reinterpret_cast<half*>(dv + key * SM::ROWB) + part * 128, 4, p.v_bits);
+                        dequant_x4_norot(reinterpret_cast<const uint32_t*>(rk) + part * 4 * p.k_bits,
+                                         reinterpret_cast<const half*>(rk + (D / 32) * 32) + part * 4,
+                                         reinterpret_cast<half*>(dk + key * SM::ROWB) + part * 128, p.k_bits);
+                        dequant_x4_norot(reinterpret_cast<const uint32_t*>(rv) + part * 4 * p.v_bits,
+                                         reinterpret_cast<const half*>(rv + (D / 32) * 32) + part * 4,
+                                         reinterpret_cast<half*>(dv + key * SM::ROWB) + part * 128, p.v_bits);
                     }
                 }
                 __syncthreads();
@@ -375,6 +397,14 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                 ll += src[D + 1] * sc;
                 #pragma unroll
                 for (int e = 0; e < D / 32; ++e) acc[e] += src[lane * (D / 32) + e] * sc;
+            }
+            if constexpr (QUANT) {
+                // back out of the rotated domain: lane = (group lane / 8, values 4 (lane % 8) .. +3), as in the KV codec
+                static_assert(!QUANT || D == 128, "one warp = the 4 groups of a 128-wide head");
+                h4(acc[0], acc[1], acc[2], acc[3]);
+                h8_lanes(acc[0], acc[1], acc[2], acc[3], lane);
+                #pragma unroll
+                for (int e = 0; e < D / 32; ++e) acc[e] *= R32;
             }
             const int qidx = row / G, head = kvh * G + (row - qidx * G);
             if (splits == 1) {

@@ -124,4 +124,47 @@ __device__ __forceinline__ void dequant_x4(const uint32_t* __restrict__ in, cons
     }
 }
 
+// The same without the inverse rotation: out = (code - (m - 1/2)) * scale / m, in the rotated domain the codes live in.
+// For attention the rotation H32/sqrt(32) of every group is orthogonal and symmetric, so q . H(c) = H(q) . c and
+// sum_j p_j H(c_j) = H(sum_j p_j c_j): the kernel rotates each query once and each output row once instead of every
+// key and value (attn_paged.cuh), and this is all the per-key work that remains.
+__device__ __forceinline__ void dequant_x4_norot(const uint32_t* __restrict__ in, const half* __restrict__ scales,
+                                                 half* __restrict__ out, int bits)
+{
+    const int lane = threadIdx.x & 31, sg = lane >> 3, sl = lane & 7;
+    uint32_t q0, q1, q2, q3;
+    unpack4(in + sg * bits, sl, bits, q0, q1, q2, q3);
+    const int m = 1 << (bits - 1);
+    const float sm = __half2float(scales[sg]) * (1.0f / (float)m), mh = (float)m - 0.5f;
+    half2 a = __floats2half2_rn(((float)(int)q0 - mh) * sm, ((float)(int)q1 - mh) * sm);
+    half2 b = __floats2half2_rn(((float)(int)q2 - mh) * sm, ((float)(int)q3 - mh) * sm);
+    uint2 o; o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
+    reinterpret_cast<uint2*>(out)[lane] = o;
+}
+
+// Unnormalised H32 of a group held in mma fragment order by the 4 lanes of a quad: v[blk][c] is element 8 blk + 2 t + c
+// (t = lane & 3).  All 32 lanes must call it.
+__device__ __forceinline__ void had32_quad(float (&v)[4][2], int t)
+{
+    #pragma unroll
+    for (int b = 0; b < 4; ++b) { const float a = v[b][0], d = v[b][1]; v[b][0] = a + d; v[b][1] = a - d; }
+    #pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const float s0 = v[0][c] + v[1][c], d0 = v[0][c] - v[1][c], s1 = v[2][c] + v[3][c], d1 = v[2][c] - v[3][c];
+        v[0][c] = s0 + s1; v[1][c] = d0 + d1; v[2][c] = s0 - s1; v[3][c] = d0 - d1;
+    }
+    #pragma unroll
+    for (int i = 1; i < 4; i <<= 1) {
+        const bool up = t & i;
+        #pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            #pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const float pv = __shfl_xor_sync(0xffffffffu, v[b][c], i);
+                v[b][c] = (up ? -v[b][c] : v[b][c]) + pv;
+            }
+        }
+    }
+}
+
 }  // namespace exl3

@@ -206,29 +206,22 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                     cp_async16(dk + SM::TILE + key * SM::ROWB, vb + so);
                 }
             } else {
-                const int groups = p.nkv * (D / 32), gpk = D / 32;
-                const int kw = gpk * p.k_bits, vw = gpk * p.v_bits;             // code words per key per head
-                // one thread per (key, word pair): words are 4 bytes, copied in 8-byte pieces (bits*gpk is even for D>=64)
-                for (int c = tid; c < AT_TK * (kw / 2); c += AT_THREADS) {
-                    const int key = c / (kw / 2), w2 = c % (kw / 2);
-                    int kj = k0 + key; if (kj >= k_end) kj = k_end - 1;
-                    const size_t tok = (size_t)bt[kj >> 8] * EXL3_PAGE + (kj & 255);
-                    cp_async8(sbase + key * SM::RAW_ROW + w2 * 8, p.qk + (tok * groups + kvh * gpk) * p.k_bits + w2 * 2);
-                }
-                for (int c = tid; c < AT_TK * (vw / 2); c += AT_THREADS) {
-                    const int key = c / (vw / 2), w2 = c % (vw / 2);
-                    int kj = k0 + key; if (kj >= k_end) kj = k_end - 1;
-                    const size_t tok = (size_t)bt[kj >> 8] * EXL3_PAGE + (kj & 255);
-                    cp_async8(sbase + SM::RAW + key * SM::RAW_ROW + w2 * 8, p.qv + (tok * groups + kvh * gpk) * p.v_bits + w2 * 2);
-                }
-                for (int c = tid; c < AT_TK * 2; c += AT_THREADS) {             // scales: gpk halfs = 8 bytes at D=128
-                    const int key = c >> 1, which = c & 1;
-                    int kj = k0 + key; if (kj >= k_end) kj = k_end - 1;
-                    const size_t tok = (size_t)bt[kj >> 8] * EXL3_PAGE + (kj & 255);
-                    const half* src = (which ? p.sv : p.sk) + tok * groups + kvh * gpk;
-                    uint8_t* dst = sbase + (which ? SM::RAW : 0) + key * SM::RAW_ROW + gpk * 8 * 4;
-                    for (int q8 = 0; q8 < gpk / 4; ++q8) cp_async8(dst + q8 * 8, src + q8 * 4);
-                }
+                // A tile of 64 keys lies inside one page (as above).  Per key and head the codes are bits x 16 bytes (4 groups
+                // x bits words) and the scales 8 bytes; two threads share a key: both copy code chunks, one the K scales,
+                // the other the V scales.
+                static_assert(D == 128, "loader assumes 4 groups per head");
+                const int groups = p.nkv * (D / 32);
+                const size_t tok0 = (size_t)bt[k0 >> 8] * EXL3_PAGE + (k0 & 255);
+                const int key = tid >> 1, half_id = tid & 1;
+                const size_t tok = tok0 + min(key, k_end - 1 - k0);
+                const uint8_t* ksrc = reinterpret_cast<const uint8_t*>(p.qk + (tok * groups + kvh * 4) * p.k_bits);
+                const uint8_t* vsrc = reinterpret_cast<const uint8_t*>(p.qv + (tok * groups + kvh * 4) * p.v_bits);
+                uint8_t* kdst = sbase + key * SM::RAW_ROW;
+                uint8_t* vdst = sbase + SM::RAW + key * SM::RAW_ROW;
+                for (int ch = half_id; ch < p.k_bits; ch += 2) cp_async16(kdst + ch * 16, ksrc + ch * 16);
+                for (int ch = half_id; ch < p.v_bits; ch += 2) cp_async16(vdst + ch * 16, vsrc + ch * 16);
+                const half* ssrc = (half_id ? p.sv : p.sk) + tok * groups + kvh * 4;
+                cp_async8((half_id ? vdst : kdst) + (D / 32) * 32, ssrc);
             }
         };
 

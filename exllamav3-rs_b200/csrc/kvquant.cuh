@@ -132,13 +132,36 @@ __device__ __forceinline__ void dequant_x4_norot(const uint32_t* __restrict__ in
                                                  half* __restrict__ out, int bits)
 {
     const int lane = threadIdx.x & 31, sg = lane >> 3, sl = lane & 7;
-    uint32_t q0, q1, q2, q3;
-    unpack4(in + sg * bits, sl, bits, q0, q1, q2, q3);
+    // Codes become fp16 numbers without an integer-to-float conversion: 0x6000 | (q << 1) is the half 512 + q (spacing
+    // 0.5 in [512, 1024), q <= 255); subtracting 512 + m - 1/2 and multiplying by scale / m are then both exact up to
+    // the single final rounding, the same value as (q - (m - 1/2)) * scale / m computed in fp32 and rounded once.
+    uint32_t p0, p1;
+    if (bits == 4) {
+        const uint32_t w = in[sg * 4 + (sl >> 1)] >> ((sl & 1) * 16);
+        p0 = 0x60006000u | ((w & 0xFu) << 1) | ((w & 0xF0u) << 13);
+        p1 = 0x60006000u | ((w & 0xF00u) >> 7) | ((w & 0xF000u) << 5);
+    } else if (bits == 6) {
+        // planes of 4 bits (high part of each code) and 2 bits (low part): q = (nibble << 2) | pair
+        const uint32_t w4 = in[sg * 6 + (sl >> 1)] >> ((sl & 1) * 16);
+        const uint32_t w2 = in[sg * 6 + 4 + (sl >> 2)] >> ((sl & 3) * 8);
+        p0 = 0x60006000u | ((w4 & 0xFu) << 3) | ((w2 & 0x3u) << 1) | ((w4 & 0xF0u) << 15) | ((w2 & 0xCu) << 15);
+        p1 = 0x60006000u | ((w4 & 0xF00u) >> 5) | ((w2 & 0x30u) >> 3) | ((w4 & 0xF000u) << 7) | ((w2 & 0xC0u) << 11);
+    } else if (bits == 8) {
+        const uint32_t w = in[sg * 8 + sl];                 // one plane of 8-bit fields: the lane's 4 codes are its 4 bytes
+        p0 = 0x60006000u | ((w & 0xFFu) << 1) | ((w & 0xFF00u) << 9);
+        p1 = 0x60006000u | ((w >> 15) & 0x1FEu) | ((w & 0xFF000000u) >> 7);
+    } else {
+        uint32_t q0, q1, q2, q3;
+        unpack4(in + sg * bits, sl, bits, q0, q1, q2, q3);
+        p0 = 0x60006000u | (q0 << 1) | (q1 << 17);
+        p1 = 0x60006000u | (q2 << 1) | (q3 << 17);
+    }
     const int m = 1 << (bits - 1);
-    const float sm = __half2float(scales[sg]) * (1.0f / (float)m), mh = (float)m - 0.5f;
-    half2 a = __floats2half2_rn(((float)(int)q0 - mh) * sm, ((float)(int)q1 - mh) * sm);
-    half2 b = __floats2half2_rn(((float)(int)q2 - mh) * sm, ((float)(int)q3 - mh) * sm);
-    uint2 o; o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
+    const half2 off = __float2half2_rn(512.0f + (float)m - 0.5f);
+    const half2 sm = __half2half2(__hmul(scales[sg], __float2half_rn(1.0f / (float)m)));
+    const half2 a = __hmul2(__hsub2(*reinterpret_cast<const half2*>(&p0), off), sm);
+    const half2 b = __hmul2(__hsub2(*reinterpret_cast<const half2*>(&p1), off), sm);
+    uint2 o; o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&b);
     reinterpret_cast<uint2*>(out)[lane] = o;
 }
 

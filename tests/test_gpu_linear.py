@@ -392,3 +392,11 @@ def test_hgemm_rejects_bad_shapes(ctx):
     c = torch.zeros(4, 16, dtype=torch.float16, device="cuda")
     with pytest.raises(exl3b200.Exl3Error):
         ctx.hgemm(a, b, c)                       # k = 96 is no multiple of 64
+
+
+@pytest.mark.parametrize("m", [5, 200, 600])
+@pytest.mark.parametrize("n", [128, 384, 1152])
+def test_gemm_tc_half_slab(ctx, ctx_small_only, m, n):
+    """column counts with n % 256 == 128: the last slab has one valid 128-column half (decoded by one CTA of the pair, the
+    other half reads zero-filled codes and is never stored)"""
+    _tc_case(ctx, ctx_small_only, None, m, 1024, n, 4, 1, m == 200, 1600 + m + n, oracle=(m <= 200))

@@ -244,6 +244,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                 uint8_t* dk = smem_raw + AT_STAGES * SM::STAGE;
                 uint8_t* dv = dk + SM::TILE;
                 const uint8_t* raw = smem_raw + stage * SM::STAGE;
+                #pragma unroll 4                                   // independent keys in flight: the chain per key is latency-bound
                 for (int key = warp; key < AT_TK; key += 4) {
                     #pragma unroll
                     for (int part = 0; part < D / 128; ++part) {

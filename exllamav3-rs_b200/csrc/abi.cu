@@ -36,9 +36,12 @@ extern "C" int exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** ou
     ctx->num_sms = prop.multiProcessorCount;
     ctx->ws_bytes = workspace_bytes ? workspace_bytes : ((size_t)512 << 20);
     ctx->n_counters = 1 << 16;
+    ctx->plan_slot_bytes = (size_t)1 << 20;
+    ctx->plan_keep = 0; ctx->plan_valid[0] = ctx->plan_valid[1] = 0;
     bool ok = cudaMalloc(&ctx->ws, ctx->ws_bytes) == cudaSuccess &&
               cudaMalloc(&ctx->counters, ctx->n_counters * sizeof(int)) == cudaSuccess &&
               cudaMalloc(&ctx->status, 64) == cudaSuccess &&
+              cudaMalloc(&ctx->plan_slots, 2 * ctx->plan_slot_bytes) == cudaSuccess &&
               cudaMemset(ctx->counters, 0, ctx->n_counters * sizeof(int)) == cudaSuccess &&
               cudaMemset(ctx->status, 0, 64) == cudaSuccess &&
               cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking) == cudaSuccess &&
@@ -57,6 +60,7 @@ extern "C" void exl3_ctx_destroy(exl3_ctx* ctx)
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->status) cudaFree(ctx->status);
+    if (ctx->plan_slots) cudaFree(ctx->plan_slots);
     delete ctx;
 }
 

@@ -213,20 +213,37 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     const int target_items = grid_x * (quant ? 4 : 2);
     const int max_items = target_items + p.bsz * rb_max + 1;
 
+    // The work list depends on the batch's lengths, not on the layer: inside exl3_step_forward it is built by the first
+    // layer's call into the context's slot for this class and reused by the other layers.
+    const int cls = decode_shape ? 0 : 1;
+    const size_t list_bytes = 256 + (((size_t)max_items * sizeof(AttnItem) + 255) & ~(size_t)255) + 2 * (((size_t)p.bsz * 4 + 255) & ~(size_t)255);
+    const bool keep = ctx->plan_keep && list_bytes <= ctx->plan_slot_bytes;
     size_t off = 0;
-    AttnPlan* plan = (AttnPlan*)exl3_ws_take(ctx, &off, sizeof(AttnPlan));
-    AttnItem* items = (AttnItem*)exl3_ws_take(ctx, &off, (size_t)max_items * sizeof(AttnItem));
-    int* seq_base = (int*)exl3_ws_take(ctx, &off, (size_t)p.bsz * 4);
-    int* seq_splits = (int*)exl3_ws_take(ctx, &off, (size_t)p.bsz * 4);
+    AttnPlan* plan; AttnItem* items; int* seq_base; int* seq_splits;
+    if (keep) {
+        uint8_t* slot = ctx->plan_slots + cls * ctx->plan_slot_bytes;
+        plan = (AttnPlan*)slot;
+        items = (AttnItem*)(slot + 256);
+        seq_base = (int*)(slot + 256 + (((size_t)max_items * sizeof(AttnItem) + 255) & ~(size_t)255));
+        seq_splits = (int*)((uint8_t*)seq_base + (((size_t)p.bsz * 4 + 255) & ~(size_t)255));
+    } else {
+        plan = (AttnPlan*)exl3_ws_take(ctx, &off, sizeof(AttnPlan));
+        items = (AttnItem*)exl3_ws_take(ctx, &off, (size_t)max_items * sizeof(AttnItem));
+        seq_base = (int*)exl3_ws_take(ctx, &off, (size_t)p.bsz * 4);
+        seq_splits = (int*)exl3_ws_take(ctx, &off, (size_t)p.bsz * 4);
+    }
     float* partial = (float*)exl3_ws_take(ctx, &off, (size_t)max_items * p.nkv * rows_per_cta * (D + 2) * 4);
     if (!plan || !items || !seq_base || !seq_splits || !partial)
         return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "attention: context scratch too small for the split-KV partials");
     p.plan = plan; p.items = items; p.seq_base = seq_base; p.seq_splits = seq_splits; p.partial = partial;
     p.status = ctx->status;
 
-    attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, rows_lo, rows_hi,
-                                          use_tc ? ATC_TN : AT_TK, target_items, max_items, plan, items, seq_base, seq_splits);
-    ctx->launches++;
+    if (!(keep && ctx->plan_valid[cls])) {
+        attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, rows_lo, rows_hi,
+                                              use_tc ? ATC_TN : AT_TK, target_items, max_items, plan, items, seq_base, seq_splits);
+        ctx->launches++;
+        if (keep) ctx->plan_valid[cls] = 1;
+    }
     dim3 grid(grid_x, p.nkv);
     cudaError_t e;
     if (use_tc) e = launch_attn_tc(ctx, p, max_items, st);

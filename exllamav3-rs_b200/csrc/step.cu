@@ -134,6 +134,12 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
     EXL3_REQUIRE(m->kv_bits == 0 || (m->kv_bits >= 2 && m->kv_bits <= 8), "step_forward: kv_bits must be 0 or 2..8");
     Scratch s;
     const size_t need = carve(m, b->rows, b->bsz, (uint8_t*)scratch, &s);
+    // attention work lists are built by the first layer and kept for the others; the flag drops on every way out
+    struct PlanKeep {
+        exl3_ctx* c;
+        explicit PlanKeep(exl3_ctx* ctx_) : c(ctx_) { c->plan_keep = 1; c->plan_valid[0] = c->plan_valid[1] = 0; }
+        ~PlanKeep() { c->plan_keep = 0; c->plan_valid[0] = c->plan_valid[1] = 0; }
+    } plan_keep(ctx);
     if (need > scratch_bytes) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "step_forward: scratch buffer too small");
     cudaStream_t st = (cudaStream_t)stream;
     const int rows = b->rows, bsz = b->bsz, hidden = m->hidden;

@@ -246,6 +246,8 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     }
     dim3 grid(grid_x, p.nkv);
     cudaError_t e;
+    if (!use_tc && cudaMemsetAsync(&plan->next, 0, sizeof(int), st) != cudaSuccess)      // the persistent kernel's work counter
+        return exl3_fail(ctx, EXL3_ERR_CUDA, "attention: cudaMemsetAsync failed");
     if (use_tc) e = launch_attn_tc(ctx, p, max_items, st);
     else if (quant) e = decode_shape ? launch_attn<128, 1, 4, true>(p, grid, st) : launch_attn<128, 4, 1, true>(p, grid, st);
     else       e = decode_shape ? launch_attn<128, 1, 4, false>(p, grid, st) : launch_attn<128, 4, 1, false>(p, grid, st);

@@ -21,7 +21,8 @@ struct AttnItem { int b, rb, split, pad; };
 struct AttnPlan {          // device-resident, written by attn_plan_kernel
     int n_items;
     int chunk;             // keys per split
-    int pad0, pad1;
+    int next;              // work counter of the persistent kernel: next (item, kv head) unit to hand out; zeroed per launch
+    int pad1;
 };
 
 struct AttnParams {
@@ -104,11 +105,20 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int wm = warp / WN, wn = warp % WN;
-    const int kvh = blockIdx.y;
     const int G = p.nq / p.nkv;
     const int n_items = p.plan->n_items, chunk = p.plan->chunk;
 
-    for (int item_idx = blockIdx.x; item_idx < n_items; item_idx += gridDim.x) {
+    // Work units = (item, kv head), handed out through a counter: items differ in length (last splits, causal cuts), and a
+    // fixed assignment left a quarter of the SM time idle at the end of the kernel.
+    __shared__ int s_unit;
+    const int n_units = n_items * p.nkv;
+    for (;;) {
+        __syncthreads();                                   // everyone is done with the previous unit (and with s_unit)
+        if (tid == 0) s_unit = atomicAdd(const_cast<int*>(&p.plan->next), 1);
+        __syncthreads();
+        const int unit = s_unit;
+        if (unit >= n_units) break;
+        const int item_idx = unit / p.nkv, kvh = unit - item_idx * p.nkv;
         const AttnItem item = p.items[item_idx];
         const int b = item.b;
         const int row_base = p.cu_q ? p.cu_q[b] : b * p.q_len;

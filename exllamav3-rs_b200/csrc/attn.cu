@@ -207,10 +207,11 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
         per_sm = std::max(1, std::min(3, (int)((227 * 1024) / (smem + 1024))));
     }
     const int grid_x = std::max(1, ctx->num_sms * per_sm / p.nkv);
-    // two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs a 133 KB
-    // partial per kv head written and read back (4 per slot was measured 20 % slower, 1 per slot 2 % slower)
+    // tcgen05 kernel: two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs a
+    // 133 KB partial per kv head written and read back (4 per slot was measured 20 % slower, 1 per slot 2 % slower).
+    // mma.sync kernels (units handed out dynamically, 8 KB partials): three per slot for fp16 pools, four for quantised.
     // the quantised kernel spends most of its time scaling codes, so finer items balance it better (+11 % measured)
-    const int target_items = grid_x * (quant ? 4 : 2);
+    const int target_items = grid_x * (use_tc ? 2 : (quant ? 4 : 3));
     const int max_items = target_items + p.bsz * rb_max + 1;
 
     // The work list depends on the batch's lengths, not on the layer: inside exl3_step_forward it is built by the first

@@ -45,6 +45,9 @@ extern "C" int exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** ou
               cudaMemset(ctx->counters, 0, ctx->n_counters * sizeof(int)) == cudaSuccess &&
               cudaMemset(ctx->status, 0, 64) == cudaSuccess &&
               cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&ctx->aux_stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
+              cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming) == cudaSuccess &&
               cudaDeviceSynchronize() == cudaSuccess;
     if (!ok) { cudaGetLastError(); exl3_ctx_destroy(ctx); return EXL3_ERR_NOMEM; }
     strcpy(ctx->err, "no error");
@@ -57,6 +60,9 @@ extern "C" void exl3_ctx_destroy(exl3_ctx* ctx)
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
+    if (ctx->aux_stream) cudaStreamDestroy(ctx->aux_stream);
+    if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+    if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->status) cudaFree(ctx->status);

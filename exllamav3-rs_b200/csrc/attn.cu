@@ -189,7 +189,7 @@ cudaError_t launch_attn_tc(exl3_ctx* ctx, const AttnParams& p, int max_items, cu
 
 // One pass = plan + attention + combine over the sequences whose packed row count lies in (rows_lo, rows_hi].
 int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int max_rows, int rows_lo, int rows_hi,
-              bool decode_shape, bool quant)
+              bool decode_shape, bool quant, size_t* ws_off)
 {
     const int D = 128;
     const int G = p.nq / p.nkv;
@@ -219,7 +219,7 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     const int cls = decode_shape ? 0 : 1;
     const size_t list_bytes = 256 + (((size_t)max_items * sizeof(AttnItem) + 255) & ~(size_t)255) + 2 * (((size_t)p.bsz * 4 + 255) & ~(size_t)255);
     const bool keep = ctx->plan_keep && list_bytes <= ctx->plan_slot_bytes;
-    size_t off = 0;
+    size_t off = *ws_off;                                // scratch of an earlier pass that may still be running
     AttnPlan* plan; AttnItem* items; int* seq_base; int* seq_splits;
     if (keep) {
         uint8_t* slot = ctx->plan_slots + cls * ctx->plan_slot_bytes;
@@ -238,6 +238,7 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
         return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "attention: context scratch too small for the split-KV partials");
     p.plan = plan; p.items = items; p.seq_base = seq_base; p.seq_splits = seq_splits; p.partial = partial;
     p.status = ctx->status;
+    *ws_off = off;
 
     if (!(keep && ctx->plan_valid[cls])) {
         attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, rows_lo, rows_hi,
@@ -267,11 +268,20 @@ int attn_impl(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
 {
     const int G = p.nq / p.nkv;
     const int max_rows = max_q_len * G;
-    if (max_rows <= 16) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 16, true, quant);
-    if (!p.cu_q) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 1 << 30, false, quant);
-    int rc = attn_pass(ctx, st, p, total_rows, 16, 0, 16, true, quant);
-    if (rc != EXL3_OK) return rc;
-    return attn_pass(ctx, st, p, total_rows, max_rows, 16, 1 << 30, false, quant);
+    size_t off = 0;
+    if (max_rows <= 16) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 16, true, quant, &off);
+    if (!p.cu_q) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 1 << 30, false, quant, &off);
+    // Ragged batch with both classes: the decode-class pass (bound by HBM) runs on the context's second stream beside the
+    // long-class pass (bound by the tensor core and the MUFU); they touch disjoint sequences and output rows, and each
+    // has its own scratch.  Fork and join by events, which also works while the caller's stream is being captured.
+    if (cudaEventRecord(ctx->ev_fork, st) != cudaSuccess || cudaStreamWaitEvent(ctx->aux_stream, ctx->ev_fork, 0) != cudaSuccess)
+        return exl3_fail(ctx, EXL3_ERR_CUDA, "attention: stream fork failed");
+    int rc = attn_pass(ctx, ctx->aux_stream, p, total_rows, 16, 0, 16, true, quant, &off);
+    int rc2 = rc == EXL3_OK ? attn_pass(ctx, st, p, total_rows, max_rows, 16, 1 << 30, false, quant, &off) : rc;
+    // always join, also after an error, so that a capture in progress stays well-formed
+    if (cudaEventRecord(ctx->ev_join, ctx->aux_stream) != cudaSuccess || cudaStreamWaitEvent(st, ctx->ev_join, 0) != cudaSuccess)
+        return exl3_fail(ctx, EXL3_ERR_CUDA, "attention: stream join failed");
+    return rc != EXL3_OK ? rc : rc2;
 }
 
 int check_common(exl3_ctx* ctx, const void* q, const void* o, const int32_t* bt, const int32_t* sl, int bsz, int q_len,

@@ -22,6 +22,8 @@ struct exl3_ctx {
     int n_counters;
     int* status;            // device status word (0 = ok)
     cudaStream_t side_stream;
+    cudaStream_t aux_stream;    // second lane inside one call: the decode-class attention pass runs beside the long-class one
+    cudaEvent_t ev_fork, ev_join;
     uint64_t launches;
     int mma_attn;
     int use_tc;             // 1: tcgen05 GEMM for large M (default), 0: small-M kernel in passes (for A/B runs)

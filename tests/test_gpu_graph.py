@@ -45,3 +45,44 @@ def test_capture_and_replay_decode_ops(ctx):
     exl3b200.lib().exl3_sync_side_stream(ctx.handle)
     assert torch.equal(c, want_c)
     assert exl3b200.lib().exl3_cuda_free_mib() > 0
+
+
+def test_capture_ragged_attention_with_stream_fork(ctx):
+    """A ragged attention call with decode rows and long row blocks forks its decode pass onto the context's second
+    stream; captured into a graph, the replay must give exactly what the eager call gives."""
+    import torch
+    import exl3b200
+    r = H.rng(77)
+    nq, nkv, hd = 40, 8, 128
+    qlens = np.array([1, 1, 256, 1, 70], np.int32)
+    ctx_lens = np.array([500, 3000, 2048, 9000, 255], np.int32)
+    cu = np.concatenate([[0], np.cumsum(qlens)]).astype(np.int32)
+    bt, pages = H.make_paged(r, len(qlens), ctx_lens + qlens, nkv, hd)
+    rows = int(cu[-1])
+    q = H.to_dev(r.standard_normal((rows, nq, hd)).astype(np.float16))
+    k = H.to_dev((0.5 * r.standard_normal((rows, nkv, hd))).astype(np.float16))
+    v = H.to_dev((0.5 * r.standard_normal((rows, nkv, hd))).astype(np.float16))
+    kc = H.to_dev((0.5 * r.standard_normal((pages, 256, nkv, hd))).astype(np.float16))
+    vc = H.to_dev((0.5 * r.standard_normal((pages, 256, nkv, hd))).astype(np.float16))
+    dbt, dsl, dcu = H.to_dev(bt), H.to_dev(ctx_lens), H.to_dev(cu)
+    want = torch.full((rows, nq, hd), float("nan"), dtype=torch.float16, device="cuda")
+    ctx.bighead_attn_paged(q, k, v, kc, vc, dbt, dsl, want, cu_q=dcu, max_q_len=int(qlens.max()))
+    ctx.poll_status()
+    torch.cuda.synchronize()
+
+    g = exl3b200.CudaGraph(ctx)
+    side = g.side_stream()
+    got = torch.full_like(want, float("nan"))
+    ctx.bighead_attn_paged(q, k, v, kc, vc, dbt, dsl, got, cu_q=dcu, max_q_len=int(qlens.max()), stream=side)   # warm-up
+    exl3b200.lib().exl3_sync_side_stream(ctx.handle)
+    g.capture_begin()
+    ctx.bighead_attn_paged(q, k, v, kc, vc, dbt, dsl, got, cu_q=dcu, max_q_len=int(qlens.max()), stream=side)
+    g.capture_end()
+    got.fill_(float("nan"))
+    torch.cuda.synchronize()
+    for _ in range(2):
+        g.replay()
+    assert exl3b200.lib().exl3_sync_side_stream(ctx.handle) == 0
+    ctx.poll_status()
+    assert torch.isfinite(got).all()
+    assert torch.equal(got, want)

@@ -336,7 +336,7 @@ def ctx_one_cta():
     c.close()
 
 
-@pytest.mark.parametrize("m", [129, 256, 257, 300, 384, 385, 512, 513, 700, 1052])
+@pytest.mark.parametrize("m", [1, 5, 64, 129, 256, 257, 300, 384, 385, 512, 513, 700, 1052])
 def test_gemm_tc_pair_equals_one_cta(ctx, ctx_one_cta, m):
     """the CTA-pair form and the one-CTA form run the same multiplies in the same order: equal bit for bit, at every
     split of the rows over the pair's four 128-row tiles"""

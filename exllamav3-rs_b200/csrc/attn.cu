@@ -212,7 +212,10 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     // mma.sync kernels (units handed out dynamically, 8 KB partials): three per slot for fp16 pools, four for quantised.
     // the quantised kernel spends most of its time scaling codes, so finer items balance it better (+11 % measured)
     const int target_items = grid_x * (use_tc ? 2 : (quant ? 4 : 3));
-    const int max_items = target_items + p.bsz * rb_max + 1;
+    // items <= target + sum of row blocks (every (sequence, row block) rounds its split count up once); the row blocks are
+    // bounded by bsz * rb_max and, usually much tighter for ragged batches, by total_rows * G / rows_per_cta + bsz
+    const long long rb_sum = std::min((long long)p.bsz * rb_max, ((long long)total_rows * G + rows_per_cta - 1) / rows_per_cta + p.bsz);
+    const int max_items = target_items + (int)std::min(rb_sum, (long long)(1 << 24)) + 1;
 
     // The work list depends on the batch's lengths, not on the layer: inside exl3_step_forward it is built by the first
     // layer's call into the context's slot for this class and reused by the other layers.

@@ -1,6 +1,7 @@
 // exl3_gemm: host-side dispatch of the fused EXL3 trellis-decode GEMM.
 #include "gemm_small.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_decode.cuh"
 
 namespace {
 
@@ -293,6 +294,109 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
     return EXL3_OK;
 }
 
+// ---- decode-regime kernel (1..16 rows)
+
+constexpr int GD_MAX_M = 16;
+
+template <int K, int CB, int MT>
+cudaError_t launch_decode(const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+{
+    constexpr int bytes = GdSmem<K, MT>::BYTES;
+    static bool configured[64] = {};
+    auto kern = gemm_decode_kernel<K, CB, MT>;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kern<<<grid, GD_THREADS, bytes, st>>>(rmap[0], rmap[1], rmap[2], p);
+    return cudaPeekAtLastError();
+}
+
+template <int K, int CB>
+cudaError_t launch_decode_mt(int mt, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+{
+    return mt == 1 ? launch_decode<K, CB, 1>(rmap, p, grid, st) : launch_decode<K, CB, 2>(rmap, p, grid, st);
+}
+
+template <int K>
+cudaError_t launch_decode_cb(int cb, int mt, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+{
+    if (cb == 0) return launch_decode_mt<K, 0>(mt, rmap, p, grid, st);
+    if (cb == 1) return launch_decode_mt<K, 1>(mt, rmap, p, grid, st);
+    return launch_decode_mt<K, 2>(mt, rmap, p, grid, st);
+}
+
+cudaError_t launch_decode_k(int K, int cb, int mt, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+{
+    switch (K) {
+        case 1: return launch_decode_cb<1>(cb, mt, rmap, p, grid, st);
+        case 2: return launch_decode_cb<2>(cb, mt, rmap, p, grid, st);
+        case 3: return launch_decode_cb<3>(cb, mt, rmap, p, grid, st);
+        case 4: return launch_decode_cb<4>(cb, mt, rmap, p, grid, st);
+        case 5: return launch_decode_cb<5>(cb, mt, rmap, p, grid, st);
+        case 6: return launch_decode_cb<6>(cb, mt, rmap, p, grid, st);
+        case 7: return launch_decode_cb<7>(cb, mt, rmap, p, grid, st);
+        default: return launch_decode_cb<8>(cb, mt, rmap, p, grid, st);
+    }
+}
+
+// Decode path for m <= 16 rows and `nseg` weight tensors that share the activations, k, bits and codebook: one launch of
+// the input transforms (fragment order, one per tensor) and one of the streaming kernel over all their column blocks.
+int gemm_decode_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const void* const* trellis, void* const* C,
+                     const half* const* suh, const half* const* svh, const int* n, int m, int k, int K, int c_fp32, int cb)
+{
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled is not available from this driver");
+    const int mt = m <= 8 ? 1 : 2;
+    size_t off = 0;
+    GemmDecodePrologueArgs pa;
+    CUtensorMap rmap[GD_MAX_SEG];
+    GemmDecodeParams p;
+    memset(&p, 0, sizeof(p));
+    int blocks = 0;
+    for (int i = 0; i < GD_MAX_SEG; ++i) {
+        const int j = i < nseg ? i : nseg - 1;              // unused slots repeat the last tensor (never selected)
+        if (i < nseg) {
+            pa.a_frag[i] = (uint32_t*)exl3_ws_take(ctx, &off, (size_t)mt * k * 32);
+            pa.rowsum[i] = (float*)exl3_ws_take(ctx, &off, (size_t)mt * 8 * 4);
+            if (!pa.a_frag[i] || !pa.rowsum[i]) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the activations");
+            pa.suh[i] = suh[i];
+            blocks += n[i] / 128;
+            cuuint64_t rdims[2] = {(cuuint64_t)(n[i] / 16) * 4 * K, (cuuint64_t)(k / 16)};
+            cuuint64_t rstrides[1] = {(cuuint64_t)(n[i] / 16) * 32 * K};
+            cuuint32_t rbox[2] = {(cuuint32_t)GD_SLOT_TILES * 4 * K, (cuuint32_t)GD_SLOT_ROWS};
+            cuuint32_t estr[2] = {1, 1};
+            CUresult r = enc(&rmap[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(trellis[i]), rdims, rstrides, rbox, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled failed for the trellis");
+        } else {
+            pa.a_frag[i] = pa.a_frag[j]; pa.rowsum[i] = pa.rowsum[j]; pa.suh[i] = pa.suh[j]; rmap[i] = rmap[j];
+        }
+        p.a_frag[i] = (const uint4*)pa.a_frag[i]; p.rowsum[i] = pa.rowsum[i];
+        p.C[i] = C[j]; p.svh[i] = svh[j]; p.n[i] = n[j];
+        p.blk_end[i] = i < nseg ? blocks : 0x7fffffff;
+    }
+    p.blk_end[GD_MAX_SEG - 1] = blocks;                     // the kernel reads the total from the last entry
+    for (int i = nseg; i < GD_MAX_SEG - 1; ++i) p.blk_end[i] = blocks;
+    if (blocks > ctx->n_counters) return exl3_fail(ctx, EXL3_ERR_INVALID, "exl3_gemm: n too large for the context's counters");
+    const int KC = (k + GD_UNIT_K - 1) / GD_UNIT_K;
+    const long long total = (long long)blocks * KC;
+    const int grid = (int)(total < ctx->num_sms ? total : ctx->num_sms);
+    p.partial = (float*)exl3_ws_take(ctx, &off, (size_t)grid * 2 * m * 128 * 4);
+    if (!p.partial) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the partial sums");
+    p.counters = ctx->counters; p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
+    gemm_decode_prologue_kernel<<<dim3(8 * mt, nseg), 256, 0, st>>>(A, pa, m, k);
+    ctx->launches++;
+    cudaError_t e = launch_decode_k(K, cb, mt, rmap, p, grid, st);
+    ctx->launches++;
+    if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
+    return EXL3_OK;
+}
+
 }  // namespace
 
 // Rows are processed in passes of up to 64; each pass = input transform + one fused decode/MMA/output-transform launch.
@@ -319,6 +423,10 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
     // at 4 bpw: the tcgen05 kernel takes 47-52 us for any m <= 256 (its decoders set the pace), the mma.sync small-M
     // kernel 54 us at m = 1, 73 us at m = 16 and 209 us at m = 64, so every row count goes to the former.  The small-M
     // kernel serves exl3_gemm_noalloc, EXL3_B200_NO_TC, and n % 256 == 128 under EXL3_B200_NO_PAIR.
+    if (m <= GD_MAX_M && ctx->use_decode) {
+        const half* suh1 = (const half*)suh; const half* svh1 = (const half*)svh;
+        return gemm_decode_rows(ctx, st, (const half*)A, 1, &trellis, &C, &suh1, &svh1, &n, m, k, K, c_fp32, cb);
+    }
     int tc_rows = 0;
     if (m > TC_MAX_SMALL_M && (n % TC_BN == 0 || ctx->use_pair) && ctx->use_tc) {
         tc_rows = m;
@@ -363,6 +471,11 @@ extern "C" int exl3_gemm_fanout(exl3_ctx* ctx, exl3_stream stream, const void* A
         same = same && w[i]->k == w[0]->k && w[i]->K == w[0]->K && w[i]->cb == w[0]->cb && w[i]->n % TC_BN == 0 &&
                w[i]->k % 128 == 0 && w[i]->K >= 1 && w[i]->K <= 8 && aligned16(w[i]->trellis) && aligned16(C[i]) &&
                aligned16(w[i]->suh) && aligned16(w[i]->svh) && (w[i]->suh != nullptr) == (w[0]->suh != nullptr);
+    }
+    if (count > 1 && same && m <= GD_MAX_M && ctx->use_decode && aligned16(A)) {
+        const void* tr[GD_MAX_SEG]; const half* suh[GD_MAX_SEG]; const half* svh[GD_MAX_SEG]; int n[GD_MAX_SEG];
+        for (int i = 0; i < count; ++i) { tr[i] = w[i]->trellis; suh[i] = (const half*)w[i]->suh; svh[i] = (const half*)w[i]->svh; n[i] = w[i]->n; }
+        return gemm_decode_rows(ctx, (cudaStream_t)stream, (const half*)A, count, tr, C, suh, svh, n, m, w[0]->k, w[0]->K, c_fp32, w[0]->cb);
     }
     if (count > 1 && same && m > TC_MAX_SMALL_M && ctx->use_tc && aligned16(A)) {
         const void* tr[TC_MAX_SEG]; const half* suh[TC_MAX_SEG]; const half* svh[TC_MAX_SEG]; int n[TC_MAX_SEG];

@@ -152,11 +152,12 @@ def _gemm_case(ctx, ref, m, k, n, K, cb, c_fp32, seed, check_oracle=True):
     return got
 
 
-@pytest.fixture(params=["tcgen05", "small-m"])
+@pytest.fixture(params=["default", "tcgen05-only", "small-m"])
 def gemm_ctx(request):
-    """Both GEMM kernels behind exl3_gemm: the default context (tcgen05 kernel whenever n % 256 == 0) and one with that
-    path switched off (mma.sync small-M kernel in 64-row passes)."""
-    return request.getfixturevalue("ctx" if request.param == "tcgen05" else "ctx_small_only")
+    """The three GEMM kernels behind exl3_gemm: the default context (streaming decode kernel up to 16 rows, tcgen05 kernel
+    above), one with the decode kernel switched off (tcgen05 kernel at every row count) and one with both switched off
+    (mma.sync small-M kernel in 64-row passes)."""
+    return request.getfixturevalue({"default": "ctx", "tcgen05-only": "ctx_tc_only", "small-m": "ctx_small_only"}[request.param])
 
 
 @pytest.mark.parametrize("cb", [0, 1, 2])
@@ -181,6 +182,31 @@ def test_gemm_shapes(ctx, ref, k, n, c_fp32):
 def test_gemm_sweep_shape(gemm_ctx, ref, m, K):
     """K=5120, N=17408 sweep of the benchmark configs at the small-M sizes, against oracle and reference op."""
     _gemm_case(gemm_ctx, ref, m, 5120, 17408, K, 1, False, 700 + m + K, check_oracle=(m <= 16))
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+@pytest.mark.parametrize("m,k,n", [(1, 1152, 384), (8, 2176, 1280), (9, 1152, 128), (16, 3200, 640), (3, 128, 128)])
+def test_gemm_decode_ragged_k_chunks(ctx, ref, m, k, n, cb):
+    """k that is no multiple of the decode kernel's 1024-k chunk (idle k-slices in the last chunk), one and two row sets,
+    column counts that are no multiple of 256"""
+    _gemm_case(ctx, ref, m, k, n, 4, cb, m % 2 == 0, 800 + m + k + cb)
+
+
+@pytest.mark.parametrize("m,k,n,K", [(16, 5120, 151936, 4), (7, 17408, 5120, 3), (12, 5120, 5120, 8)])
+def test_gemm_decode_model_shapes(ctx, ref, m, k, n, K):
+    """the head, down_proj and o_proj shapes of the 27B-class model at decode row counts: against the reference op, and
+    against the oracle on a seeded subset of 128-column blocks (the product has no cross-block terms)"""
+    from oracle import oracle as O
+    torch = _torch()
+    got = _gemm_case(ctx, ref, m, k, n, K, 1, False, 900 + m, check_oracle=False)
+    r = H.rng(900 + m)                                    # same stream as _gemm_case: regenerate its inputs
+    A = r.standard_normal((m, k)).astype(np.float16)
+    tr = H.rand_trellis(r, k, n, K)
+    suh, svh = H.rand_signs(r, k), H.rand_signs(r, n)
+    for nb in H.rng(1).choice(n // 128, size=3, replace=False):
+        cols = slice(int(nb) * 128, int(nb) * 128 + 128)
+        want = O.exl3_gemm(A, np.ascontiguousarray(tr[:, int(nb) * 8:int(nb) * 8 + 8]), suh, svh[cols], K, 1, c_fp32=False).astype(np.float32)
+        assert H.gemm_mismatch(got[:, cols], want, GEMM_TOL, True) <= 1.0
 
 
 def test_gemm_deterministic_and_reusable(gemm_ctx):
@@ -246,6 +272,20 @@ def ctx_small_only():
     c.close()
 
 
+@pytest.fixture(scope="module")
+def ctx_tc_only():
+    """A context without the streaming decode kernel: the tcgen05 kernel takes every row count."""
+    import os
+    import exl3b200
+    os.environ["EXL3_B200_NO_DECODE"] = "1"
+    try:
+        c = exl3b200.Ctx(0)
+    finally:
+        del os.environ["EXL3_B200_NO_DECODE"]
+    yield c
+    c.close()
+
+
 def _tc_case(ctx, ctx_small_only, ref, m, k, n, K, cb, c_fp32, seed, oracle=False):
     torch = _torch()
     r = H.rng(seed)
@@ -296,7 +336,8 @@ def test_gemm_tc_step_shape(ctx, ctx_small_only):
 
 
 @pytest.mark.parametrize("m,ns,K,c_fp32", [(200, (512, 256, 256), 4, False), (1052, (1024, 256, 256), 4, False),
-                                            (300, (768, 768), 3, True), (40, (512, 256), 4, False),
+                                            (300, (768, 768), 3, True), (40, (512, 256), 4, False), (5, (512, 256, 256), 4, False), (16, (768, 768), 5, True),
+                                            (1, (5120, 1024, 1024), 4, False),
                                             (260, (512, 384), 4, False)])
 def test_gemm_fanout_equals_separate_calls(ctx, m, ns, K, c_fp32):
     """q/k/v and gate/up style fan-out: one grouped launch must give what separate exl3_gemm calls give, bit for bit

@@ -298,12 +298,12 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
 
 constexpr int GD_MAX_M = 16;
 
-template <int K, int CB, int MT>
+template <int K, int CB, int MT, int VAR>
 cudaError_t launch_decode(const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
 {
     constexpr int bytes = GdSmem<K, MT>::BYTES;
     static bool configured[64] = {};
-    auto kern = gemm_decode_kernel<K, CB, MT>;
+    auto kern = gemm_decode_kernel<K, CB, MT, VAR>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -311,35 +311,49 @@ cudaError_t launch_decode(const CUtensorMap* rmap, const GemmDecodeParams& p, in
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kern<<<grid, GD_THREADS, bytes, st>>>(rmap[0], rmap[1], rmap[2], p);
-    return cudaPeekAtLastError();
+    // launched as a programmatic dependent of the input transform that precedes it on the stream
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GD_THREADS); cfg.dynamicSmemBytes = bytes; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, rmap[0], rmap[1], rmap[2], p);
 }
 
 template <int K, int CB>
-cudaError_t launch_decode_mt(int mt, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+cudaError_t launch_decode_mt(int mt, int var, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
 {
-    return mt == 1 ? launch_decode<K, CB, 1>(rmap, p, grid, st) : launch_decode<K, CB, 2>(rmap, p, grid, st);
+    if constexpr (K == 4) {
+        if (var == 1) return mt == 1 ? launch_decode<K, CB, 1, 1>(rmap, p, grid, st) : launch_decode<K, CB, 2, 1>(rmap, p, grid, st);
+        if constexpr (CB == 1) {
+            if (var == 2) return launch_decode<K, CB, 1, 2>(rmap, p, grid, st);
+            if (var == 4) return launch_decode<K, CB, 1, 4>(rmap, p, grid, st);
+            if (var == 6) return launch_decode<K, CB, 1, 6>(rmap, p, grid, st);
+        }
+    }
+    return mt == 1 ? launch_decode<K, CB, 1, 0>(rmap, p, grid, st) : launch_decode<K, CB, 2, 0>(rmap, p, grid, st);
 }
 
 template <int K>
-cudaError_t launch_decode_cb(int cb, int mt, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+cudaError_t launch_decode_cb(int cb, int mt, int var, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
 {
-    if (cb == 0) return launch_decode_mt<K, 0>(mt, rmap, p, grid, st);
-    if (cb == 1) return launch_decode_mt<K, 1>(mt, rmap, p, grid, st);
-    return launch_decode_mt<K, 2>(mt, rmap, p, grid, st);
+    if (cb == 0) return launch_decode_mt<K, 0>(mt, var, rmap, p, grid, st);
+    if (cb == 1) return launch_decode_mt<K, 1>(mt, var, rmap, p, grid, st);
+    return launch_decode_mt<K, 2>(mt, var, rmap, p, grid, st);
 }
 
-cudaError_t launch_decode_k(int K, int cb, int mt, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+cudaError_t launch_decode_k(int K, int cb, int mt, int var, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
 {
     switch (K) {
-        case 1: return launch_decode_cb<1>(cb, mt, rmap, p, grid, st);
-        case 2: return launch_decode_cb<2>(cb, mt, rmap, p, grid, st);
-        case 3: return launch_decode_cb<3>(cb, mt, rmap, p, grid, st);
-        case 4: return launch_decode_cb<4>(cb, mt, rmap, p, grid, st);
-        case 5: return launch_decode_cb<5>(cb, mt, rmap, p, grid, st);
-        case 6: return launch_decode_cb<6>(cb, mt, rmap, p, grid, st);
-        case 7: return launch_decode_cb<7>(cb, mt, rmap, p, grid, st);
-        default: return launch_decode_cb<8>(cb, mt, rmap, p, grid, st);
+        case 1: return launch_decode_cb<1>(cb, mt, var, rmap, p, grid, st);
+        case 2: return launch_decode_cb<2>(cb, mt, var, rmap, p, grid, st);
+        case 3: return launch_decode_cb<3>(cb, mt, var, rmap, p, grid, st);
+        case 4: return launch_decode_cb<4>(cb, mt, var, rmap, p, grid, st);
+        case 5: return launch_decode_cb<5>(cb, mt, var, rmap, p, grid, st);
+        case 6: return launch_decode_cb<6>(cb, mt, var, rmap, p, grid, st);
+        case 7: return launch_decode_cb<7>(cb, mt, var, rmap, p, grid, st);
+        default: return launch_decode_cb<8>(cb, mt, var, rmap, p, grid, st);
     }
 }
 
@@ -391,7 +405,7 @@ int gemm_decode_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, co
     p.counters = ctx->counters; p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
     gemm_decode_prologue_kernel<<<dim3(8 * mt, nseg), 256, 0, st>>>(A, pa, m, k);
     ctx->launches++;
-    cudaError_t e = launch_decode_k(K, cb, mt, rmap, p, grid, st);
+    cudaError_t e = launch_decode_k(K, cb, mt, ctx->gd_var, rmap, p, grid, st);
     ctx->launches++;
     if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
     return EXL3_OK;
@@ -583,3 +597,10 @@ extern "C" int exl3_gemm_noalloc(exl3_stream stream, const void* A, const void* 
     }
     return EXL3_OK;
 }
+
+#ifdef GD_TRACE
+extern "C" EXL3_API int exl3_debug_gd_trace(unsigned long long* host_out)
+{
+    return cudaMemcpyFromSymbol(host_out, exl3::g_gd_trace, sizeof(unsigned long long) * 148 * 16 * 8) == cudaSuccess ? 0 : -1;
+}
+#endif

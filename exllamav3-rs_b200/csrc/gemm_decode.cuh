@@ -6,7 +6,7 @@
 //   C = H128( fp16(H128(A o suh)/sqrt128) . W ) / sqrt128 o svh
 //
 // Layout of the work.  A CTA has 16 warps = 8 k-slices x 2 column halves.  Its unit of work is (128-column block,
-// 1024-k chunk); inside a unit warp (ks, ch) owns the 8 x 4 weight tiles of k-slice ks (128 k) and column half ch (64
+// 512-k chunk); inside a unit warp (ks, ch) owns the 4 x 4 weight tiles of k-slice ks (64 k) and column half ch (64
 // columns).  Units are ordered column-block-major and dealt to the CTAs as contiguous ranges (stream-K), so a warp walks
 // down k with its accumulators in registers and only meets the other warps when the CTA leaves a column block: the 8
 // k-slices are added in a fixed order through shared memory, a block shared with a neighbouring CTA goes through a
@@ -31,11 +31,26 @@
 
 namespace exl3 {
 
+#ifdef GD_TRACE
+// timeline of one launch (debug builds only): per CTA and warp [start, first data, loop end, end] in nanoseconds
+__device__ unsigned long long g_gd_trace[148 * 16 * 8];
+__device__ __forceinline__ unsigned long long gd_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define GD_STAMP(slot) do { if (lane == 0 && blockIdx.x < 148) g_gd_trace[(blockIdx.x * 16 + warp) * 8 + (slot)] = gd_now(); } while (0)
+#define GD_ACC(slot, v) do { if (lane == 0 && blockIdx.x < 148) g_gd_trace[(blockIdx.x * 16 + warp) * 8 + (slot)] += (v); } while (0)
+#define GD_T0() const unsigned long long gd_t0_ = gd_now()
+#define GD_DT() (gd_now() - gd_t0_)
+#else
+#define GD_STAMP(slot) do { } while (0)
+#define GD_ACC(slot, v) do { } while (0)
+#define GD_T0() do { } while (0)
+#define GD_DT() 0
+#endif
+
 constexpr int GD_WARPS = 16;
 constexpr int GD_THREADS = GD_WARPS * 32;
-constexpr int GD_KSL = 8;                    // k-slices (128 k each) of a CTA unit
-constexpr int GD_UNIT_K = GD_KSL * 128;      // k extent of a unit
-constexpr int GD_SLOT_ROWS = 4;              // tile rows per TMA box
+constexpr int GD_KSL = 8;                    // k-slices of a CTA unit
+constexpr int GD_SLOT_ROWS = 4;              // tile rows per TMA box = one k-slice (64 k)
+constexpr int GD_UNIT_K = GD_KSL * GD_SLOT_ROWS * 16;      // k extent of a unit: 512
 constexpr int GD_SLOT_TILES = 4;             // tiles per row of a box (one column half)
 constexpr int GD_MAX_SEG = 3;
 constexpr int GD_RSTRIDE = 132;              // floats per row of the reduction tiles
@@ -47,7 +62,7 @@ template <int K, int MT> struct GdSmem {
     static constexpr int ROWS = 8 * MT;                                            // batch rows held by the MMAs
     static constexpr int SLOT_BYTES = GD_SLOT_ROWS * GD_SLOT_TILES * 32 * K;       // 512 K
     static constexpr int RED_BYTES = GD_KSL * ROWS * GD_RSTRIDE * 4;               // per-slice partial tiles
-    static constexpr int SC_BYTES = ROWS * GD_RSTRIDE * 4;                         // the summed tile
+    static constexpr int SC_BYTES = 0;
     static constexpr int ROOM = 227 * 1024 - RED_BYTES - SC_BYTES - 1024;
     static constexpr int DEPTH_FIT = ROOM / (GD_WARPS * SLOT_BYTES);
     static constexpr int DEPTH = DEPTH_FIT > 8 ? 8 : DEPTH_FIT;
@@ -103,6 +118,66 @@ __device__ __forceinline__ void lane_states4(const uint32_t* __restrict__ tile, 
     st[0] = __byte_perm(cl, 0, 0x4432);
 }
 
+// One slot = 4 tile rows x 4 tiles of one warp: decode and multiply.  VAR selects the instruction mix of the 4 bpw
+// decode (0: every state cut out of the window and cleaned by a byte permute before its multiply; 1: the four states
+// whose upper neighbour state is already clean in this lane are multiplied as uncleaned 32-bit windows and corrected by a
+// second multiply, x(s) = u*C + D - s_up*(C << 16) with u = s + (s_up << 16): two shifts and four permutes move from the
+// ALU pipe, which limits the kernel, to the multiplier pipe).
+template <int CB> struct GdCodebook {
+    static constexpr uint32_t MUL = CB == 0 ? 89226354u : (CB == 1 ? 0xCBAC1FEDu : 0x83DCD12Du);
+    static constexpr uint32_t ADD = CB == 0 ? 64248484u : 0u;
+    static constexpr uint32_t MUL_UP = 0u - (MUL << 16);          // -(C << 16) mod 2^32
+};
+
+template <int CB>
+__device__ __forceinline__ uint32_t gd_finish(uint32_t x)
+{
+    if constexpr (CB == 2) return __dp4a(x, 0x01010101u, 0xE5FE6400u);
+    else return lop_3inst(x);
+}
+
+template <int K, int CB, int MT, int VAR>
+__device__ __forceinline__ void gd_slot(const uint32_t* __restrict__ sb, int lane, int lane_prev, const uint4 (&af)[MT][GD_SLOT_ROWS],
+                                        float (&acc)[MT][GD_SLOT_TILES][4])
+{
+    #pragma unroll
+    for (int r = 0; r < GD_SLOT_ROWS; ++r) {
+        #pragma unroll
+        for (int c = 0; c < GD_SLOT_TILES; ++c) {
+            const uint32_t* tile = sb + (r * GD_SLOT_TILES + c) * 8 * K;
+            uint32_t y[8];
+            if constexpr (K == 4 && VAR == 1) {
+                using CBK = GdCodebook<CB>;
+                const uint32_t b = tile[lane], a = tile[lane_prev];
+                const uint32_t cw = __funnelshift_r(b, a, 16), c4 = cw >> 4;
+                const uint32_t s3 = __byte_perm(cw, 0, 0x4410), s2 = __byte_perm(c4, 0, 0x4410);
+                const uint32_t s1 = __byte_perm(cw, 0, 0x4421), s0 = __byte_perm(c4, 0, 0x4421);
+                const uint32_t u4 = __funnelshift_r(b, a, 4), u8 = __funnelshift_r(b, a, 8), u12 = __funnelshift_r(b, a, 12);
+                uint32_t x[8];
+                x[3] = s3 * CBK::MUL + CBK::ADD; x[2] = s2 * CBK::MUL + CBK::ADD;
+                x[1] = s1 * CBK::MUL + CBK::ADD; x[0] = s0 * CBK::MUL + CBK::ADD;
+                x[7] = s3 * CBK::MUL_UP + (b * CBK::MUL + CBK::ADD);
+                x[6] = s2 * CBK::MUL_UP + (u4 * CBK::MUL + CBK::ADD);
+                x[5] = s1 * CBK::MUL_UP + (u8 * CBK::MUL + CBK::ADD);
+                x[4] = s0 * CBK::MUL_UP + (u12 * CBK::MUL + CBK::ADD);
+                #pragma unroll
+                for (int q = 0; q < 8; ++q) y[q] = gd_finish<CB>(x[q]);
+            } else {
+                uint32_t st[8];
+                if constexpr (K == 4) lane_states4(tile, lane, lane_prev, st);
+                else lane_states<K>(tile, lane, st);
+                #pragma unroll
+                for (int q = 0; q < 8; ++q) y[q] = decode_raw<CB>(st[q]);
+            }
+            #pragma unroll
+            for (int s = 0; s < MT; ++s) {
+                gd_mma(acc[s][c], y[0], y[4], y[1], y[5], af[s][r].x, af[s][r].y);
+                gd_mma(acc[s][c], y[2], y[6], y[3], y[7], af[s][r].z, af[s][r].w);
+            }
+        }
+    }
+}
+
 // Activations in fragment order.  One CTA per (batch row slot b, tensor): row b < m is transformed as in
 // kernels/quant/hadamard_inner.cuh:93-147 (fp16 pre-scale multiply, fp32 butterflies, one fp16 rounding); slots past m
 // are zero-filled.  Word (set, kslot, r, lane = 4 g + t, w) holds the value of batch row 8 set + g at
@@ -113,6 +188,7 @@ __global__ void __launch_bounds__(256) gemm_decode_prologue_kernel(const half* _
                                                                    int m, int k)
 {
     __shared__ float sh[8];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x, seg = blockIdx.y;
     const half* __restrict__ suh = args.suh[seg];
@@ -167,20 +243,70 @@ __global__ void __launch_bounds__(256) gemm_decode_prologue_kernel(const half* _
     }
 }
 
+// Output transform of one row of a 128-column block held by a warp (lane = 4 consecutive columns): codebook-2 affine
+// map, 128-point Hadamard, svh, store.
+template <int CB>
+__device__ __forceinline__ void gd_store_row(float4 v, int lane, float rowsum, const half* __restrict__ svh, void* Cout, size_t off,
+                                             int col0, int c_fp32)
+{
+    if constexpr (CB == 2) {
+        const float rs = rowsum * GD_MUL1_DELTA;
+        v.x = fmaf(v.x, GD_MUL1_KINV, rs); v.y = fmaf(v.y, GD_MUL1_KINV, rs);
+        v.z = fmaf(v.z, GD_MUL1_KINV, rs); v.w = fmaf(v.w, GD_MUL1_KINV, rs);
+    }
+    if (svh) {
+        float s0 = v.x + v.y, d0 = v.x - v.y, s1 = v.z + v.w, d1 = v.z - v.w;
+        v.x = s0 + s1; v.y = d0 + d1; v.z = s0 - s1; v.w = d0 - d1;
+        #pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            float p0 = __shfl_xor_sync(0xffffffffu, v.x, o), p1 = __shfl_xor_sync(0xffffffffu, v.y, o);
+            float p2 = __shfl_xor_sync(0xffffffffu, v.z, o), p3 = __shfl_xor_sync(0xffffffffu, v.w, o);
+            const bool up = lane & o;
+            v.x = (up ? -v.x : v.x) + p0; v.y = (up ? -v.y : v.y) + p1;
+            v.z = (up ? -v.z : v.z) + p2; v.w = (up ? -v.w : v.w) + p3;
+        }
+        v.x *= GD_R128; v.y *= GD_R128; v.z *= GD_R128; v.w *= GD_R128;
+        uint2 sr = *reinterpret_cast<const uint2*>(svh + col0 + lane * 4);
+        half2 sa2 = *reinterpret_cast<half2*>(&sr.x), sb2 = *reinterpret_cast<half2*>(&sr.y);
+        if (c_fp32) {
+            v.x *= __low2float(sa2); v.y *= __high2float(sa2); v.z *= __low2float(sb2); v.w *= __high2float(sb2);
+            *reinterpret_cast<float4*>((float*)Cout + off) = v;
+        } else {
+            half2 a = __hmul2(__floats2half2_rn(v.x, v.y), sa2), b = __hmul2(__floats2half2_rn(v.z, v.w), sb2);
+            uint2 o2; o2.x = *reinterpret_cast<uint32_t*>(&a); o2.y = *reinterpret_cast<uint32_t*>(&b);
+            *reinterpret_cast<uint2*>((half*)Cout + off) = o2;
+        }
+    } else {
+        if (c_fp32) *reinterpret_cast<float4*>((float*)Cout + off) = v;
+        else {
+            half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+            uint2 o2; o2.x = *reinterpret_cast<uint32_t*>(&a); o2.y = *reinterpret_cast<uint32_t*>(&b);
+            *reinterpret_cast<uint2*>((half*)Cout + off) = o2;
+        }
+    }
+}
+
 // grid = CTAs of the stream-K split (at most one per SM), 512 threads, GdSmem<K, MT>::BYTES of dynamic shared memory.
 // rmap*: the trellis of each tensor as a matrix of 64-bit words [k/16][n/16 * 4K], box 4 rows x 4 tiles.
-template <int K, int CB, int MT>
+//
+// Leaving a column block does not stop the CTA: every warp drops its accumulators into the reduction tile and goes on
+// with the next block; the warp that arrives last adds the 8 k-slices, exchanges partial sums with the neighbouring CTAs
+// where the block is shared, transforms and stores, and then hands the tile back (an mbarrier the other warps test before
+// their next drop, several units later).  While that warp waits on the memory fences and the arrival counter of the
+// exchange, the other three warps of its scheduler use its issue slots.
+template <int K, int CB, int MT, int VAR>
 __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid_constant__ CUtensorMap rmap0,
                                                                    const __grid_constant__ CUtensorMap rmap1,
                                                                    const __grid_constant__ CUtensorMap rmap2,
                                                                    const GemmDecodeParams p)
 {
     using SM = GdSmem<K, MT>;
+    constexpr bool PREFETCH = MT == 1;                  // the next slot's activations are loaded one slot ahead (registers permitting)
     extern __shared__ uint8_t gd_smem_unaligned[];
     uint8_t* smem = gd_smem_unaligned + ((128u - (smem_u32(gd_smem_unaligned) & 127u)) & 127u);
     float* red = reinterpret_cast<float*>(smem + SM::OFF_RED);
-    float* sc = reinterpret_cast<float*>(smem + SM::OFF_SC);
-    __shared__ int s_flag;
+    __shared__ int s_drops;
+    __shared__ __align__(8) uint64_t s_red_free;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -192,6 +318,10 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
     const int nunits = (int)(u1 - u0);
     const int mrows = p.m;
 
+    GD_STAMP(0);
+#ifdef GD_TRACE
+    if (lane == 0 && blockIdx.x < 148) { g_gd_trace[(blockIdx.x * 16 + warp) * 8 + 4] = 0; g_gd_trace[(blockIdx.x * 16 + warp) * 8 + 5] = 0; g_gd_trace[(blockIdx.x * 16 + warp) * 8 + 6] = 0; }
+#endif
     uint8_t* ring = smem + SM::OFF_RING + warp * SM::DEPTH * SM::SLOT_BYTES;
     const uint32_t ring_u32 = smem_u32(ring);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR) + warp * SM::DEPTH;
@@ -199,24 +329,24 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
     if (lane == 0) {
         #pragma unroll
         for (int s = 0; s < SM::DEPTH; ++s) mbar_init(&bars[s], 1);
+        if (warp == 0) { mbar_init(&s_red_free, 1); s_drops = 0; }
         mbar_fence_init();
     }
-    __syncwarp();
+    __syncthreads();
 
     // Units are walked with two cursors (the one being multiplied and the one being requested, DEPTH - 1 slots ahead),
     // each stepped one unit at a time: (column block, k chunk) without a division in the loop.
     const int nbg0 = (int)(u0 / KC), kc0 = (int)(u0 - (long long)nbg0 * KC);
     auto seg_of = [&](int nbg) -> int { return (nbg >= p.blk_end[0]) + (nbg >= p.blk_end[1]); };
     auto col0_of = [&](int nbg, int seg) -> int { return (nbg - (seg == 0 ? 0 : (seg == 1 ? p.blk_end[0] : p.blk_end[1]))) * 128; };
-    // slot j = 2 i + h of this warp: tile rows [64 kc + 8 ks + 4 h, +4) of unit i; a unit whose chunk ends before this
-    // warp's k-slice has no slots for it
-    auto slot_active = [&](int kc) -> bool { return (kc * GD_UNIT_K + ks * 128) < p.k; };
-    const int nslots = 2 * nunits;
+    // unit i of this CTA is one slot of this warp: tile rows [32 kc + 4 ks, +4); a unit whose chunk ends before this
+    // warp's k-slice has no slot for it
+    auto slot_active = [&](int kc) -> bool { return (kc * GD_UNIT_K + ks * (GD_SLOT_ROWS * 16)) < p.k; };
     int issued = 0, consumed = 0;
     int j_iss = 0, nbg_iss = nbg0, kc_iss = kc0;
     bool failed = false;
     auto issue_next = [&]() {
-        if (j_iss >= nslots) return;
+        if (j_iss >= nunits) return;
         if (slot_active(kc_iss) && !failed) {
             if (lane == 0) {
                 const int seg = seg_of(nbg_iss);
@@ -225,15 +355,33 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
                 const uint32_t bar = bars_u32 + 8u * s;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)SM::SLOT_BYTES) : "memory");
                 gd_tma_load_2d(ring_u32 + s * SM::SLOT_BYTES, rmap, ((col0_of(nbg_iss, seg) >> 4) + ch * GD_SLOT_TILES) * 4 * K,
-                               kc_iss * (GD_UNIT_K / 16) + ks * 8 + (j_iss & 1) * GD_SLOT_ROWS, bar);
+                               kc_iss * (GD_UNIT_K / 16) + ks * GD_SLOT_ROWS, bar);
             }
             ++issued;
         }
-        if (j_iss & 1) { if (++kc_iss == KC) { kc_iss = 0; ++nbg_iss; } }
+        if (++kc_iss == KC) { kc_iss = 0; ++nbg_iss; }
         ++j_iss;
     };
-    #pragma unroll 1
-    for (int j = 0; j < SM::DEPTH - 1; ++j) issue_next();
+    // Only the first slot of every warp is requested up front.  Sixteen warps per SM that queue their whole ring at once
+    // put 19 MB in flight across the chip and the first useful byte arrives when most of that has landed (4.5 us measured);
+    // the rest of the ring is requested as soon as the first slot is in, while it is being multiplied.
+    issue_next();
+
+    // activations of a unit's slot: batch rows 8 set + g, k = 64 kslot + 16 r + {2t, 2t+1, 2t+8, 2t+9} (a k-slice past
+    // the end of a ragged last chunk reads the last valid slot; it is never used)
+    const int kslot_max = p.k / 64 - 1;
+    auto load_af = [&](int nbg_, int kc_, uint4 (&af)[MT][GD_SLOT_ROWS]) {
+        const int seg = seg_of(nbg_);
+        const uint4* afr = (seg == 0 ? p.a_frag[0] : (seg == 1 ? p.a_frag[1] : p.a_frag[2]));
+        const int kslot = min(kc_ * GD_KSL + ks, kslot_max);
+        #pragma unroll
+        for (int s = 0; s < MT; ++s)
+            #pragma unroll
+            for (int r = 0; r < GD_SLOT_ROWS; ++r) {
+                if constexpr ((VAR & 2) != 0) af[s][r] = make_uint4(0x3c003c00u + kslot, 0x38003800u + r, 0x34003400u + lane, 0x3c003c00u);
+                else af[s][r] = __ldg(afr + (((size_t)s * (p.k / 64) + kslot) * 4 + r) * 32 + lane);
+            }
+    };
 
     float acc[MT][GD_SLOT_TILES][4];
     #pragma unroll
@@ -243,56 +391,55 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
             #pragma unroll
             for (int e = 0; e < 4; ++e) acc[s][c][e] = 0.0f;
 
+    // The launch may overlap the tail of the kernel that writes the activations (programmatic dependent launch): the
+    // requests for the codes above do not depend on it, everything below does.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
     const int lane_prev = (lane + 31) & 31;
     int nbg = nbg0, kc = kc0 - 1;
+    int events = 0;                                     // column blocks this CTA has left so far
+    uint4 af_next[MT][GD_SLOT_ROWS];
+    if constexpr (PREFETCH) { if (nunits > 0) load_af(nbg0, kc0, af_next); }
     #pragma unroll 1
     for (int i = 0; i < nunits; ++i) {
         if (++kc == KC) { kc = 0; ++nbg; }
-        const int seg = seg_of(nbg);
-        const int n0 = col0_of(nbg, seg);
-        const bool active = slot_active(kc);
-        const uint4* afr = (seg == 0 ? p.a_frag[0] : (seg == 1 ? p.a_frag[1] : p.a_frag[2]));
-        #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-            // the slot freed by the previous iteration is refilled first (all lanes have consumed its words)
-            __syncwarp();
-            issue_next();
-            if (!active || failed) continue;
-            // this slot's activations: batch rows 8 set + g, k = 64 kslot + 16 r + {2t, 2t+1, 2t+8, 2t+9}
-            const int kslot = kc * (GD_UNIT_K / 64) + ks * 2 + h;
-            uint4 af[MT][GD_SLOT_ROWS];
+        uint4 af[MT][GD_SLOT_ROWS];
+        if constexpr (PREFETCH) {
             #pragma unroll
-            for (int s = 0; s < MT; ++s)
-                #pragma unroll
-                for (int r = 0; r < GD_SLOT_ROWS; ++r)
-                    af[s][r] = __ldg(afr + (((size_t)s * (p.k / 64) + kslot) * 4 + r) * 32 + lane);
-            const int s_idx = consumed % SM::DEPTH;
-            const bool ok = mbar_wait_sleep_warp(&bars[s_idx], (consumed / SM::DEPTH) & 1);
-            ++consumed;
-            if (!ok) { failed = true; continue; }
-            const uint32_t* sb = reinterpret_cast<const uint32_t*>(ring + s_idx * SM::SLOT_BYTES);
-            #pragma unroll
-            for (int r = 0; r < GD_SLOT_ROWS; ++r) {
-                #pragma unroll
-                for (int c = 0; c < GD_SLOT_TILES; ++c) {
-                    uint32_t st[8], y[8];
-                    if constexpr (K == 4) lane_states4(sb + (r * GD_SLOT_TILES + c) * 8 * K, lane, lane_prev, st);
-                    else lane_states<K>(sb + (r * GD_SLOT_TILES + c) * 8 * K, lane, st);
-                    #pragma unroll
-                    for (int q = 0; q < 8; ++q) y[q] = decode_raw<CB>(st[q]);
-                    #pragma unroll
-                    for (int s = 0; s < MT; ++s) {
-                        gd_mma(acc[s][c], y[0], y[4], y[1], y[5], af[s][r].x, af[s][r].y);
-                        gd_mma(acc[s][c], y[2], y[6], y[3], y[7], af[s][r].z, af[s][r].w);
-                    }
-                }
+            for (int r = 0; r < GD_SLOT_ROWS; ++r) af[0][r] = af_next[0][r];
+            if (i + 1 < nunits) {
+                const bool wrap = kc + 1 == KC;
+                load_af(wrap ? nbg + 1 : nbg, wrap ? 0 : kc + 1, af_next);
             }
+        }
+        if (!slot_active(kc)) { while (issued - consumed < SM::DEPTH - 1 && j_iss < nunits) issue_next(); }
+        if (slot_active(kc) && !failed) {
+            if constexpr (!PREFETCH) load_af(nbg, kc, af);
+            const int s_idx = consumed % SM::DEPTH;
+            GD_T0();
+            const bool ok = mbar_wait_sleep_warp(&bars[s_idx], (consumed / SM::DEPTH) & 1);
+            if (i > 0) GD_ACC(4, GD_DT());
+            ++consumed;
+            if (i == 0) GD_STAMP(1);
+            // top the ring up: every slot but the one about to be multiplied may be in flight (the slot freed by the
+            // previous iteration has been read by all lanes: they are past the wait above)
+            while (issued - consumed < SM::DEPTH - 1 && j_iss < nunits) issue_next();
+            if (ok) gd_slot<K, CB, MT, VAR>(reinterpret_cast<const uint32_t*>(ring + s_idx * SM::SLOT_BYTES), lane, lane_prev, af, acc);
+            else failed = true;
         }
 
         const bool block_done = kc == KC - 1 || i == nunits - 1;
+        if (i == nunits - 1) GD_STAMP(2);
         if (!block_done) continue;
+        if constexpr ((VAR & 4) != 0) {
+            if (acc[0][0][0] == 123.456f) reinterpret_cast<float*>(p.C[0])[tid] = acc[0][1][1] + acc[0][2][2] + acc[0][3][3];
+            continue;
+        }
 
-        // ---- the CTA leaves column block nbg: per-slice tiles -> shared memory, then added in slice order
+        // ---- the CTA leaves column block nbg.  The reduction tile is free again once the warp that finished the previous
+        // block has read it (that was several units ago unless this is the CTA's last, short block).
+        if (events > 0 && !mbar_wait_sleep_warp(&s_red_free, (events - 1) & 1)) failed = true;
+        ++events;
         #pragma unroll
         for (int s = 0; s < MT; ++s)
             #pragma unroll
@@ -302,110 +449,94 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
                 dst[8] = acc[s][c][2]; dst[GD_RSTRIDE + 8] = acc[s][c][3];
                 acc[s][c][0] = acc[s][c][1] = acc[s][c][2] = acc[s][c][3] = 0.0f;
             }
-        if (__syncthreads_or(failed)) { failed = true; break; }
-        for (int e = tid; e < SM::ROWS * 32; e += GD_THREADS) {
-            const int row = e >> 5, c4 = e & 31;
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+            __threadfence_block();
+            last = atomicAdd(&s_drops, 1) == GD_WARPS - 1;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) continue;
+
+        // ---- this warp arrived last: it finishes the block on its own
+        GD_T0();
+        if (lane == 0) s_drops = 0;
+        __threadfence_block();
+        const int seg = seg_of(nbg);
+        const int n0 = col0_of(nbg, seg);
+        const half* svh = seg == 0 ? p.svh[0] : (seg == 1 ? p.svh[1] : p.svh[2]);
+        void* Cout = seg == 0 ? p.C[0] : (seg == 1 ? p.C[1] : p.C[2]);
+        const int n = seg == 0 ? p.n[0] : (seg == 1 ? p.n[1] : p.n[2]);
+        const float* rsum = seg == 0 ? p.rowsum[0] : (seg == 1 ? p.rowsum[1] : p.rowsum[2]);
+        // sum of the 8 k-slices of one row, in slice order; lane = 4 consecutive columns
+        auto row_sum = [&](int row) -> float4 {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
             #pragma unroll
             for (int s = 0; s < GD_KSL; ++s) {
-                const float4 v = *reinterpret_cast<const float4*>(red + ((size_t)s * SM::ROWS + row) * GD_RSTRIDE + c4 * 4);
+                const float4 v = *reinterpret_cast<const float4*>(red + ((size_t)s * SM::ROWS + row) * GD_RSTRIDE + lane * 4);
                 a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
             }
-            *reinterpret_cast<float4*>(sc + row * GD_RSTRIDE + c4 * 4) = a;
-        }
-        __syncthreads();
-
+            return a;
+        };
         // CTAs that own a part of this block: those whose unit range meets [nbg * KC, (nbg + 1) * KC)
         const long long first = (long long)nbg * KC;
         auto owner = [&](long long u) -> int { return (int)(((u + 1) * G + total - 1) / total - 1); };
         const int c_first = owner(first), c_last = owner(first + KC - 1);
         const int ncontrib = c_last - c_first + 1;
-        bool finish = true;
-        if (ncontrib > 1) {
+        if (ncontrib == 1) {
+            for (int row = 0; row < mrows; ++row)
+                gd_store_row<CB>(row_sum(row), lane, CB == 2 ? rsum[row] : 0.f, svh, Cout, (size_t)row * n + n0 + lane * 4, n0, p.c_fp32);
+            if (lane == 0) mbar_arrive(&s_red_free);
+        } else {
             // a CTA shares at most its first and its last column block: slot 0 and slot 1 of its pair
             auto slot_of = [&](int cta) -> float* {
                 const long long fb = (total * cta / G) / KC;
                 return p.partial + ((size_t)cta * 2 + (fb == nbg ? 0 : 1)) * mrows * 128;
             };
             float* mine = slot_of(blockIdx.x);
-            for (int e = tid; e < mrows * 32; e += GD_THREADS) {
-                const int row = e >> 5, c4 = e & 31;
-                *reinterpret_cast<float4*>(mine + row * 128 + c4 * 4) = *reinterpret_cast<const float4*>(sc + row * GD_RSTRIDE + c4 * 4);
+            for (int row = 0; row < mrows; ++row)
+                *reinterpret_cast<float4*>(mine + row * 128 + lane * 4) = row_sum(row);
+            if (lane == 0) mbar_arrive(&s_red_free);              // the tile has been read: the other warps may drop again
+            __syncwarp();
+            // one arrival per CTA: the release half publishes this warp's partial sums (ordered before it by the warp
+            // barrier above), the acquire half makes the other owners' visible to the CTA that arrives last
+            int fin = 0;
+            if (lane == 0) {
+                int old;
+                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + nbg) : "memory");
+                fin = old == ncontrib - 1;
+                if (fin) p.counters[nbg] = 0;
             }
-            __threadfence();
-            __syncthreads();
-            if (tid == 0) {
-                const int old = atomicAdd(&p.counters[nbg], 1);
-                s_flag = (old == ncontrib - 1);
-                if (s_flag) p.counters[nbg] = 0;
-            }
-            __syncthreads();
-            finish = s_flag != 0;
-            if (finish) {
-                __threadfence();
-                for (int e = tid; e < mrows * 32; e += GD_THREADS) {
-                    const int row = e >> 5, c4 = e & 31;
-                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int s = c_first; s <= c_last; ++s) {           // owner order: independent of arrival order
-                        const float4 v = __ldcg(reinterpret_cast<const float4*>(slot_of(s) + row * 128 + c4 * 4));
-                        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
-                    }
-                    *reinterpret_cast<float4*>(sc + row * GD_RSTRIDE + c4 * 4) = a;
-                }
-                __syncthreads();
-            }
-        }
-        if (finish) {
-            // output transform: one warp per row, lane holds 4 consecutive columns
-            const half* svh = seg == 0 ? p.svh[0] : (seg == 1 ? p.svh[1] : p.svh[2]);
-            void* Cout = seg == 0 ? p.C[0] : (seg == 1 ? p.C[1] : p.C[2]);
-            const int n = seg == 0 ? p.n[0] : (seg == 1 ? p.n[1] : p.n[2]);
-            for (int row = warp; row < mrows; row += GD_WARPS) {
-                float4 v = *reinterpret_cast<const float4*>(sc + row * GD_RSTRIDE + lane * 4);
-                if constexpr (CB == 2) {
-                    const float* rsum = seg == 0 ? p.rowsum[0] : (seg == 1 ? p.rowsum[1] : p.rowsum[2]);
-                    const float rs = rsum[row] * GD_MUL1_DELTA;
-                    v.x = fmaf(v.x, GD_MUL1_KINV, rs); v.y = fmaf(v.y, GD_MUL1_KINV, rs);
-                    v.z = fmaf(v.z, GD_MUL1_KINV, rs); v.w = fmaf(v.w, GD_MUL1_KINV, rs);
-                }
-                const size_t off = (size_t)row * n + n0 + lane * 4;
-                if (svh) {
-                    float s0 = v.x + v.y, d0 = v.x - v.y, s1 = v.z + v.w, d1 = v.z - v.w;
-                    v.x = s0 + s1; v.y = d0 + d1; v.z = s0 - s1; v.w = d0 - d1;
+            fin = __shfl_sync(0xffffffffu, fin, 0);
+            if (fin) {
+                __syncwarp();
+                // all owners' partial sums of up to 8 rows are requested before the first is used
+                for (int row0 = 0; row0 < mrows; row0 += 8) {
+                    float4 a[8];
                     #pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        float p0 = __shfl_xor_sync(0xffffffffu, v.x, o), p1 = __shfl_xor_sync(0xffffffffu, v.y, o);
-                        float p2 = __shfl_xor_sync(0xffffffffu, v.z, o), p3 = __shfl_xor_sync(0xffffffffu, v.w, o);
-                        const bool up = lane & o;
-                        v.x = (up ? -v.x : v.x) + p0; v.y = (up ? -v.y : v.y) + p1;
-                        v.z = (up ? -v.z : v.z) + p2; v.w = (up ? -v.w : v.w) + p3;
+                    for (int r = 0; r < 8; ++r) a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int s = c_first; s <= c_last; ++s) {           // owner order: independent of arrival order
+                        const float* src = slot_of(s) + lane * 4;
+                        #pragma unroll
+                        for (int r = 0; r < 8; ++r)
+                            if (row0 + r < mrows) {
+                                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (row0 + r) * 128));
+                                a[r].x += v.x; a[r].y += v.y; a[r].z += v.z; a[r].w += v.w;
+                            }
                     }
-                    v.x *= GD_R128; v.y *= GD_R128; v.z *= GD_R128; v.w *= GD_R128;
-                    uint2 sr = *reinterpret_cast<const uint2*>(svh + n0 + lane * 4);
-                    half2 sa2 = *reinterpret_cast<half2*>(&sr.x), sb2 = *reinterpret_cast<half2*>(&sr.y);
-                    if (p.c_fp32) {
-                        v.x *= __low2float(sa2); v.y *= __high2float(sa2); v.z *= __low2float(sb2); v.w *= __high2float(sb2);
-                        *reinterpret_cast<float4*>((float*)Cout + off) = v;
-                    } else {
-                        half2 a = __hmul2(__floats2half2_rn(v.x, v.y), sa2), b = __hmul2(__floats2half2_rn(v.z, v.w), sb2);
-                        uint2 o2; o2.x = *reinterpret_cast<uint32_t*>(&a); o2.y = *reinterpret_cast<uint32_t*>(&b);
-                        *reinterpret_cast<uint2*>((half*)Cout + off) = o2;
-                    }
-                } else {
-                    if (p.c_fp32) *reinterpret_cast<float4*>((float*)Cout + off) = v;
-                    else {
-                        half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
-                        uint2 o2; o2.x = *reinterpret_cast<uint32_t*>(&a); o2.y = *reinterpret_cast<uint32_t*>(&b);
-                        *reinterpret_cast<uint2*>((half*)Cout + off) = o2;
-                    }
+                    #pragma unroll
+                    for (int r = 0; r < 8; ++r)
+                        if (row0 + r < mrows)
+                            gd_store_row<CB>(a[r], lane, CB == 2 ? rsum[row0 + r] : 0.f, svh, Cout, (size_t)(row0 + r) * n + n0 + lane * 4, n0, p.c_fp32);
                 }
             }
         }
-        __syncthreads();      // the reduction tiles are reused by the next column block
+        GD_ACC(5, GD_DT());
     }
+    GD_STAMP(3);
     // A wait that ran out: no new copies are issued after it, but boxes already requested may still land; give them the
     // same bounded time before the CTA's shared memory is released.
-    if (failed) {
+    if (__syncthreads_or(failed)) {
         while (consumed < issued) {
             mbar_wait_sleep_warp(&bars[consumed % SM::DEPTH], (consumed / SM::DEPTH) & 1, 1u << 12);
             ++consumed;

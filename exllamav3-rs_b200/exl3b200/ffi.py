@@ -9,7 +9,7 @@ import os
 import torch
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG, "libexl3b200.so")
+LIB_PATH = os.environ.get("EXL3_B200_LIB") or os.path.join(_PKG, "libexl3b200.so")
 
 ROPE_NONE, ROPE_GPTJ, ROPE_NEOX = 0, 1, 2   # src/ffi.rs:217-219
 

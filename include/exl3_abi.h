@@ -297,6 +297,43 @@ EXL3_API int exl3_step_build_descriptors(exl3_ctx* ctx, exl3_stream stream, cons
 EXL3_API int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_model* model, const exl3_batch* batch,
                                void* scratch, size_t scratch_bytes, int64_t* out_tokens, float* logits);
 
+/* --------------------------------------------------------------------------------------- pools and page table
+ * The reference keeps the paged KV pools and the page allocator on the Rust side: PagedCache::new / QuantPagedCache::new
+ * (src/paged.rs:18-92) allocate one K and one V plane per layer, PageTable (src/paged.rs:330-506) hands out 256-token
+ * pages from a free list, counts references per physical page and shares complete prompt-prefix pages between
+ * sequences through chained content hashes (least recently released hashed pages are repurposed when the free list is
+ * empty).  A host that has no tensor library gets the same objects here; the page table is host state, the planes are
+ * device memory owned by the pool. */
+typedef struct exl3_pool exl3_pool;
+/* k_bits = v_bits = 0: fp16 planes [pages,256,nkv,hd]; 2..8: int32 codes [pages,256,groups*bits] + fp16 scales
+ * [pages,256,groups], groups = nkv*hd/32.  All planes start zeroed.  EXL3_ERR_NOMEM when the device cannot hold them. */
+EXL3_API int  exl3_pool_create(int device, int n_layers, int pages, int nkv, int hd, int k_bits, int v_bits, exl3_pool** out);
+EXL3_API void exl3_pool_destroy(exl3_pool* pool);
+/* device pointers of one layer: fp16 pools -> *k, *v (sk, sv NULL); quantised -> *k = codes of K, *sk = scales of K, ... */
+EXL3_API int  exl3_pool_layer(const exl3_pool* pool, int layer, void** k, void** v, void** sk, void** sv);
+EXL3_API int  exl3_pool_num_pages(const exl3_pool* pool);
+/* pages that can be handed out: free + unreferenced hashed ones (PageTable::num_free) */
+EXL3_API int  exl3_pool_num_free(const exl3_pool* pool);
+EXL3_API int  exl3_pool_refcount(const exl3_pool* pool, int page);
+/* PageTable::alloc: n fresh pages (reference count 1 each) into out_pages (host), or EXL3_ERR_NOMEM and nothing taken */
+EXL3_API int  exl3_pool_alloc(exl3_pool* pool, int n, int32_t* out_pages);
+/* PageTable::alloc_prefix: pages for a prompt of n_ids tokens plus gen_reserve tokens.  With sharing switched on
+ * (exl3_pool_set_dedup) the complete leading pages whose chained hash is registered are shared instead of taken fresh;
+ * *out_matched_tokens = tokens already resident in them.  out_block (host) receives *out_count page ids. */
+EXL3_API int  exl3_pool_alloc_prefix(exl3_pool* pool, const int64_t* prompt_ids, int n_ids, int gen_reserve, int32_t* out_block,
+                                     int block_capacity, int* out_count, int64_t* out_matched_tokens);
+EXL3_API void exl3_pool_set_dedup(exl3_pool* pool, int on);
+/* PageTable::register_page_hash: `page` now holds the complete 256-token span token_ids (host); prev_page = the page
+ * before it in the sequence or -1.  Idempotent; spans of other lengths are ignored. */
+EXL3_API int  exl3_pool_register_page_hash(exl3_pool* pool, int page, int prev_page, const int64_t* token_ids, int n_ids);
+/* PageTable::release: drop one reference per listed page; unreferenced pages go back to the free list, or, if they
+ * carry a hash, to the reclaimable queue */
+EXL3_API int  exl3_pool_release(exl3_pool* pool, const int32_t* pages, int n);
+/* PageTable::drain_evicted: hashed pages that were repurposed since the last call; returns how many were written */
+EXL3_API int  exl3_pool_drain_evicted(exl3_pool* pool, int32_t* out_pages, int capacity);
+/* PageTable::prefix_stats */
+EXL3_API void exl3_pool_prefix_stats(const exl3_pool* pool, uint64_t* cached_tokens, uint64_t* prompt_tokens);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,5 +1,6 @@
 // Context, CUDA-graph and memory entry points of libexl3b200.so.
 #include "common.cuh"
+#include "async_copy.cuh"
 #include <new>
 #include <stdlib.h>
 
@@ -26,7 +27,6 @@ extern "C" int exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** ou
     ctx->mma_attn = 1;
     ctx->use_tc = getenv("EXL3_B200_NO_TC") ? 0 : 1;
     ctx->use_pair = getenv("EXL3_B200_NO_PAIR") ? 0 : 1;
-    ctx->gd_var = getenv("EXL3_B200_GD_VAR") ? atoi(getenv("EXL3_B200_GD_VAR")) : 0;
     ctx->use_decode = (getenv("EXL3_B200_NO_DECODE") || getenv("EXL3_B200_NO_TC")) ? 0 : 1;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete ctx; cudaGetLastError(); return EXL3_ERR_CUDA; }
@@ -87,6 +87,9 @@ extern "C" int exl3_ctx_poll_status(exl3_ctx* ctx, exl3_stream stream)
         return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e));
     }
     if (h != 0) {
+        // CTAs that gave up may have left arrival counters of shared column blocks half-way: back to the all-zero state
+        // every GEMM launch expects
+        cudaMemsetAsync(ctx->counters, 0, (size_t)ctx->n_counters * sizeof(int), st);
         cudaMemsetAsync(ctx->status, 0, sizeof(int), st);
         cudaStreamSynchronize(st);
         char buf[128];
@@ -94,6 +97,31 @@ extern "C" int exl3_ctx_poll_status(exl3_ctx* ctx, exl3_stream stream)
         return exl3_fail(ctx, EXL3_ERR_DEVICE_WAIT, buf);
     }
     return EXL3_OK;
+}
+
+// Self-test of the bounded-wait path every kernel of the library uses: one thread waits, with the library's own helper and
+// a small poll limit, on an mbarrier that nothing ever arrives on; the wait gives up, the kernel records status 1 in the
+// context's status word and returns normally (no trap, no fault).  exl3_ctx_poll_status then reports
+// EXL3_ERR_DEVICE_WAIT and the context stays usable.
+namespace {
+__global__ void selftest_wait_kernel(int* status, uint32_t polls)
+{
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        exl3::mbar_init(&bar, 1);
+        exl3::mbar_fence_init();
+        if (!exl3::mbar_wait(&bar, 0, polls)) atomicExch(status, 1);
+    }
+}
+}  // namespace
+
+extern "C" int exl3_selftest_bounded_wait(exl3_ctx* ctx, exl3_stream stream, uint32_t polls)
+{
+    if (!ctx) return EXL3_ERR_INVALID;
+    if (polls == 0 || polls > (1u << 20)) return exl3_fail(ctx, EXL3_ERR_INVALID, "selftest_bounded_wait: polls must be 1..2^20");
+    selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctx->status, polls);
+    ctx->launches++;
+    return exl3_check_launch(ctx, "selftest_bounded_wait");
 }
 
 extern "C" void exl3_set_mma_attn(exl3_ctx* ctx, int on) { if (ctx) ctx->mma_attn = on ? 1 : 0; }

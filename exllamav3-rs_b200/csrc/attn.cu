@@ -16,7 +16,7 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
                                                          const int32_t* __restrict__ cu_q, int bsz, int q_len,
                                                          int kv_append, int G, int rows_per_cta, int rows_lo, int rows_hi, int chunk_mult, int target_items,
                                                          int max_items, AttnPlan* plan, AttnItem* items, int* seq_base,
-                                                         int* seq_splits)
+                                                         int* seq_splits, int* status)
 {
     __shared__ long long s_total;
     __shared__ int s_scan[1024];
@@ -78,6 +78,9 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
     if (tid == 0) {
         plan->n_items = s_carry < max_items ? s_carry : max_items;
         plan->chunk = chunk;
+        // the host sizes the list from bounds on the batch; a list that does not fit would silently drop work, so it is
+        // reported through the status word like a device-side wait that ran out
+        if (s_carry > max_items) atomicExch(status, 3);
     }
 }
 
@@ -245,7 +248,7 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
 
     if (!(keep && ctx->plan_valid[cls])) {
         attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, rows_lo, rows_hi,
-                                              use_tc ? ATC_TN : AT_TK, target_items, max_items, plan, items, seq_base, seq_splits);
+                                              use_tc ? ATC_TN : AT_TK, target_items, max_items, plan, items, seq_base, seq_splits, ctx->status);
         ctx->launches++;
         if (keep) ctx->plan_valid[cls] = 1;
     }

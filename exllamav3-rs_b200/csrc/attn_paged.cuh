@@ -254,6 +254,13 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                 uint8_t* dk = smem_raw + AT_STAGES * SM::STAGE;
                 uint8_t* dv = dk + SM::TILE;
                 const uint8_t* raw = smem_raw + stage * SM::STAGE;
+                if (p.k_bits == 4 && p.v_bits == 4) {
+                    static_assert(!QUANT || D == 128, "the 4-bit path scales one 128-wide head per half warp");
+                    #pragma unroll 4
+                    for (int key = warp; key < AT_TK; key += 4)
+                        dequant4_kv_norot(raw + key * SM::RAW_ROW, raw + SM::RAW + key * SM::RAW_ROW, (D / 32) * 32,
+                                          reinterpret_cast<half*>(dk + key * SM::ROWB), reinterpret_cast<half*>(dv + key * SM::ROWB));
+                } else
                 #pragma unroll 4                                   // independent keys in flight: the chain per key is latency-bound
                 for (int key = warp; key < AT_TK; key += 4) {
                     #pragma unroll

@@ -28,7 +28,6 @@ struct exl3_ctx {
     int mma_attn;
     int use_tc;             // 1: tcgen05 GEMM for large M (default), 0: small-M kernel in passes (for A/B runs)
     int use_decode;         // 1: the streaming decode kernel takes calls of up to 16 rows (default), 0: they go the way of larger row counts
-    int gd_var;             // instruction-mix variant of the decode kernel (A/B runs)
     int use_pair;           // 1: the tcgen05 GEMM runs on CTA pairs (cta_group::2, default), 0: one CTA per tile
     // Work lists of the attention kernels kept across the layers of one exl3_step_forward call (they depend on the batch's
     // lengths only, not on the layer): slot 0 = decode class, slot 1 = long class.  plan_keep is set for the duration of a

@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(const TI* __restrict__ x
 // RMSNorm (value rounded to fp16, weight + bias in fp16, fp16 product), then the rotation in fp32 with __sinf/__cosf of
 // inv_freq[t] * float(pos), rounded to fp16.
 template <int EPL>   // elements per lane = hd / 32
-__global__ void __launch_bounds__(256) rope_kernel(half* __restrict__ q, half* __restrict__ k,
+__global__ void __launch_bounds__(256) rope_kernel(const half* q, const half* k, half* out_q, half* out_k,
                                                    const float* __restrict__ inv_freq, int n_freq, uint32_t position,
                                                    const int32_t* __restrict__ positions,
                                                    const int32_t* __restrict__ row_pos, const half* __restrict__ q_norm,
@@ -172,9 +172,9 @@ __global__ void __launch_bounds__(256) rope_kernel(half* __restrict__ q, half* _
     const int heads = nq + nk;
     if (gw >= (long long)rows * heads) return;
     const int row = (int)(gw / heads), h = (int)(gw % heads);
-    half* p; const half* nw;
-    if (h < nq) { p = q + ((size_t)row * nq + h) * HD; nw = q_norm; }
-    else        { p = k + ((size_t)row * nk + (h - nq)) * HD; nw = k_norm; }
+    const half* p; half* po; const half* nw;
+    if (h < nq) { p = q + ((size_t)row * nq + h) * HD; po = out_q + ((size_t)row * nq + h) * HD; nw = q_norm; }
+    else        { p = k + ((size_t)row * nk + (h - nq)) * HD; po = out_k + ((size_t)row * nk + (h - nq)) * HD; nw = k_norm; }
     int pos;
     if (row_pos) pos = row_pos[row];
     else         pos = (row % seq) + (positions ? positions[row / seq] : (int)position);
@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(256) rope_kernel(half* __restrict__ q, half* _
         }
     }
     #pragma unroll
-    for (int i = 0; i < EPL; ++i) p[lane + 32 * i] = x[i];
+    for (int i = 0; i < EPL; ++i) po[lane + 32 * i] = x[i];
 }
 
 // --------------------------------------------------------------------------------------------- activations
@@ -395,7 +395,7 @@ extern "C" int exl3_rms_norm_res_in(exl3_ctx* ctx, exl3_stream stream, const voi
     return rms_norm_impl(ctx, stream, x, x_fp32, w, y, y_fp32, r, eps, constant_bias, constant_scale, rows, dim);
 }
 
-extern "C" int exl3_rope(exl3_ctx* ctx, exl3_stream stream, void* q, void* k, const float* inv_freq, int n_freq,
+extern "C" int exl3_rope(exl3_ctx* ctx, exl3_stream stream, void* q, void* out_q, void* k, void* out_k, const float* inv_freq, int n_freq,
                          uint32_t position, const int32_t* positions, const int32_t* row_pos, const void* q_norm,
                          const void* k_norm, float norm_eps, float norm_constant_bias, int rope_mode,
                          float attn_factor, int bsz, int seq, int nq, int nk, int hd)
@@ -416,7 +416,7 @@ extern "C" int exl3_rope(exl3_ctx* ctx, exl3_stream stream, void* q, void* k, co
     cudaStream_t st = (cudaStream_t)stream;
     const int nk_eff = k ? nk : 0;
 #define ROPE_LAUNCH(E)                                                                                                 \
-    rope_kernel<E><<<grid, 256, 0, st>>>((half*)q, (half*)k, inv_freq, n_freq, position, positions, row_pos,           \
+    rope_kernel<E><<<grid, 256, 0, st>>>((const half*)q, (const half*)k, (half*)(out_q ? out_q : q), (half*)(out_k ? out_k : k), inv_freq, n_freq, position, positions, row_pos, \
                                          (const half*)q_norm, (const half*)k_norm, norm_eps, norm_constant_bias,       \
                                          rope_mode, attn_factor, rows, seq, nq, nk_eff)
     if (hd == 64) ROPE_LAUNCH(2); else if (hd == 128) ROPE_LAUNCH(4); else ROPE_LAUNCH(8);

@@ -83,21 +83,14 @@ cudaError_t launch_small(GemmSmallParams& p, int num_sms, size_t partial_room, f
     const long long total = (long long)(p.n / 128) * NST;
     long long grid = (long long)num_sms * ctas_per_sm;
     if (grid > total) grid = total;
-    // a column block is shared by at most ceil(NST / units-per-CTA) + 1 CTAs; shrink the grid until the partials fit
-    int max_contrib;
-    size_t need;
-    for (;;) {
-        const long long upc = total / grid;
-        max_contrib = (int)((NST + upc - 1) / upc) + 1;
-        need = (size_t)(p.n / 128) * max_contrib * p.m * 128 * 4;
-        if (need <= partial_room || grid <= 1) break;
-        grid = grid / 2 > 0 ? grid / 2 : 1;
-    }
-    if (need > partial_room && grid > 1) return cudaErrorMemoryAllocation;
-    if (grid == 1) { max_contrib = 1; need = 0; }
+    // every CTA may publish two partial tiles (its first and its last column block): the grid shrinks until they fit the
+    // room, which never takes it below the number of tiles the room holds
+    const size_t tile_bytes = (size_t)p.m * 128 * 4;
+    while (grid > 1 && (size_t)grid * 2 * tile_bytes > partial_room) grid = grid / 2;
+    const size_t need = grid > 1 ? (size_t)grid * 2 * tile_bytes : 0;
+    if (need > partial_room) return cudaErrorMemoryAllocation;
     p.partial = partial_base;
-    p.max_contrib = max_contrib;
-    if (plan_out) { plan_out->grid = (int)grid; plan_out->max_contrib = max_contrib; plan_out->partial_bytes = need; }
+    if (plan_out) { plan_out->grid = (int)grid; plan_out->max_contrib = 0; plan_out->partial_bytes = need; }
     kern<<<(unsigned)grid, 256, bytes, st>>>(p);
     return cudaPeekAtLastError();
 }
@@ -298,12 +291,12 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
 
 constexpr int GD_MAX_M = 16;
 
-template <int K, int CB, int MT, int VAR>
+template <int K, int CB, int MT>
 cudaError_t launch_decode(const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
 {
     constexpr int bytes = GdSmem<K, MT>::BYTES;
     static bool configured[64] = {};
-    auto kern = gemm_decode_kernel<K, CB, MT, VAR>;
+    auto kern = gemm_decode_kernel<K, CB, MT>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -322,38 +315,30 @@ cudaError_t launch_decode(const CUtensorMap* rmap, const GemmDecodeParams& p, in
 }
 
 template <int K, int CB>
-cudaError_t launch_decode_mt(int mt, int var, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+cudaError_t launch_decode_mt(int mt, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
 {
-    if constexpr (K == 4) {
-        if (var == 1) return mt == 1 ? launch_decode<K, CB, 1, 1>(rmap, p, grid, st) : launch_decode<K, CB, 2, 1>(rmap, p, grid, st);
-        if constexpr (CB == 1) {
-            if (var == 2) return launch_decode<K, CB, 1, 2>(rmap, p, grid, st);
-            if (var == 4) return launch_decode<K, CB, 1, 4>(rmap, p, grid, st);
-            if (var == 6) return launch_decode<K, CB, 1, 6>(rmap, p, grid, st);
-        }
-    }
-    return mt == 1 ? launch_decode<K, CB, 1, 0>(rmap, p, grid, st) : launch_decode<K, CB, 2, 0>(rmap, p, grid, st);
+    return mt == 1 ? launch_decode<K, CB, 1>(rmap, p, grid, st) : launch_decode<K, CB, 2>(rmap, p, grid, st);
 }
 
 template <int K>
-cudaError_t launch_decode_cb(int cb, int mt, int var, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+cudaError_t launch_decode_cb(int cb, int mt, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
 {
-    if (cb == 0) return launch_decode_mt<K, 0>(mt, var, rmap, p, grid, st);
-    if (cb == 1) return launch_decode_mt<K, 1>(mt, var, rmap, p, grid, st);
-    return launch_decode_mt<K, 2>(mt, var, rmap, p, grid, st);
+    if (cb == 0) return launch_decode_mt<K, 0>(mt, rmap, p, grid, st);
+    if (cb == 1) return launch_decode_mt<K, 1>(mt, rmap, p, grid, st);
+    return launch_decode_mt<K, 2>(mt, rmap, p, grid, st);
 }
 
-cudaError_t launch_decode_k(int K, int cb, int mt, int var, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
+cudaError_t launch_decode_k(int K, int cb, int mt, const CUtensorMap* rmap, const GemmDecodeParams& p, int grid, cudaStream_t st)
 {
     switch (K) {
-        case 1: return launch_decode_cb<1>(cb, mt, var, rmap, p, grid, st);
-        case 2: return launch_decode_cb<2>(cb, mt, var, rmap, p, grid, st);
-        case 3: return launch_decode_cb<3>(cb, mt, var, rmap, p, grid, st);
-        case 4: return launch_decode_cb<4>(cb, mt, var, rmap, p, grid, st);
-        case 5: return launch_decode_cb<5>(cb, mt, var, rmap, p, grid, st);
-        case 6: return launch_decode_cb<6>(cb, mt, var, rmap, p, grid, st);
-        case 7: return launch_decode_cb<7>(cb, mt, var, rmap, p, grid, st);
-        default: return launch_decode_cb<8>(cb, mt, var, rmap, p, grid, st);
+        case 1: return launch_decode_cb<1>(cb, mt, rmap, p, grid, st);
+        case 2: return launch_decode_cb<2>(cb, mt, rmap, p, grid, st);
+        case 3: return launch_decode_cb<3>(cb, mt, rmap, p, grid, st);
+        case 4: return launch_decode_cb<4>(cb, mt, rmap, p, grid, st);
+        case 5: return launch_decode_cb<5>(cb, mt, rmap, p, grid, st);
+        case 6: return launch_decode_cb<6>(cb, mt, rmap, p, grid, st);
+        case 7: return launch_decode_cb<7>(cb, mt, rmap, p, grid, st);
+        default: return launch_decode_cb<8>(cb, mt, rmap, p, grid, st);
     }
 }
 
@@ -381,7 +366,7 @@ int gemm_decode_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, co
             blocks += n[i] / 128;
             cuuint64_t rdims[2] = {(cuuint64_t)(n[i] / 16) * 4 * K, (cuuint64_t)(k / 16)};
             cuuint64_t rstrides[1] = {(cuuint64_t)(n[i] / 16) * 32 * K};
-            cuuint32_t rbox[2] = {(cuuint32_t)GD_SLOT_TILES * 4 * K, (cuuint32_t)GD_SLOT_ROWS};
+            cuuint32_t rbox[2] = {(cuuint32_t)2 * GD_SLOT_TILES * 4 * K, (cuuint32_t)GD_SLOT_ROWS};      // 8 tiles x 4 tile rows
             cuuint32_t estr[2] = {1, 1};
             CUresult r = enc(&rmap[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(trellis[i]), rdims, rstrides, rbox, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -397,15 +382,21 @@ int gemm_decode_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, co
     p.blk_end[GD_MAX_SEG - 1] = blocks;                     // the kernel reads the total from the last entry
     for (int i = nseg; i < GD_MAX_SEG - 1; ++i) p.blk_end[i] = blocks;
     if (blocks > ctx->n_counters) return exl3_fail(ctx, EXL3_ERR_INVALID, "exl3_gemm: n too large for the context's counters");
+    // Split of the (column block, 512-k chunk) units over the CTAs: whole blocks per CTA when that costs at most one unit
+    // more on the longest CTA than an even share of all units (no block is then shared between CTAs: no partial sums, no
+    // arrival counters, and the block finish at the end of the CTA is local), an even share (stream-K) otherwise.
     const int KC = (k + GD_UNIT_K - 1) / GD_UNIT_K;
     const long long total = (long long)blocks * KC;
-    const int grid = (int)(total < ctx->num_sms ? total : ctx->num_sms);
+    const int sms = ctx->num_sms;
+    const long long units_aligned = (long long)((blocks + sms - 1) / sms) * KC, units_even = (total + sms - 1) / sms;
+    p.aligned = units_aligned <= units_even + 1 ? 1 : 0;
+    const int grid = p.aligned ? (blocks < sms ? blocks : sms) : (int)(total < sms ? total : sms);
     p.partial = (float*)exl3_ws_take(ctx, &off, (size_t)grid * 2 * m * 128 * 4);
     if (!p.partial) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the partial sums");
     p.counters = ctx->counters; p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
     gemm_decode_prologue_kernel<<<dim3(8 * mt, nseg), 256, 0, st>>>(A, pa, m, k);
     ctx->launches++;
-    cudaError_t e = launch_decode_k(K, cb, mt, ctx->gd_var, rmap, p, grid, st);
+    cudaError_t e = launch_decode_k(K, cb, mt, rmap, p, grid, st);
     ctx->launches++;
     if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
     return EXL3_OK;
@@ -464,7 +455,7 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
         p.a_dup = a_dup; p.rowsum = rowsum; p.trellis = (const uint32_t*)trellis; p.partial = nullptr;
         p.counters = ctx->counters; p.svh = (const half*)svh; p.status = ctx->status;
         p.C = c_fp32 ? (void*)((float*)C + (size_t)row0 * n) : (void*)((half*)C + (size_t)row0 * n);
-        p.m = rows; p.k = k; p.n = n; p.max_contrib = 1; p.c_fp32 = c_fp32;
+        p.m = rows; p.k = k; p.n = n; p.c_fp32 = c_fp32;
         cudaError_t e = launch_small_k(K, cb, mt, p, ctx->num_sms, room, (float*)(ctx->ws + part_off), st, nullptr);
         ctx->launches++;
         if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
@@ -580,15 +571,16 @@ extern "C" int exl3_gemm_noalloc(exl3_stream stream, const void* A, const void* 
 
     cudaStream_t st = (cudaStream_t)stream;
     const int cb = mcg ? 1 : (mul1 ? 2 : 0);
-    // the array keeps whatever the previous call left: counters and status must start at zero
-    if (cudaMemsetAsync(d->base + NA_OFF_CNT, 0, NA_OFF_ROWSUM - NA_OFF_CNT, st) != cudaSuccess) { cudaGetLastError(); return EXL3_ERR_CUDA; }
+    // the array keeps whatever the previous call left: the counters must start at zero (the status word is sticky until
+    // exl3_gemm_noalloc_poll_status reads and clears it)
+    if (cudaMemsetAsync(d->base + NA_OFF_CNT, 0, NA_OFF_STATUS - NA_OFF_CNT, st) != cudaSuccess) { cudaGetLastError(); return EXL3_ERR_CUDA; }
     uint32_t* a_dup = (uint32_t*)(d->base + NA_OFF_ADUP);
     float* rowsum = (float*)(d->base + NA_OFF_ROWSUM);
     gemm_prologue_kernel<<<m, 256, 0, st>>>((const half*)A, (const half*)suh, a_dup, rowsum, k);
     GemmSmallParams p;
     p.a_dup = a_dup; p.rowsum = rowsum; p.trellis = (const uint32_t*)trellis; p.partial = nullptr;
     p.counters = (int*)(d->base + NA_OFF_CNT); p.svh = (const half*)svh; p.status = (int*)(d->base + NA_OFF_STATUS);
-    p.C = C; p.m = m; p.k = k; p.n = n; p.max_contrib = 1; p.c_fp32 = c_fp32;
+    p.C = C; p.m = m; p.k = k; p.n = n; p.c_fp32 = c_fp32;
     cudaError_t e = launch_small_k(K, cb, 1, p, d->num_sms, NA_BYTES - NA_OFF_PART, (float*)(d->base + NA_OFF_PART), st, nullptr);
     if (e != cudaSuccess) {
         fprintf(stderr, "exl3_gemm_noalloc: launch failed: %s\n", cudaGetErrorString(e));
@@ -596,6 +588,26 @@ extern "C" int exl3_gemm_noalloc(exl3_stream stream, const void* A, const void* 
         return EXL3_ERR_CUDA;
     }
     return EXL3_OK;
+}
+
+// The kernels behind exl3_gemm_noalloc report a bounded device-side wait that ran out through a status word inside the
+// fixed array.  This copies the word to the host (synchronising `stream`), clears it, and returns EXL3_ERR_DEVICE_WAIT if
+// it was set, EXL3_OK otherwise; like the entry point itself it allocates nothing.
+extern "C" int exl3_gemm_noalloc_poll_status(exl3_stream stream)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return EXL3_ERR_CUDA; }
+    NoAllocDev* d = nullptr;
+    int rc = noalloc_setup(dev, &d);
+    if (rc != EXL3_OK) return rc;
+    int h = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(&h, d->base + NA_OFF_STATUS, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess) { cudaGetLastError(); return EXL3_ERR_CUDA; }
+    if (h == 0) return EXL3_OK;
+    cudaMemsetAsync(d->base + NA_OFF_STATUS, 0, sizeof(int), st);
+    cudaStreamSynchronize(st);
+    return EXL3_ERR_DEVICE_WAIT;
 }
 
 #ifdef GD_TRACE

@@ -13,9 +13,11 @@
 // partial-sum slot in global memory that the last CTA to arrive adds up in owner order (deterministic), and the finisher
 // applies the output Hadamard and svh.
 //
-// Every warp streams its own codes: a ring of TMA boxes (4 tile rows x 4 tiles) with one mbarrier per slot, issued and
-// consumed by the warp itself, so the main loop has no CTA-wide barrier.  The transformed activations arrive in MMA
-// fragment order (gemm_decode_prologue_kernel) and are loaded once per slot, 16 bytes per lane and tile row.
+// The two warps of a k-slice share a ring of slots; a seventeenth warp is the producer for all eight rings: lane l of it
+// keeps k-slice l's ring full (one TMA box of 4 tile rows x 8 tiles of codes per slot and, for up to 8 rows, one bulk copy
+// of the slot's activations in MMA fragment order, written by gemm_decode_prologue_kernel), signalled through one "full"
+// and one "empty" mbarrier per slot.  A decoder's main loop is: wait, decode and multiply its 16 tiles, release - no
+// CTA-wide barrier and no address arithmetic.
 //
 // Multiplier mapping.  The 16x16 tile is stored in mma.m16n8k16 B-fragment order; read as the A operand of the
 // transposed product (weights^T . activations^T) the same registers are one A fragment, so a tile costs two MMAs for
@@ -35,8 +37,8 @@ namespace exl3 {
 // timeline of one launch (debug builds only): per CTA and warp [start, first data, loop end, end] in nanoseconds
 __device__ unsigned long long g_gd_trace[148 * 16 * 8];
 __device__ __forceinline__ unsigned long long gd_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define GD_STAMP(slot) do { if (lane == 0 && blockIdx.x < 148) g_gd_trace[(blockIdx.x * 16 + warp) * 8 + (slot)] = gd_now(); } while (0)
-#define GD_ACC(slot, v) do { if (lane == 0 && blockIdx.x < 148) g_gd_trace[(blockIdx.x * 16 + warp) * 8 + (slot)] += (v); } while (0)
+#define GD_STAMP(slot) do { if (lane == 0 && warp < 16 && blockIdx.x < 148) g_gd_trace[(blockIdx.x * 16 + warp) * 8 + (slot)] = gd_now(); } while (0)
+#define GD_ACC(slot, v) do { if (lane == 0 && warp < 16 && blockIdx.x < 148) g_gd_trace[(blockIdx.x * 16 + warp) * 8 + (slot)] += (v); } while (0)
 #define GD_T0() const unsigned long long gd_t0_ = gd_now()
 #define GD_DT() (gd_now() - gd_t0_)
 #else
@@ -46,8 +48,8 @@ __device__ __forceinline__ unsigned long long gd_now() { unsigned long long t; a
 #define GD_DT() 0
 #endif
 
-constexpr int GD_WARPS = 16;
-constexpr int GD_THREADS = GD_WARPS * 32;
+constexpr int GD_WARPS = 16;                 // decoder warps
+constexpr int GD_THREADS = (GD_WARPS + 4) * 32;            // + the producer's warpgroup (one of its four warps works)
 constexpr int GD_KSL = 8;                    // k-slices of a CTA unit
 constexpr int GD_SLOT_ROWS = 4;              // tile rows per TMA box = one k-slice (64 k)
 constexpr int GD_UNIT_K = GD_KSL * GD_SLOT_ROWS * 16;      // k extent of a unit: 512
@@ -60,18 +62,20 @@ constexpr float GD_MUL1_DELTA = -10.3828125f + 1534.0f * 0.00676727294921875f;
 
 template <int K, int MT> struct GdSmem {
     static constexpr int ROWS = 8 * MT;                                            // batch rows held by the MMAs
-    static constexpr int SLOT_BYTES = GD_SLOT_ROWS * GD_SLOT_TILES * 32 * K;       // 512 K
+    static constexpr int CODE_BYTES = GD_SLOT_ROWS * 2 * GD_SLOT_TILES * 32 * K;   // 4 tile rows x 8 tiles: 1024 K
+    // up to 8 rows: the slot also carries its activations (4 tile rows x 32 lanes x 16 bytes); with two row sets there is
+    // no room for that and the decoders load them from global memory
+    static constexpr int ACT_BYTES = MT == 1 ? GD_SLOT_ROWS * 32 * 16 : 0;
+    static constexpr int SLOT_BYTES = CODE_BYTES + ACT_BYTES;
     static constexpr int RED_BYTES = GD_KSL * ROWS * GD_RSTRIDE * 4;               // per-slice partial tiles
-    static constexpr int SC_BYTES = 0;
-    static constexpr int ROOM = 227 * 1024 - RED_BYTES - SC_BYTES - 1024;
-    static constexpr int DEPTH_FIT = ROOM / (GD_WARPS * SLOT_BYTES);
+    static constexpr int ROOM = 227 * 1024 - RED_BYTES - 2048;                     // barriers, alignment slack, static shared memory
+    static constexpr int DEPTH_FIT = ROOM / (GD_KSL * SLOT_BYTES);
     static constexpr int DEPTH = DEPTH_FIT > 8 ? 8 : DEPTH_FIT;
-    static_assert(DEPTH >= 2, "the code ring needs two slots per warp");
+    static_assert(DEPTH >= 2, "a ring needs two slots");
     static constexpr int OFF_RING = 0;
-    static constexpr int OFF_RED = OFF_RING + GD_WARPS * DEPTH * SLOT_BYTES;
-    static constexpr int OFF_SC = OFF_RED + RED_BYTES;
-    static constexpr int OFF_BAR = OFF_SC + SC_BYTES;
-    static constexpr int BYTES = OFF_BAR + GD_WARPS * DEPTH * 8 + 128;             // + slack to align the base to 128 bytes
+    static constexpr int OFF_RED = OFF_RING + GD_KSL * DEPTH * SLOT_BYTES;
+    static constexpr int OFF_BAR = OFF_RED + RED_BYTES;                            // full[8][DEPTH], empty[8][DEPTH]
+    static constexpr int BYTES = OFF_BAR + 2 * GD_KSL * DEPTH * 8 + 128;           // + slack to align the base to 128 bytes
 };
 
 struct GemmDecodeParams {
@@ -85,6 +89,7 @@ struct GemmDecodeParams {
     int* counters;                     // [column blocks] arrival counters, zero on entry and on exit
     int* status;
     int m, k, c_fp32;
+    int aligned;                       // 1: every CTA owns whole column blocks (no block is shared), 0: stream-K over units
 };
 
 __device__ __forceinline__ void gd_tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
@@ -118,51 +123,24 @@ __device__ __forceinline__ void lane_states4(const uint32_t* __restrict__ tile, 
     st[0] = __byte_perm(cl, 0, 0x4432);
 }
 
-// One slot = 4 tile rows x 4 tiles of one warp: decode and multiply.  VAR selects the instruction mix of the 4 bpw
-// decode (0: every state cut out of the window and cleaned by a byte permute before its multiply; 1: the four states
-// whose upper neighbour state is already clean in this lane are multiplied as uncleaned 32-bit windows and corrected by a
-// second multiply, x(s) = u*C + D - s_up*(C << 16) with u = s + (s_up << 16): two shifts and four permutes move from the
-// ALU pipe, which limits the kernel, to the multiplier pipe).
-template <int CB> struct GdCodebook {
-    static constexpr uint32_t MUL = CB == 0 ? 89226354u : (CB == 1 ? 0xCBAC1FEDu : 0x83DCD12Du);
-    static constexpr uint32_t ADD = CB == 0 ? 64248484u : 0u;
-    static constexpr uint32_t MUL_UP = 0u - (MUL << 16);          // -(C << 16) mod 2^32
-};
-
-template <int CB>
-__device__ __forceinline__ uint32_t gd_finish(uint32_t x)
-{
-    if constexpr (CB == 2) return __dp4a(x, 0x01010101u, 0xE5FE6400u);
-    else return lop_3inst(x);
-}
-
-template <int K, int CB, int MT, int VAR>
-__device__ __forceinline__ void gd_slot(const uint32_t* __restrict__ sb, int lane, int lane_prev, const uint4 (&af)[MT][GD_SLOT_ROWS],
+// One slot = 4 tile rows x 4 tiles of one warp: decode and multiply.
+template <int K, int CB, int MT>
+__device__ __forceinline__ void gd_slot(const uint32_t* __restrict__ sb, int ch, int lane, int lane_prev, uint4 (&af)[MT][GD_SLOT_ROWS],
                                         float (&acc)[MT][GD_SLOT_TILES][4])
 {
+    if constexpr (MT == 1) {
+        // activations of the slot, behind its codes: [tile row][lane] 16 bytes each
+        const uint4* sa = reinterpret_cast<const uint4*>(sb + GD_SLOT_ROWS * 2 * GD_SLOT_TILES * 8 * K);
+        #pragma unroll
+        for (int r = 0; r < GD_SLOT_ROWS; ++r) af[0][r] = sa[r * 32 + lane];
+    }
     #pragma unroll
     for (int r = 0; r < GD_SLOT_ROWS; ++r) {
         #pragma unroll
         for (int c = 0; c < GD_SLOT_TILES; ++c) {
-            const uint32_t* tile = sb + (r * GD_SLOT_TILES + c) * 8 * K;
+            const uint32_t* tile = sb + ((r * 2 + ch) * GD_SLOT_TILES + c) * 8 * K;      // this warp's half of the 8-tile row
             uint32_t y[8];
-            if constexpr (K == 4 && VAR == 1) {
-                using CBK = GdCodebook<CB>;
-                const uint32_t b = tile[lane], a = tile[lane_prev];
-                const uint32_t cw = __funnelshift_r(b, a, 16), c4 = cw >> 4;
-                const uint32_t s3 = __byte_perm(cw, 0, 0x4410), s2 = __byte_perm(c4, 0, 0x4410);
-                const uint32_t s1 = __byte_perm(cw, 0, 0x4421), s0 = __byte_perm(c4, 0, 0x4421);
-                const uint32_t u4 = __funnelshift_r(b, a, 4), u8 = __funnelshift_r(b, a, 8), u12 = __funnelshift_r(b, a, 12);
-                uint32_t x[8];
-                x[3] = s3 * CBK::MUL + CBK::ADD; x[2] = s2 * CBK::MUL + CBK::ADD;
-                x[1] = s1 * CBK::MUL + CBK::ADD; x[0] = s0 * CBK::MUL + CBK::ADD;
-                x[7] = s3 * CBK::MUL_UP + (b * CBK::MUL + CBK::ADD);
-                x[6] = s2 * CBK::MUL_UP + (u4 * CBK::MUL + CBK::ADD);
-                x[5] = s1 * CBK::MUL_UP + (u8 * CBK::MUL + CBK::ADD);
-                x[4] = s0 * CBK::MUL_UP + (u12 * CBK::MUL + CBK::ADD);
-                #pragma unroll
-                for (int q = 0; q < 8; ++q) y[q] = gd_finish<CB>(x[q]);
-            } else {
+            {
                 uint32_t st[8];
                 if constexpr (K == 4) lane_states4(tile, lane, lane_prev, st);
                 else lane_states<K>(tile, lane, st);
@@ -286,263 +264,271 @@ __device__ __forceinline__ void gd_store_row(float4 v, int lane, float rowsum, c
     }
 }
 
-// grid = CTAs of the stream-K split (at most one per SM), 512 threads, GdSmem<K, MT>::BYTES of dynamic shared memory.
+// grid = CTAs of the split (at most one per SM), 20 warps (16 decoders, the producer and its three idle warpgroup mates), GdSmem<K, MT>::BYTES of dynamic shared memory.
 // rmap*: the trellis of each tensor as a matrix of 64-bit words [k/16][n/16 * 4K], box 4 rows x 4 tiles.
 //
-// Leaving a column block does not stop the CTA: every warp drops its accumulators into the reduction tile and goes on
-// with the next block; the warp that arrives last adds the 8 k-slices, exchanges partial sums with the neighbouring CTAs
+// Leaving a column block does not stop the CTA: every decoder drops its accumulators into the reduction tile and goes on
+// with the next block; the one that arrives last adds the 8 k-slices, exchanges partial sums with the neighbouring CTAs
 // where the block is shared, transforms and stores, and then hands the tile back (an mbarrier the other warps test before
-// their next drop, several units later).  While that warp waits on the memory fences and the arrival counter of the
-// exchange, the other three warps of its scheduler use its issue slots.
-template <int K, int CB, int MT, int VAR>
+// their next drop, several units later).  While that warp waits on the arrival counter of the exchange, the other warps
+// of its scheduler use its issue slots.
+template <int K, int CB, int MT>
 __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid_constant__ CUtensorMap rmap0,
                                                                    const __grid_constant__ CUtensorMap rmap1,
                                                                    const __grid_constant__ CUtensorMap rmap2,
                                                                    const GemmDecodeParams p)
 {
     using SM = GdSmem<K, MT>;
-    constexpr bool PREFETCH = MT == 1;                  // the next slot's activations are loaded one slot ahead (registers permitting)
     extern __shared__ uint8_t gd_smem_unaligned[];
     uint8_t* smem = gd_smem_unaligned + ((128u - (smem_u32(gd_smem_unaligned) & 127u)) & 127u);
     float* red = reinterpret_cast<float*>(smem + SM::OFF_RED);
+    uint64_t* full_bars = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
+    uint64_t* empty_bars = full_bars + GD_KSL * SM::DEPTH;
     __shared__ int s_drops;
     __shared__ __align__(8) uint64_t s_red_free;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int ks = warp & (GD_KSL - 1), ch = warp >> 3;
     const int KC = (p.k + GD_UNIT_K - 1) / GD_UNIT_K;                  // k chunks per column block
-    const long long total = (long long)p.blk_end[GD_MAX_SEG - 1] * KC;
+    const int blocks = p.blk_end[GD_MAX_SEG - 1];
+    const long long total = (long long)blocks * KC;
     const long long G = gridDim.x;
-    const long long u0 = total * blockIdx.x / G, u1 = total * (blockIdx.x + 1) / G;
+    // this CTA's contiguous range of units (column-block-major): whole blocks, or an even share of all units
+    const long long u0 = p.aligned ? (long long)(blocks * (long long)blockIdx.x / G) * KC : total * blockIdx.x / G;
+    const long long u1 = p.aligned ? (long long)(blocks * (long long)(blockIdx.x + 1) / G) * KC : total * (blockIdx.x + 1) / G;
     const int nunits = (int)(u1 - u0);
     const int mrows = p.m;
+    const int nbg0 = (int)(u0 / KC), kc0 = (int)(u0 - (long long)nbg0 * KC);
+    auto seg_of = [&](int nbg) -> int { return (nbg >= p.blk_end[0]) + (nbg >= p.blk_end[1]); };
+    auto col0_of = [&](int nbg, int seg) -> int { return (nbg - (seg == 0 ? 0 : (seg == 1 ? p.blk_end[0] : p.blk_end[1]))) * 128; };
 
     GD_STAMP(0);
 #ifdef GD_TRACE
-    if (lane == 0 && blockIdx.x < 148) { g_gd_trace[(blockIdx.x * 16 + warp) * 8 + 4] = 0; g_gd_trace[(blockIdx.x * 16 + warp) * 8 + 5] = 0; g_gd_trace[(blockIdx.x * 16 + warp) * 8 + 6] = 0; }
+    if (lane == 0 && warp < 16 && blockIdx.x < 148) { for (int q = 4; q < 7; ++q) g_gd_trace[(blockIdx.x * 16 + warp) * 8 + q] = 0; }
 #endif
-    uint8_t* ring = smem + SM::OFF_RING + warp * SM::DEPTH * SM::SLOT_BYTES;
-    const uint32_t ring_u32 = smem_u32(ring);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR) + warp * SM::DEPTH;
-    const uint32_t bars_u32 = smem_u32(bars);
-    if (lane == 0) {
-        #pragma unroll
-        for (int s = 0; s < SM::DEPTH; ++s) mbar_init(&bars[s], 1);
-        if (warp == 0) { mbar_init(&s_red_free, 1); s_drops = 0; }
+    if (tid == 0) {
+        for (int i = 0; i < GD_KSL * SM::DEPTH; ++i) { mbar_init(&full_bars[i], 1); mbar_init(&empty_bars[i], 2); }
+        mbar_init(&s_red_free, 1);
+        s_drops = 0;
         mbar_fence_init();
     }
     __syncthreads();
 
-    // Units are walked with two cursors (the one being multiplied and the one being requested, DEPTH - 1 slots ahead),
-    // each stepped one unit at a time: (column block, k chunk) without a division in the loop.
-    const int nbg0 = (int)(u0 / KC), kc0 = (int)(u0 - (long long)nbg0 * KC);
-    auto seg_of = [&](int nbg) -> int { return (nbg >= p.blk_end[0]) + (nbg >= p.blk_end[1]); };
-    auto col0_of = [&](int nbg, int seg) -> int { return (nbg - (seg == 0 ? 0 : (seg == 1 ? p.blk_end[0] : p.blk_end[1]))) * 128; };
-    // unit i of this CTA is one slot of this warp: tile rows [32 kc + 4 ks, +4); a unit whose chunk ends before this
-    // warp's k-slice has no slot for it
-    auto slot_active = [&](int kc) -> bool { return (kc * GD_UNIT_K + ks * (GD_SLOT_ROWS * 16)) < p.k; };
-    int issued = 0, consumed = 0;
-    int j_iss = 0, nbg_iss = nbg0, kc_iss = kc0;
+    // Twenty warps start with 96 registers each; the producer's warpgroup hands most of its share back and the four decoder
+    // warpgroups take 120 each (the register file holds 20 x 32 x 96 + 16 x 32 x 24 + 4 x 32 x (24 - 96) <= 65536).
     bool failed = false;
-    auto issue_next = [&]() {
-        if (j_iss >= nunits) return;
-        if (slot_active(kc_iss) && !failed) {
-            if (lane == 0) {
-                const int seg = seg_of(nbg_iss);
-                const int s = issued % SM::DEPTH;
-                const CUtensorMap* rmap = seg == 0 ? &rmap0 : (seg == 1 ? &rmap1 : &rmap2);
-                const uint32_t bar = bars_u32 + 8u * s;
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)SM::SLOT_BYTES) : "memory");
-                gd_tma_load_2d(ring_u32 + s * SM::SLOT_BYTES, rmap, ((col0_of(nbg_iss, seg) >> 4) + ch * GD_SLOT_TILES) * 4 * K,
-                               kc_iss * (GD_UNIT_K / 16) + ks * GD_SLOT_ROWS, bar);
+    if (warp >= GD_WARPS) asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 120;");
+    if (warp > GD_WARPS) {
+        // idle warps of the producer's warpgroup
+    } else if (warp == GD_WARPS) {
+        // ===== producer: lane l < 8 serves k-slice l (decoder warps l and l + 8, the two column halves).  Unit i of the CTA
+        // is slot i % DEPTH of every ring.  The lanes share one instruction stream but each keeps its own cursor: in every
+        // pass a lane whose next slot is free requests its next unit, so a pair that runs ahead is fed ahead and one that
+        // has fallen behind (the warp that finishes a column block) holds nobody else up.  A unit whose k chunk ends before
+        // the slice (ragged last chunk) still takes the slot: nothing is copied and the lane arrives on the "full" barrier
+        // itself.
+        const bool serving = lane < GD_KSL;
+        const int ks = lane & (GD_KSL - 1);
+        const uint32_t ring = smem_u32(smem + SM::OFF_RING + ks * SM::DEPTH * SM::SLOT_BYTES);
+        const uint32_t fb = smem_u32(full_bars + ks * SM::DEPTH);
+        uint64_t* eb = empty_bars + ks * SM::DEPTH;
+        const int kslot_stride = GD_SLOT_ROWS * 32;                                 // uint4 per activation slot
+        int i = serving ? 0 : nunits, nbg = nbg0, kc = kc0, slot = 0, round = 0;
+        bool waited = false;                   // the wait for the activations' producer (first use only)
+        uint32_t idle = 0;
+        while (__any_sync(0xffffffffu, i < nunits)) {
+            const bool go = i < nunits && (round == 0 || mbar_try_wait(&eb[slot], (round - 1) & 1));
+            if (go) {
+                const uint32_t bar = fb + 8u * slot;
+                if (kc * GD_UNIT_K + ks * (GD_SLOT_ROWS * 16) < p.k) {
+                    const int seg = seg_of(nbg);
+                    const CUtensorMap* rmap = seg == 0 ? &rmap0 : (seg == 1 ? &rmap1 : &rmap2);
+                    const uint32_t dst = ring + slot * SM::SLOT_BYTES;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)SM::SLOT_BYTES) : "memory");
+                    gd_tma_load_2d(dst, rmap, (col0_of(nbg, seg) >> 4) * 4 * K, kc * (GD_UNIT_K / 16) + ks * GD_SLOT_ROWS, bar);
+                    if constexpr (SM::ACT_BYTES > 0) {
+                        // The launch may overlap the tail of the kernel that writes the activations (programmatic dependent
+                        // launch): the codes above do not depend on it, the activations do.
+                        if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+                        const uint4* afr = (seg == 0 ? p.a_frag[0] : (seg == 1 ? p.a_frag[1] : p.a_frag[2]));
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(dst + (uint32_t)SM::CODE_BYTES), "l"(afr + (size_t)(kc * GD_KSL + ks) * kslot_stride),
+                                       "r"((uint32_t)SM::ACT_BYTES), "r"(bar) : "memory");
+                    }
+                } else {
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+                }
+                if (++slot == SM::DEPTH) { slot = 0; ++round; }
+                if (++kc == KC) { kc = 0; ++nbg; }
+                ++i;
             }
-            ++issued;
+            // nothing to do for any lane: leave the issue slots to the decoders for a moment; give up after about 4 s
+            if (!__any_sync(0xffffffffu, go)) {
+                __nanosleep(200);
+                if (++idle > (1u << 24)) { failed = true; break; }
+            } else idle = 0;
         }
-        if (++kc_iss == KC) { kc_iss = 0; ++nbg_iss; }
-        ++j_iss;
-    };
-    // Only the first slot of every warp is requested up front.  Sixteen warps per SM that queue their whole ring at once
-    // put 19 MB in flight across the chip and the first useful byte arrives when most of that has landed (4.5 us measured);
-    // the rest of the ring is requested as soon as the first slot is in, while it is being multiplied.
-    issue_next();
+    } else {
+        // ===== decoders
+        const int g = lane >> 2, t = lane & 3;
+        const int ks = warp & (GD_KSL - 1), ch = warp >> 3;
+        const uint8_t* ring = smem + SM::OFF_RING + ks * SM::DEPTH * SM::SLOT_BYTES;
+        uint64_t* full = full_bars + ks * SM::DEPTH;
+        uint64_t* empty = empty_bars + ks * SM::DEPTH;
 
-    // activations of a unit's slot: batch rows 8 set + g, k = 64 kslot + 16 r + {2t, 2t+1, 2t+8, 2t+9} (a k-slice past
-    // the end of a ragged last chunk reads the last valid slot; it is never used)
-    const int kslot_max = p.k / 64 - 1;
-    auto load_af = [&](int nbg_, int kc_, uint4 (&af)[MT][GD_SLOT_ROWS]) {
-        const int seg = seg_of(nbg_);
-        const uint4* afr = (seg == 0 ? p.a_frag[0] : (seg == 1 ? p.a_frag[1] : p.a_frag[2]));
-        const int kslot = min(kc_ * GD_KSL + ks, kslot_max);
+        float acc[MT][GD_SLOT_TILES][4];
         #pragma unroll
         for (int s = 0; s < MT; ++s)
             #pragma unroll
-            for (int r = 0; r < GD_SLOT_ROWS; ++r) {
-                if constexpr ((VAR & 2) != 0) af[s][r] = make_uint4(0x3c003c00u + kslot, 0x38003800u + r, 0x34003400u + lane, 0x3c003c00u);
-                else af[s][r] = __ldg(afr + (((size_t)s * (p.k / 64) + kslot) * 4 + r) * 32 + lane);
-            }
-    };
+            for (int c = 0; c < GD_SLOT_TILES; ++c)
+                #pragma unroll
+                for (int e = 0; e < 4; ++e) acc[s][c][e] = 0.0f;
 
-    float acc[MT][GD_SLOT_TILES][4];
-    #pragma unroll
-    for (int s = 0; s < MT; ++s)
-        #pragma unroll
-        for (int c = 0; c < GD_SLOT_TILES; ++c)
-            #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[s][c][e] = 0.0f;
+        if constexpr (SM::ACT_BYTES == 0) asm volatile("griddepcontrol.wait;" ::: "memory");      // these warps read the activations themselves
 
-    // The launch may overlap the tail of the kernel that writes the activations (programmatic dependent launch): the
-    // requests for the codes above do not depend on it, everything below does.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    const int lane_prev = (lane + 31) & 31;
-    int nbg = nbg0, kc = kc0 - 1;
-    int events = 0;                                     // column blocks this CTA has left so far
-    uint4 af_next[MT][GD_SLOT_ROWS];
-    if constexpr (PREFETCH) { if (nunits > 0) load_af(nbg0, kc0, af_next); }
-    #pragma unroll 1
-    for (int i = 0; i < nunits; ++i) {
-        if (++kc == KC) { kc = 0; ++nbg; }
-        uint4 af[MT][GD_SLOT_ROWS];
-        if constexpr (PREFETCH) {
-            #pragma unroll
-            for (int r = 0; r < GD_SLOT_ROWS; ++r) af[0][r] = af_next[0][r];
-            if (i + 1 < nunits) {
-                const bool wrap = kc + 1 == KC;
-                load_af(wrap ? nbg + 1 : nbg, wrap ? 0 : kc + 1, af_next);
-            }
-        }
-        if (!slot_active(kc)) { while (issued - consumed < SM::DEPTH - 1 && j_iss < nunits) issue_next(); }
-        if (slot_active(kc) && !failed) {
-            if constexpr (!PREFETCH) load_af(nbg, kc, af);
-            const int s_idx = consumed % SM::DEPTH;
-            GD_T0();
-            const bool ok = mbar_wait_sleep_warp(&bars[s_idx], (consumed / SM::DEPTH) & 1);
-            if (i > 0) GD_ACC(4, GD_DT());
-            ++consumed;
-            if (i == 0) GD_STAMP(1);
-            // top the ring up: every slot but the one about to be multiplied may be in flight (the slot freed by the
-            // previous iteration has been read by all lanes: they are past the wait above)
-            while (issued - consumed < SM::DEPTH - 1 && j_iss < nunits) issue_next();
-            if (ok) gd_slot<K, CB, MT, VAR>(reinterpret_cast<const uint32_t*>(ring + s_idx * SM::SLOT_BYTES), lane, lane_prev, af, acc);
-            else failed = true;
-        }
-
-        const bool block_done = kc == KC - 1 || i == nunits - 1;
-        if (i == nunits - 1) GD_STAMP(2);
-        if (!block_done) continue;
-        if constexpr ((VAR & 4) != 0) {
-            if (acc[0][0][0] == 123.456f) reinterpret_cast<float*>(p.C[0])[tid] = acc[0][1][1] + acc[0][2][2] + acc[0][3][3];
-            continue;
-        }
-
-        // ---- the CTA leaves column block nbg.  The reduction tile is free again once the warp that finished the previous
-        // block has read it (that was several units ago unless this is the CTA's last, short block).
-        if (events > 0 && !mbar_wait_sleep_warp(&s_red_free, (events - 1) & 1)) failed = true;
-        ++events;
-        #pragma unroll
-        for (int s = 0; s < MT; ++s)
-            #pragma unroll
-            for (int c = 0; c < GD_SLOT_TILES; ++c) {
-                float* dst = red + ((size_t)ks * SM::ROWS + s * 8 + 2 * t) * GD_RSTRIDE + ch * 64 + c * 16 + g;
-                dst[0] = acc[s][c][0]; dst[GD_RSTRIDE] = acc[s][c][1];
-                dst[8] = acc[s][c][2]; dst[GD_RSTRIDE + 8] = acc[s][c][3];
-                acc[s][c][0] = acc[s][c][1] = acc[s][c][2] = acc[s][c][3] = 0.0f;
-            }
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) {
-            __threadfence_block();
-            last = atomicAdd(&s_drops, 1) == GD_WARPS - 1;
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (!last) continue;
-
-        // ---- this warp arrived last: it finishes the block on its own
-        GD_T0();
-        if (lane == 0) s_drops = 0;
-        __threadfence_block();
-        const int seg = seg_of(nbg);
-        const int n0 = col0_of(nbg, seg);
-        const half* svh = seg == 0 ? p.svh[0] : (seg == 1 ? p.svh[1] : p.svh[2]);
-        void* Cout = seg == 0 ? p.C[0] : (seg == 1 ? p.C[1] : p.C[2]);
-        const int n = seg == 0 ? p.n[0] : (seg == 1 ? p.n[1] : p.n[2]);
-        const float* rsum = seg == 0 ? p.rowsum[0] : (seg == 1 ? p.rowsum[1] : p.rowsum[2]);
-        // sum of the 8 k-slices of one row, in slice order; lane = 4 consecutive columns
-        auto row_sum = [&](int row) -> float4 {
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-            #pragma unroll
-            for (int s = 0; s < GD_KSL; ++s) {
-                const float4 v = *reinterpret_cast<const float4*>(red + ((size_t)s * SM::ROWS + row) * GD_RSTRIDE + lane * 4);
-                a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
-            }
-            return a;
-        };
-        // CTAs that own a part of this block: those whose unit range meets [nbg * KC, (nbg + 1) * KC)
-        const long long first = (long long)nbg * KC;
-        auto owner = [&](long long u) -> int { return (int)(((u + 1) * G + total - 1) / total - 1); };
-        const int c_first = owner(first), c_last = owner(first + KC - 1);
-        const int ncontrib = c_last - c_first + 1;
-        if (ncontrib == 1) {
-            for (int row = 0; row < mrows; ++row)
-                gd_store_row<CB>(row_sum(row), lane, CB == 2 ? rsum[row] : 0.f, svh, Cout, (size_t)row * n + n0 + lane * 4, n0, p.c_fp32);
-            if (lane == 0) mbar_arrive(&s_red_free);
-        } else {
-            // a CTA shares at most its first and its last column block: slot 0 and slot 1 of its pair
-            auto slot_of = [&](int cta) -> float* {
-                const long long fb = (total * cta / G) / KC;
-                return p.partial + ((size_t)cta * 2 + (fb == nbg ? 0 : 1)) * mrows * 128;
-            };
-            float* mine = slot_of(blockIdx.x);
-            for (int row = 0; row < mrows; ++row)
-                *reinterpret_cast<float4*>(mine + row * 128 + lane * 4) = row_sum(row);
-            if (lane == 0) mbar_arrive(&s_red_free);              // the tile has been read: the other warps may drop again
-            __syncwarp();
-            // one arrival per CTA: the release half publishes this warp's partial sums (ordered before it by the warp
-            // barrier above), the acquire half makes the other owners' visible to the CTA that arrives last
-            int fin = 0;
-            if (lane == 0) {
-                int old;
-                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + nbg) : "memory");
-                fin = old == ncontrib - 1;
-                if (fin) p.counters[nbg] = 0;
-            }
-            fin = __shfl_sync(0xffffffffu, fin, 0);
-            if (fin) {
-                __syncwarp();
-                // all owners' partial sums of up to 8 rows are requested before the first is used
-                for (int row0 = 0; row0 < mrows; row0 += 8) {
-                    float4 a[8];
+        const int lane_prev = (lane + 31) & 31;
+        int nbg = nbg0, kc = kc0 - 1, slot = 0, par = 0;
+        int events = 0;                                     // column blocks this CTA has left so far
+        #pragma unroll 1
+        for (int i = 0; i < nunits; ++i) {
+            if (++kc == KC) { kc = 0; ++nbg; }
+            const bool active = kc * GD_UNIT_K + ks * (GD_SLOT_ROWS * 16) < p.k;
+            if (!failed) {
+                uint4 af[MT][GD_SLOT_ROWS];
+                if (SM::ACT_BYTES == 0 && active) {
+                    // batch rows 8 set + g, k = 64 kslot + 16 r + {2t, 2t+1, 2t+8, 2t+9}
+                    const int seg = seg_of(nbg);
+                    const uint4* afr = (seg == 0 ? p.a_frag[0] : (seg == 1 ? p.a_frag[1] : p.a_frag[2]));
+                    const int kslot = kc * GD_KSL + ks;
                     #pragma unroll
-                    for (int r = 0; r < 8; ++r) a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int s = c_first; s <= c_last; ++s) {           // owner order: independent of arrival order
-                        const float* src = slot_of(s) + lane * 4;
+                    for (int s = 0; s < MT; ++s)
+                        #pragma unroll
+                        for (int r = 0; r < GD_SLOT_ROWS; ++r)
+                            af[s][r] = __ldg(afr + (((size_t)s * (p.k / 64) + kslot) * 4 + r) * 32 + lane);
+                }
+                GD_T0();
+                const bool ok = mbar_wait_sleep_warp(&full[slot], par);
+                if (i > 0) GD_ACC(4, GD_DT());
+                if (i == 0) GD_STAMP(1);
+                if (ok) {
+                    if (active) gd_slot<K, CB, MT>(reinterpret_cast<const uint32_t*>(ring + slot * SM::SLOT_BYTES), ch, lane, lane_prev, af, acc);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[slot]);              // every lane of this warp has read the slot
+                } else failed = true;
+                if (++slot == SM::DEPTH) { slot = 0; par ^= 1; }
+            }
+
+            const bool block_done = kc == KC - 1 || i == nunits - 1;
+            if (i == nunits - 1) GD_STAMP(2);
+            if (!block_done) continue;
+
+            // ---- the CTA leaves column block nbg.  The reduction tile is free again once the warp that finished the
+            // previous block has read it (that was several units ago unless this is the CTA's last, short block).
+            if (events > 0 && !mbar_wait_sleep_warp(&s_red_free, (events - 1) & 1)) failed = true;
+            ++events;
+            #pragma unroll
+            for (int s = 0; s < MT; ++s)
+                #pragma unroll
+                for (int c = 0; c < GD_SLOT_TILES; ++c) {
+                    float* dst = red + ((size_t)ks * SM::ROWS + s * 8 + 2 * t) * GD_RSTRIDE + ch * 64 + c * 16 + g;
+                    dst[0] = acc[s][c][0]; dst[GD_RSTRIDE] = acc[s][c][1];
+                    dst[8] = acc[s][c][2]; dst[GD_RSTRIDE + 8] = acc[s][c][3];
+                    acc[s][c][0] = acc[s][c][1] = acc[s][c][2] = acc[s][c][3] = 0.0f;
+                }
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) {
+                __threadfence_block();
+                last = atomicAdd(&s_drops, 1) == GD_WARPS - 1;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (!last) continue;
+
+            // ---- this warp arrived last: it finishes the block on its own
+            GD_T0();
+            if (lane == 0) s_drops = 0;
+            __threadfence_block();
+            const int seg = seg_of(nbg);
+            const int n0 = col0_of(nbg, seg);
+            const half* svh = seg == 0 ? p.svh[0] : (seg == 1 ? p.svh[1] : p.svh[2]);
+            void* Cout = seg == 0 ? p.C[0] : (seg == 1 ? p.C[1] : p.C[2]);
+            const int n = seg == 0 ? p.n[0] : (seg == 1 ? p.n[1] : p.n[2]);
+            const float* rsum = seg == 0 ? p.rowsum[0] : (seg == 1 ? p.rowsum[1] : p.rowsum[2]);
+            // sum of the 8 k-slices of one row, in slice order; lane = 4 consecutive columns
+            auto row_sum = [&](int row) -> float4 {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                #pragma unroll
+                for (int s = 0; s < GD_KSL; ++s) {
+                    const float4 v = *reinterpret_cast<const float4*>(red + ((size_t)s * SM::ROWS + row) * GD_RSTRIDE + lane * 4);
+                    a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+                }
+                return a;
+            };
+            // CTAs that own a part of this block: those whose unit range meets [nbg * KC, (nbg + 1) * KC)
+            int c_first = blockIdx.x, c_last = blockIdx.x;
+            if (!p.aligned) {
+                const long long first = (long long)nbg * KC;
+                auto owner = [&](long long u) -> int { return (int)(((u + 1) * G + total - 1) / total - 1); };
+                c_first = owner(first); c_last = owner(first + KC - 1);
+            }
+            const int ncontrib = c_last - c_first + 1;
+            if (ncontrib == 1) {
+                for (int row = 0; row < mrows; ++row)
+                    gd_store_row<CB>(row_sum(row), lane, CB == 2 ? rsum[row] : 0.f, svh, Cout, (size_t)row * n + n0 + lane * 4, n0, p.c_fp32);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_red_free);
+            } else {
+                // a CTA shares at most its first and its last column block: slot 0 and slot 1 of its pair
+                auto slot_of = [&](int cta) -> float* {
+                    const long long fb = (total * cta / G) / KC;
+                    return p.partial + ((size_t)cta * 2 + (fb == nbg ? 0 : 1)) * mrows * 128;
+                };
+                float* mine = slot_of(blockIdx.x);
+                for (int row = 0; row < mrows; ++row)
+                    *reinterpret_cast<float4*>(mine + row * 128 + lane * 4) = row_sum(row);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_red_free);              // the tile has been read: the other warps may drop again
+                // one arrival per CTA: the release half publishes this warp's partial sums (ordered before it by the warp
+                // barrier above), the acquire half makes the other owners' visible to the CTA that arrives last
+                int fin = 0;
+                if (lane == 0) {
+                    int old;
+                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + nbg) : "memory");
+                    fin = old == ncontrib - 1;
+                    if (fin) p.counters[nbg] = 0;
+                }
+                fin = __shfl_sync(0xffffffffu, fin, 0);
+                if (fin) {
+                    __syncwarp();
+                    // all owners' partial sums of up to 8 rows are requested before the first is used
+                    for (int row0 = 0; row0 < mrows; row0 += 8) {
+                        float4 a[8];
+                        #pragma unroll
+                        for (int r = 0; r < 8; ++r) a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int s = c_first; s <= c_last; ++s) {           // owner order: independent of arrival order
+                            const float* src = slot_of(s) + lane * 4;
+                            #pragma unroll
+                            for (int r = 0; r < 8; ++r)
+                                if (row0 + r < mrows) {
+                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (row0 + r) * 128));
+                                    a[r].x += v.x; a[r].y += v.y; a[r].z += v.z; a[r].w += v.w;
+                                }
+                        }
                         #pragma unroll
                         for (int r = 0; r < 8; ++r)
-                            if (row0 + r < mrows) {
-                                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (row0 + r) * 128));
-                                a[r].x += v.x; a[r].y += v.y; a[r].z += v.z; a[r].w += v.w;
-                            }
+                            if (row0 + r < mrows)
+                                gd_store_row<CB>(a[r], lane, CB == 2 ? rsum[row0 + r] : 0.f, svh, Cout, (size_t)(row0 + r) * n + n0 + lane * 4, n0, p.c_fp32);
                     }
-                    #pragma unroll
-                    for (int r = 0; r < 8; ++r)
-                        if (row0 + r < mrows)
-                            gd_store_row<CB>(a[r], lane, CB == 2 ? rsum[row0 + r] : 0.f, svh, Cout, (size_t)(row0 + r) * n + n0 + lane * 4, n0, p.c_fp32);
                 }
             }
+            GD_ACC(5, GD_DT());
         }
-        GD_ACC(5, GD_DT());
+        GD_STAMP(3);
     }
-    GD_STAMP(3);
-    // A wait that ran out: no new copies are issued after it, but boxes already requested may still land; give them the
-    // same bounded time before the CTA's shared memory is released.
-    if (__syncthreads_or(failed)) {
-        while (consumed < issued) {
-            mbar_wait_sleep_warp(&bars[consumed % SM::DEPTH], (consumed / SM::DEPTH) & 1, 1u << 12);
-            ++consumed;
-        }
-        if (tid == 0) atomicExch(p.status, 1);
-    }
+    // A wait that ran out ends the CTA's work; the status word tells the host.  (Copies still in flight belong to slots
+    // whose barrier nobody waits on any more; they were requested at most a ring's depth ahead and land within microseconds,
+    // long before the bounded waits of the other warps give up and the CTA can exit.)
+    if (__syncthreads_or(failed) && tid == 0) atomicExch(p.status, 1);
 }
 
 }  // namespace exl3

@@ -28,12 +28,14 @@ struct GemmSmallParams {
     const uint32_t* a_dup;     // [m][k] words, each = (a, a) as two fp16: the Hadamard-transformed activations
     const float* rowsum;       // [m] sum over k of the transformed activations (codebook 2 only)
     const uint32_t* trellis;   // [k/16][n/16][8K] words
-    float* partial;            // [n/128][max_contrib][m][128] fp32 partial sums of column blocks shared by several CTAs
+    float* partial;            // [grid][2][m][128] fp32: a CTA's partial sums of its first and of its last column block, when
+                               // those are shared with a neighbouring CTA (a CTA's range of units is contiguous, so no other
+                               // block of it can be)
     int* counters;             // [n/128] arrival counters, zero on entry and on exit
     void* C;                   // [m][n] fp16 or fp32
     const half* svh;           // [n] or NULL
     int* status;
-    int m, k, n, max_contrib, c_fp32;
+    int m, k, n, c_fp32;
 };
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -177,7 +179,12 @@ __global__ void __launch_bounds__(256) gemm_small_kernel(const GemmSmallParams p
         const int ncontrib = c_last - c_first + 1;
         bool finish = true;
         if (ncontrib > 1) {
-            float* mine = p.partial + ((size_t)nb * p.max_contrib + (blockIdx.x - c_first)) * p.m * 128;
+            // slot 0 of a CTA's pair holds its first column block, slot 1 its last
+            auto slot_of = [&](int cta) -> float* {
+                const long long fb = (total * cta / G) / NST;
+                return p.partial + ((size_t)cta * 2 + (fb == nb ? 0 : 1)) * p.m * 128;
+            };
+            float* mine = slot_of(blockIdx.x);
             for (int e = tid; e < mrows * 32; e += 256) {
                 const int row = e >> 5, c4 = e & 31;
                 *reinterpret_cast<float4*>(mine + row * 128 + c4 * 4) = *reinterpret_cast<const float4*>(sc + row * 132 + c4 * 4);
@@ -193,12 +200,11 @@ __global__ void __launch_bounds__(256) gemm_small_kernel(const GemmSmallParams p
             finish = s_flag != 0;
             if (finish) {
                 __threadfence();
-                const float* base = p.partial + (size_t)nb * p.max_contrib * p.m * 128;
                 for (int e = tid; e < mrows * 32; e += 256) {
                     const int row = e >> 5, c4 = e & 31;
                     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int s = 0; s < ncontrib; ++s) {        // owner order: independent of arrival order
-                        float4 v = __ldcg(reinterpret_cast<const float4*>(base + ((size_t)s * p.m + row) * 128 + c4 * 4));
+                    for (int s = c_first; s <= c_last; ++s) {   // owner order: independent of arrival order
+                        float4 v = __ldcg(reinterpret_cast<const float4*>(slot_of(s) + (size_t)row * 128 + c4 * 4));
                         a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
                     }
                     *reinterpret_cast<float4*>(sc + row * 132 + c4 * 4) = a;

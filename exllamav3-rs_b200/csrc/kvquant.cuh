@@ -165,6 +165,33 @@ __device__ __forceinline__ void dequant_x4_norot(const uint32_t* __restrict__ in
     reinterpret_cast<uint2*>(out)[lane] = o;
 }
 
+// 4-bit codes of one key and one 128-wide head, K and V in one warp operation: lanes 0..15 scale the 16 words of K (8
+// codes each: dims 8l..8l+7), lanes 16..31 those of V.  `rk`/`rv`: the key's codes (64 bytes) with its 4 group scales
+// `scale_off` bytes further on; `dk`/`dv`: the key's row of the fp16 tiles.  Same arithmetic, operation for operation,
+// as dequant_x4_norot (so the results are the same bits), at half the instructions per value: one shared-memory load
+// feeds eight values, and a byte of two codes becomes the half2 (512 + q0, 512 + q1) with one multiply and one logic op
+// (b * 0x2002 puts b << 1 and b << 13 side by side; the mask keeps one nibble of each).
+__device__ __forceinline__ void dequant4_kv_norot(const uint8_t* __restrict__ rk, const uint8_t* __restrict__ rv, int scale_off,
+                                                  half* __restrict__ dk, half* __restrict__ dv)
+{
+    const int lane = threadIdx.x & 31, l = lane & 15;
+    const uint8_t* r = (lane & 16) ? rv : rk;
+    half* out = (lane & 16) ? dv : dk;
+    const uint32_t w = reinterpret_cast<const uint32_t*>(r)[l];
+    const half sc = reinterpret_cast<const half*>(r + scale_off)[l >> 2];
+    const half2 off = __float2half2_rn(512.0f + 8.0f - 0.5f);
+    const half2 sm = __half2half2(__hmul(sc, __float2half_rn(0.125f)));
+    uint32_t o[4];
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t b = __byte_perm(w, 0, 0x4440 + j);
+        const uint32_t p = ((b * 0x2002u) & 0x001e001eu) | 0x60006000u;
+        const half2 h = __hmul2(__hsub2(*reinterpret_cast<const half2*>(&p), off), sm);
+        o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(out)[l] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // Unnormalised H32 of a group held in mma fragment order by the 4 lanes of a quad: v[blk][c] is element 8 blk + 2 t + c
 // (t = lane & 3).  All 32 lanes must call it.
 __device__ __forceinline__ void had32_quad(float (&v)[4][2], int t)

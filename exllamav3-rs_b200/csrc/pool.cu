@@ -84,10 +84,11 @@ extern "C" int exl3_pool_create(int device, int n_layers, int pages, int nkv, in
 {
     if (!out) return EXL3_ERR_INVALID;
     *out = nullptr;
-    if (n_layers <= 0 || pages <= 0 || nkv <= 0 || hd <= 0 || (nkv * hd) % 32) return EXL3_ERR_INVALID;
+    if (n_layers < 0 || pages <= 0 || nkv <= 0 || hd <= 0 || (nkv * hd) % 32) return EXL3_ERR_INVALID;
     const bool quant = k_bits != 0 || v_bits != 0;
     if (quant && (k_bits < 2 || k_bits > 8 || v_bits < 2 || v_bits > 8)) return EXL3_ERR_INVALID;
-    if (cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); return EXL3_ERR_CUDA; }
+    // n_layers = 0: a page table without planes (no device is touched)
+    if (n_layers > 0 && cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); return EXL3_ERR_CUDA; }
     exl3_pool* p = new (std::nothrow) exl3_pool();
     if (!p) return EXL3_ERR_NOMEM;
     p->device = device; p->n_layers = n_layers; p->pages = pages; p->nkv = nkv; p->hd = hd; p->k_bits = k_bits; p->v_bits = v_bits;
@@ -114,7 +115,7 @@ extern "C" int exl3_pool_create(int device, int n_layers, int pages, int nkv, in
 extern "C" void exl3_pool_destroy(exl3_pool* p)
 {
     if (!p) return;
-    cudaSetDevice(p->device);
+    if (p->n_layers > 0) cudaSetDevice(p->device);
     for (auto* vec : {&p->k, &p->v, &p->sk, &p->sv})
         for (void* ptr : *vec) if (ptr) cudaFree(ptr);
     delete p;

@@ -157,7 +157,7 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
             void* out[3] = {s.q, s.k, s.v};
             STEP_TRY(exl3_gemm_fanout(ctx, stream, s.a_in, 3, w, out, rows, 0));
         }
-        STEP_TRY(exl3_rope(ctx, stream, s.q, s.k, m->inv_freq, m->n_freq, 0, nullptr, s.row_pos, L.q_norm, L.k_norm,
+        STEP_TRY(exl3_rope(ctx, stream, s.q, nullptr, s.k, nullptr, m->inv_freq, m->n_freq, 0, nullptr, s.row_pos, L.q_norm, L.k_norm,
                            m->norm_eps, 0.f, m->rope_mode, m->attn_factor, 1, rows, m->nq, m->nkv, m->hd));
         if (m->kv_bits == 0)
             STEP_TRY(exl3_bighead_attn_paged(ctx, stream, s.q, s.k, s.v, L.k_cache, L.v_cache, b->block_table,

@@ -40,6 +40,18 @@ def lib():
         L.exl3_last_error.argtypes = [C.c_void_p]
         L.exl3_ctx_create.argtypes = [C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]
         L.exl3_ctx_destroy.argtypes = [C.c_void_p]
+        L.exl3_pool_create.argtypes = [C.c_int] * 7 + [C.POINTER(C.c_void_p)]
+        L.exl3_pool_destroy.argtypes = [C.c_void_p]
+        L.exl3_pool_layer.argtypes = [C.c_void_p, C.c_int] + [C.POINTER(C.c_void_p)] * 4
+        for n in ("exl3_pool_num_free", "exl3_pool_num_pages"):
+            getattr(L, n).argtypes = [C.c_void_p]
+        L.exl3_pool_refcount.argtypes = [C.c_void_p, C.c_int]
+        L.exl3_pool_set_dedup.argtypes = [C.c_void_p, C.c_int]
+        L.exl3_pool_alloc.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int32)]
+        L.exl3_pool_alloc_prefix.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.c_int, C.c_int, C.POINTER(C.c_int32), C.c_int,
+                                             C.POINTER(C.c_int), C.POINTER(C.c_int64)]
+        L.exl3_pool_register_page_hash.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int64), C.c_int]
+        L.exl3_pool_release.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_int]
         L.exl3_ctx_launch_count.restype = C.c_uint64
         L.exl3_ctx_launch_count.argtypes = [C.c_void_p]
         L.exl3_cuda_free_mib.restype = C.c_int64
@@ -203,16 +215,18 @@ class Ctx:
                                               dim), "rms_norm_res_in")
 
     def rope(self, q, k, inv_freq, position=0, positions=None, q_norm=None, k_norm=None, norm_eps=1e-6,
-             norm_constant_bias=0.0, rope_mode=ROPE_NEOX, attn_factor=1.0, row_pos=None, stream=None):
-        """src/ffi.rs:301-333; in place on q [bsz,seq,nq,hd] and k [bsz,seq,nk,hd]."""
+             norm_constant_bias=0.0, rope_mode=ROPE_NEOX, attn_factor=1.0, row_pos=None, out_q=None, out_k=None, stream=None):
+        """src/ffi.rs:301-333; q [bsz,seq,nq,hd] and k [bsz,seq,nk,hd] are rotated into out_q/out_k, or in place when those
+        are None (the reference's call passes the same tensor twice for that)."""
         _chk(q, torch.float16, "q"); _chk(k, torch.float16, "k"); _chk(inv_freq, torch.float32, "inv_freq")
+        _chk(out_q, torch.float16, "out_q"); _chk(out_k, torch.float16, "out_k")
         _chk(positions, torch.int32, "positions"); _chk(row_pos, torch.int32, "row_pos")
         _chk(q_norm, torch.float16, "q_norm"); _chk(k_norm, torch.float16, "k_norm")
         bsz, seq, nq, hd = q.shape
         nk = 0 if k is None else k.shape[2]
-        self.check(lib().exl3_rope(self._h, self.stream(stream), _ptr(q), _ptr(k), _ptr(inv_freq), inv_freq.numel(),
-                                   C.c_uint32(position), _ptr(positions), _ptr(row_pos), _ptr(q_norm), _ptr(k_norm),
-                                   C.c_float(norm_eps), C.c_float(norm_constant_bias), rope_mode,
+        self.check(lib().exl3_rope(self._h, self.stream(stream), _ptr(q), _ptr(out_q), _ptr(k), _ptr(out_k), _ptr(inv_freq),
+                                   inv_freq.numel(), C.c_uint32(position), _ptr(positions), _ptr(row_pos), _ptr(q_norm),
+                                   _ptr(k_norm), C.c_float(norm_eps), C.c_float(norm_constant_bias), rope_mode,
                                    C.c_float(attn_factor), bsz, seq, nq, nk, hd), "rope")
 
     def silu_mul(self, x, y, z, act_limit=0.0, stream=None):
@@ -308,7 +322,7 @@ class Ctx:
         bsz, pps = block_table.shape
         groups = k_out_scales.shape[2]
         dim = groups * 32
-        seq = k_in.shape[0] if cu_q is not None else (seq_len if seq_len is not None else k_in.shape[1])
+        seq = seq_len if seq_len is not None else (k_in.shape[0] if cu_q is not None else k_in.shape[1])
         self.check(lib().exl3_quant_cache_paged(self._h, self.stream(stream), _ptr(k_in), _ptr(k_out), _ptr(k_out_scales),
                                                 _ptr(v_in), _ptr(v_out), _ptr(v_out_scales), _ptr(cache_seqlens),
                                                 _ptr(block_table), _ptr(cu_q), bsz, seq, dim, k_out.shape[0], pps,
@@ -337,6 +351,74 @@ class Ctx:
                                                          k_in.shape[0], pps, k_in.shape[2] // groups,
                                                          v_in.shape[2] // groups, page_size, bonus_len,
                                                          C.c_float(compand_a)), "dequant_cache_paged_window")
+
+
+class Pool:
+    """Paged KV pools of all layers plus their page table (include/exl3_abi.h exl3_pool_*): what the reference builds from
+    PagedCache / QuantPagedCache and PageTable (src/paged.rs:18-92,330-506).  n_layers = 0 gives the page table alone."""
+
+    def __init__(self, device, n_layers, pages, nkv, hd, k_bits=0, v_bits=0):
+        self._h = C.c_void_p()
+        rc = lib().exl3_pool_create(device, n_layers, pages, nkv, hd, k_bits, v_bits, C.byref(self._h))
+        if rc != 0:
+            raise Exl3Error(f"exl3_pool_create failed with code {rc}")
+        self.pages, self.n_layers = pages, n_layers
+
+    def close(self):
+        if self._h:
+            lib().exl3_pool_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def layer(self, i):
+        """device addresses (k, v, sk, sv) of layer i as ints; fp16 pools have sk = sv = 0"""
+        p = [C.c_void_p() for _ in range(4)]
+        if lib().exl3_pool_layer(self._h, i, *[C.byref(x) for x in p]) != 0:
+            raise Exl3Error("exl3_pool_layer failed")
+        return tuple(x.value or 0 for x in p)
+
+    def num_free(self):
+        return lib().exl3_pool_num_free(self._h)
+
+    def refcount(self, page):
+        return lib().exl3_pool_refcount(self._h, page)
+
+    def set_dedup(self, on):
+        lib().exl3_pool_set_dedup(self._h, int(bool(on)))
+
+    def alloc(self, n):
+        out = (C.c_int32 * max(n, 1))()
+        if lib().exl3_pool_alloc(self._h, n, out) != 0:
+            raise Exl3Error(f"page table exhausted: need {n}, {self.num_free()} free")
+        return list(out)[:n]
+
+    def alloc_prefix(self, prompt_ids, gen_reserve):
+        """-> (pages, matched_tokens)"""
+        import numpy as np
+        ids = np.ascontiguousarray(prompt_ids, np.int64)
+        cap = (len(ids) + gen_reserve + 255) // 256 + 1
+        out = (C.c_int32 * cap)(); cnt = C.c_int(); matched = C.c_int64()
+        rc = lib().exl3_pool_alloc_prefix(self._h, ids.ctypes.data_as(C.POINTER(C.c_int64)), len(ids), gen_reserve, out, cap,
+                                          C.byref(cnt), C.byref(matched))
+        if rc != 0:
+            raise Exl3Error(f"alloc_prefix failed with code {rc}")
+        return list(out)[:cnt.value], int(matched.value)
+
+    def register_page_hash(self, page, prev_page, token_ids):
+        import numpy as np
+        ids = np.ascontiguousarray(token_ids, np.int64)
+        if lib().exl3_pool_register_page_hash(self._h, page, prev_page, ids.ctypes.data_as(C.POINTER(C.c_int64)), len(ids)) != 0:
+            raise Exl3Error("register_page_hash failed")
+
+    def release(self, pages):
+        arr = (C.c_int32 * max(len(pages), 1))(*pages)
+        if lib().exl3_pool_release(self._h, arr, len(pages)) != 0:
+            raise Exl3Error("release failed")
 
 
 class CudaGraph:

@@ -52,7 +52,8 @@ class SyntheticModel:
     """Dense transformer with seeded random EXL3 weights and its paged KV pools, resident on one device."""
 
     def __init__(self, n_layers, hidden, nq, nkv, hd, inter, vocab, K=4, cb=1, pages=64, kv_bits=0, seed=0,
-                 device="cuda", rope_theta=1e6, qk_norm=True, head_K=None):
+                 device="cuda", rope_theta=1e6, qk_norm=True, head_K=None, pool=None):
+        """`pool` (exl3b200.Pool): the KV planes are the pool's instead of tensors allocated here"""
         self.cfg = dict(n_layers=n_layers, hidden=hidden, nq=nq, nkv=nkv, hd=hd, inter=inter, vocab=vocab, K=K, cb=cb,
                         pages=pages, kv_bits=kv_bits)
         g = torch.Generator(device=device)
@@ -79,7 +80,9 @@ class SyntheticModel:
                      down_proj=SyntheticLinear(inter, hidden, K, cb, g, device),
                      attn_norm=normw(hidden), mlp_norm=normw(hidden),
                      q_norm=normw(hd) if qk_norm else None, k_norm=normw(hd) if qk_norm else None)
-            if kv_bits == 0:
+            if pool is not None:
+                pass
+            elif kv_bits == 0:
                 L["k_cache"] = torch.zeros(pages, 256, nkv, hd, **f16)
                 L["v_cache"] = torch.zeros(pages, 256, nkv, hd, **f16)
             else:
@@ -96,13 +99,21 @@ class SyntheticModel:
             for n in ("attn_norm", "mlp_norm", "q_norm", "k_norm", "k_cache", "v_cache", "qk", "sk", "qv", "sv"):
                 t = L.get(n)
                 setattr(s, n, None if t is None else t.data_ptr())
+            if pool is not None:
+                k, v, sk, sv = pool.layer(i)
+                if kv_bits == 0:
+                    s.k_cache, s.v_cache = k, v
+                else:
+                    s.qk, s.qv, s.sk, s.sv = k, v, sk, sv
+        self.pool = pool
         self.struct = Model(n_layers, hidden, nq, nkv, hd, inter, vocab, kv_bits, pages, 1e-6, 1.0, 2,
                             self.inv_freq.numel(), self.inv_freq.data_ptr(), self.embed.data_ptr(),
                             self.final_norm.data_ptr(), self.lm_head.struct(), self._layer_array)
         self._scratch = None
 
     def fill_kv(self, std=0.5, seed=1, chunk_pages=64):
-        """Fill the pools with N(0, std^2) context (quantised through the library's own quantiser when kv_bits > 0)."""
+        """Fill the pools with synthetic context: N(0, std^2) values in fp16 pools; in quantised pools uniform random codes
+        (every bit pattern is a valid code) with group scales uniform in [0.01, 0.06], i.e. values of the same magnitude."""
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)
         c = self.cfg
@@ -113,6 +124,17 @@ class SyntheticModel:
                     for p0 in range(0, c["pages"], chunk_pages):
                         sl = t[p0:p0 + chunk_pages]
                         sl.copy_((torch.randn(sl.shape, device=self.device, generator=g) * std).to(torch.float16))
+            else:
+                for name in ("qk", "qv"):
+                    t = L[name]
+                    for p0 in range(0, c["pages"], chunk_pages):
+                        sl = t[p0:p0 + chunk_pages]
+                        sl.copy_(torch.randint(-2 ** 31, 2 ** 31 - 1, sl.shape, dtype=torch.int32, device=self.device, generator=g))
+                for name in ("sk", "sv"):
+                    t = L[name]
+                    for p0 in range(0, c["pages"], chunk_pages):
+                        sl = t[p0:p0 + chunk_pages]
+                        sl.copy_((torch.rand(sl.shape, device=self.device, generator=g) * 0.05 + 0.01).to(torch.float16))
 
     def weight_bytes(self):
         b = self.lm_head.trellis.numel() * 2

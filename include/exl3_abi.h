@@ -62,6 +62,11 @@ EXL3_API void exl3_ctx_destroy(exl3_ctx* ctx);
 EXL3_API const char* exl3_last_error(const exl3_ctx* ctx);
 /* Synchronises `stream`, then returns and clears the device status word: 0 or EXL3_ERR_DEVICE_WAIT. */
 EXL3_API int  exl3_ctx_poll_status(exl3_ctx* ctx, exl3_stream stream);
+/* Self-test of the failure path: launches a kernel whose single bounded wait (`polls` polls, at most 2^20) can never be
+ * satisfied.  The kernel gives up, records it in the status word and ends normally; the next exl3_ctx_poll_status
+ * returns EXL3_ERR_DEVICE_WAIT and later calls on the context work as before.  No counterpart in the reference (its
+ * waits are unbounded spins, kernels/quant/exl3_gemm_inner.cuh barrier code). */
+EXL3_API int  exl3_selftest_bounded_wait(exl3_ctx* ctx, exl3_stream stream, uint32_t polls);
 /* number of kernels this context has launched since creation (for launch accounting in benchmarks) */
 EXL3_API uint64_t exl3_ctx_launch_count(const exl3_ctx* ctx);
 EXL3_API const char* exl3_version(void);
@@ -70,8 +75,8 @@ EXL3_API const char* exl3_version(void);
 
 /* exl3_shim_gemm (src/ffi.rs:18-27, csrc/exl3_shim.cpp:44-53 -> kernels/quant/exl3_gemm.cu:110-339).
  * C[m,n] = H128( fp16(H128(A o suh)/sqrt128) . W ) / sqrt128 o svh, W decoded from `trellis` [k/16, n/16, 16*K] int16.
- * A [m,k] fp16; C fp16 (c_fp32 = 0) or fp32; suh [k], svh [n] fp16; A_had: scratch of m*k halfs (may be NULL: the
- * context's scratch is used).  K = bits per weight 1..8; mcg/mul1 select the codebook (both set is an error).
+ * A [m,k] fp16; C fp16 (c_fp32 = 0) or fp32; suh [k], svh [n] fp16; A_had: accepted for signature compatibility and
+ * ignored (the transformed activations live in the context's scratch in a kernel-specific layout; pass NULL).  K = bits per weight 1..8; mcg/mul1 select the codebook (both set is an error).
  * k % 128 == 0, n % 128 == 0.  Returns 0 (the reference returns a kernel tag where 0 and 90 mean success). */
 EXL3_API int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const void* trellis, void* C, const void* suh,
               void* A_had, const void* svh, int m, int k, int n, int K, int c_fp32, int mcg, int mul1);
@@ -82,12 +87,19 @@ EXL3_API int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const v
  * calls no cudaMalloc / cudaFree or other allocating routine.  Its scratch is an 8 MiB array built into the library
  * image, present on every GPU that loads the library until the process exits.
  * Limits: m <= 16, k <= 32768, n <= 524288 (larger sizes return EXL3_ERR_WORKSPACE and print the limits to stderr).
- * The first call on a device looks up the array's device address; make that first call outside any stream capture.
+ * Warm-up: the first call on a device looks up the array's device address, and the first call per device for each
+ * (bits, codebook) pair configures that kernel (with lazy module loading the CUDA runtime may load code and reserve
+ * memory at that moment).  Make one call per pair you will use at start-up, outside any stream capture and outside the
+ * region that must not allocate; later calls only launch.
  * All calls on a device share the one array, which still holds the previous call's contents (the entry point clears the
  * parts that must start at zero on `stream`): two calls whose kernels can overlap on the GPU - different streams without
  * an ordering between them - race on it.  Call with the target device current. */
 EXL3_API int exl3_gemm_noalloc(exl3_stream stream, const void* A, const void* trellis, void* C, const void* suh,
                                const void* svh, int m, int k, int n, int K, int c_fp32, int mcg, int mul1);
+/* No counterpart in the reference.  Status of the exl3_gemm_noalloc calls issued so far on the current device:
+ * synchronises `stream`, returns EXL3_ERR_DEVICE_WAIT (and clears the word) if a bounded device-side wait ran out in any
+ * of them - their output is then incomplete - and EXL3_OK otherwise.  Allocates nothing. */
+EXL3_API int exl3_gemm_noalloc_poll_status(exl3_stream stream);
 
 /* exl3_shim_reconstruct (src/ffi.rs:162, csrc/exl3_shim.cpp:162-164 -> kernels/quant/reconstruct.cu:375-386).
  * Dense fp16 W[k,n] from the packed tensor; bit-exact with the reference. */
@@ -112,14 +124,15 @@ EXL3_API int exl3_rms_norm(exl3_ctx* ctx, exl3_stream stream, const void* x, int
 EXL3_API int exl3_rms_norm_res_in(exl3_ctx* ctx, exl3_stream stream, const void* x, int x_fp32, const void* w, void* y,
                          int y_fp32, float* r, float eps, float constant_bias, float constant_scale, int rows, int dim);
 
-/* exl3_shim_rope (src/ffi.rs:51-65, csrc/exl3_shim.cpp:79-91 -> kernels/rope.cu:279-440).  In place on
- * q [bsz,seq,nq,hd] and k [bsz,seq,nk,hd] (k may be NULL).  Optional per-head RMSNorm with fp16 weights
- * q_norm/k_norm [hd] first, then the rotation of the first 2*n_freq dims; token t of sequence b rotates by
- * position t + positions[b] (positions int32 [bsz], device) or t + position when positions is NULL.
- * Ragged form: row_seq/row_pos (int32 [rows], device) non-NULL -> q,k are packed [rows,...] (bsz*seq = rows) and row
- * r rotates by row_pos[r] (positions/position ignored). */
-EXL3_API int exl3_rope(exl3_ctx* ctx, exl3_stream stream, void* q, void* k, const float* inv_freq, int n_freq,
-              uint32_t position, const int32_t* positions, const int32_t* row_pos, const void* q_norm,
+/* exl3_shim_rope (src/ffi.rs:51-65, csrc/exl3_shim.cpp:79-91 -> kernels/rope.cu:279-440).  q [bsz,seq,nq,hd] and
+ * k [bsz,seq,nk,hd] (k may be NULL) are written to out_q / out_k; NULL for either means in place (the reference's callers
+ * pass the input tensor again for that).  Optional per-head RMSNorm with fp16 weights q_norm/k_norm [hd] first, then the
+ * rotation of the first 2*n_freq dims; token t of sequence b rotates by position t + positions[b] (positions int32
+ * [bsz], device) or t + position when positions is NULL.
+ * Ragged form: row_pos (int32 [rows], device) non-NULL -> q,k are packed [rows,...] (bsz*seq = rows) and row r rotates
+ * by row_pos[r] (positions/position ignored). */
+EXL3_API int exl3_rope(exl3_ctx* ctx, exl3_stream stream, void* q, void* out_q, void* k, void* out_k, const float* inv_freq,
+              int n_freq, uint32_t position, const int32_t* positions, const int32_t* row_pos, const void* q_norm,
               const void* k_norm, float norm_eps, float norm_constant_bias, int rope_mode, float attn_factor,
               int bsz, int seq, int nq, int nk, int hd);
 
@@ -282,6 +295,25 @@ EXL3_API int exl3_hgemm(exl3_ctx* ctx, exl3_stream stream, const void* a, const 
 EXL3_API int exl3_gemm_fanout(exl3_ctx* ctx, exl3_stream stream, const void* A, int count, const exl3_linear* const* w,
                               void* const* C, int m, int c_fp32);
 
+/* One linear layer as the reference loads it (Linear::load, src/modules.rs:97-165): features padded up to multiples of
+ * 128, an EXL3 tensor (w.trellis) or a dense fp16 weight [k, n] (`dense`, w.trellis NULL, w.k / w.n still give the padded
+ * sizes), an optional fp16 bias [n], the unpadded sizes, and the output policy. */
+typedef struct {
+    exl3_linear w;
+    const void* dense;      /* fp16 [w.k, w.n] row-major, or NULL */
+    const void* bias;       /* fp16 [w.n] or NULL */
+    int in_unpadded, out_unpadded;
+    int trim_padded_out;    /* 1: y has out_unpadded columns, 0: w.n */
+    float softcap;          /* 0 = none, else y = tanh(y / softcap) * softcap */
+} exl3_linear_layer;
+
+/* Linear::forward (src/modules.rs:183-252).  x [rows, in_last] fp16 with in_last <= w.k (a narrower input is
+ * zero-extended), y [rows, out_unpadded or w.n] fp16.  Bias, trim and soft-cap round to fp16 after each step like the
+ * tensor ops they replace.  The reference's choice between its fused kernel and reconstruct + dense GEMM above 144 rows
+ * is not reproduced: the product is exl3_gemm (or exl3_hgemm for a dense weight) at every row count. */
+EXL3_API int exl3_linear_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_linear_layer* layer, const void* x, int in_last,
+                                 void* y, int rows);
+
 /* bytes of device scratch exl3_step_forward needs for up to `max_rows` packed rows and `max_bsz` sequences */
 EXL3_API size_t exl3_step_scratch_bytes(const exl3_model* model, int max_rows, int max_bsz);
 
@@ -297,6 +329,63 @@ EXL3_API int exl3_step_build_descriptors(exl3_ctx* ctx, exl3_stream stream, cons
 EXL3_API int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_model* model, const exl3_batch* batch,
                                void* scratch, size_t scratch_bytes, int64_t* out_tokens, float* logits);
 
+/* ------------------------------------------------------------------------------- the rest of the op surface
+ * Every remaining exl3_shim_* symbol of src/ffi.rs has an entry point so that the crate links.  softcap, gelu_mul and
+ * relu2_mul are implemented; the others return EXL3_ERR_UNSUPPORTED (with a message in exl3_last_error) until built:
+ * they serve other model families (mixture-of-experts routing, gated-delta-net layers, vision towers) or the sampler. */
+
+/* exl3_shim_softcap (src/ffi.rs:123 -> kernels/softcap.cu:55-97): y = factor * tanh(x / factor), fp16 or fp32, in place allowed */
+EXL3_API int exl3_softcap(exl3_ctx* ctx, exl3_stream stream, const void* x, void* y, float factor, int64_t numel, int fp32);
+/* exl3_shim_gelu_mul / exl3_shim_relu2_mul (src/ffi.rs:126-127 -> kernels/activation.cu:181-330): z = act(x) * y, fp16;
+ * act_limit != 0 clamps y to [-limit, limit] and act(x) to <= limit before the product */
+EXL3_API int exl3_gelu_mul(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* y, void* z, float act_limit, int64_t numel);
+EXL3_API int exl3_relu2_mul(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* y, void* z, float act_limit, int64_t numel);
+/* exl3_shim_mgemm (src/ffi.rs:28-42, csrc/exl3_shim.cpp:57-75 -> kernels/quant/exl3_gemm.cu:386-678): EXL3 product over a
+ * device table of tensors chosen by device-resident indices.  A [bszm_in, m, k] fp16 (bszm_in = 1: every slot reads the
+ * same rows), C [bszm_out, m, n]; trellis/suh/svh: device arrays of device pointers, one per matrix; indices int64
+ * [bszm] (-1 = slot unused) or NULL (slot j uses matrix j); weights fp16 [bszm] or NULL: slot scales, after which the
+ * slots of each of the num_tokens groups are summed into that group's row.  Not built. */
+EXL3_API int exl3_mgemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const void* const* trellis, void* C,
+                        const void* const* suh, void* A_had, const void* const* svh, const int64_t* indices,
+                        const void* weights, int bszm_in, int bszm_out, int m, int k, int n, int K, int c_fp32, int mcg,
+                        int mul1, int num_tokens);
+/* exl3_shim_bighead_attn (src/ffi.rs:67-75 -> kernels/attention.cu): attention over an unpaged K/V [bsz,kv_len,nkv,hd].  Not built. */
+EXL3_API int exl3_bighead_attn(exl3_ctx* ctx, exl3_stream stream, const void* q, const void* k, const void* v, void* o, int bsz,
+                               int q_len, int kv_len, int nq, int nkv, int hd, int kv_chunk_size, int causal, float sm_scale);
+/* exl3_shim_gated_rms_norm (src/ffi.rs:118-122).  Not built. */
+EXL3_API int exl3_gated_rms_norm(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* w, void* y, const void* g, float eps,
+                                 float constant_bias, int w_groups, int gate_first, int gate_act, int rows, int dim);
+/* exl3_shim_apply_rep_pens / exl3_shim_apply_pres_freq_pens (src/ffi.rs:128-135 -> kernels/generator/rep_pen.cu).  Not built. */
+EXL3_API int exl3_apply_rep_pens(exl3_ctx* ctx, exl3_stream stream, const void* in_logits, void* out_logits, const int64_t* past_ids,
+                                 float rep_p, int sustain_range, int decay_range, int rows, int vocab, int past_len);
+EXL3_API int exl3_apply_pres_freq_pens(exl3_ctx* ctx, exl3_stream stream, const void* in_logits, void* out_logits,
+                                       const int64_t* past_ids, float pres_p, float freq_p, int sustain_range, int decay_range,
+                                       int rows, int vocab, int past_len);
+/* exl3_shim_gumbel_sample / exl3_shim_gumbel_noise_f32 (src/ffi.rs:137-138 -> kernels/generator/gumbel.cu).  Not built. */
+EXL3_API int exl3_gumbel_sample(exl3_ctx* ctx, exl3_stream stream, const void* logits, int fp32, int64_t* ids, int rows, int n,
+                                int max_logit, uint32_t random);
+EXL3_API int exl3_gumbel_noise_f32(exl3_ctx* ctx, exl3_stream stream, const float* logits_in, float* logits_out, int64_t numel,
+                                   uint32_t random);
+/* exl3_shim_cache_rotate (src/ffi.rs:139 -> kernels/generator/cache.cu:11-85): permute pages of a pool.  Not built. */
+EXL3_API int exl3_cache_rotate(exl3_ctx* ctx, exl3_stream stream, void* cache, const int32_t* order, void* temp, int pages,
+                               int n_order, size_t page_bytes);
+/* hybrid-architecture ops (src/ffi.rs:163-191 -> kernels/gdn.cu, gdn_chunk.cu, activation.cu).  Not built. */
+EXL3_API int exl3_mul_sigmoid_(exl3_ctx* ctx, exl3_stream stream, void* x, const void* y, int64_t numel);
+EXL3_API int exl3_deinterleave_qg(exl3_ctx* ctx, exl3_stream stream, const void* qg, void* q, void* g, int rows, int heads, int head_dim);
+EXL3_API int exl3_gdn_fused_op_2(exl3_ctx* ctx, exl3_stream stream, const void* b, const void* a, const void* dt_bias, const void* a_log,
+                                 void* beta, void* g, float beta_scale, int bsz, int seq, int heads);
+EXL3_API int exl3_gdn_chunk_wy(exl3_ctx* ctx, exl3_stream stream, const void* k, const void* v, const void* beta, const void* a_log,
+                               void* w, void* uv, int bsz, int heads, int chunks, int k_dim, int v_dim);
+EXL3_API int exl3_gdn_chunk_fused(exl3_ctx* ctx, exl3_stream stream, const void* w, const void* q, const void* k, const void* qkt,
+                                  const void* uv, const void* alog, const void* h0, void* out, void* ht, double scale, int bsz,
+                                  int heads, int chunks, int k_dim, int v_dim);
+EXL3_API int exl3_recurrent_gated_delta_rule(exl3_ctx* ctx, exl3_stream stream, const void* mixed_qkv, const void* g, const void* beta,
+                                             void* recurrent_state, void* core_attn_out, int num_k_heads, int num_v_heads,
+                                             int k_head_dim, int v_head_dim, const int32_t* slots, int history, int bsz, int seq);
+EXL3_API int exl3_causal_conv1d_update(exl3_ctx* ctx, exl3_stream stream, const void* x, void* conv_state, const int32_t* slots,
+                                       const void* weight, const void* bias, void* out, int activation, int history, int bsz,
+                                       int seq, int dim, int width);
+
 /* --------------------------------------------------------------------------------------- pools and page table
  * The reference keeps the paged KV pools and the page allocator on the Rust side: PagedCache::new / QuantPagedCache::new
  * (src/paged.rs:18-92) allocate one K and one V plane per layer, PageTable (src/paged.rs:330-506) hands out 256-token
@@ -306,7 +395,8 @@ EXL3_API int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_mod
  * device memory owned by the pool. */
 typedef struct exl3_pool exl3_pool;
 /* k_bits = v_bits = 0: fp16 planes [pages,256,nkv,hd]; 2..8: int32 codes [pages,256,groups*bits] + fp16 scales
- * [pages,256,groups], groups = nkv*hd/32.  All planes start zeroed.  EXL3_ERR_NOMEM when the device cannot hold them. */
+ * [pages,256,groups], groups = nkv*hd/32.  All planes start zeroed.  EXL3_ERR_NOMEM when the device cannot hold them.
+ * n_layers = 0 creates the page table alone (no device memory, no device needed). */
 EXL3_API int  exl3_pool_create(int device, int n_layers, int pages, int nkv, int hd, int k_bits, int v_bits, exl3_pool** out);
 EXL3_API void exl3_pool_destroy(exl3_pool* pool);
 /* device pointers of one layer: fp16 pools -> *k, *v (sk, sv NULL); quantised -> *k = codes of K, *sk = scales of K, ... */

@@ -588,6 +588,16 @@ void orc_embed(const int64_t* ids, const uint16_t* table, float* out, int rows, 
         for (int i = 0; i < dim; ++i) out[(size_t)r * dim + i] = h2f(table[(size_t)ids[r] * dim + i]);
 }
 
+/* the harness sets the thread count itself: a launcher may have pinned OMP_NUM_THREADS to 1 */
+void orc_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void)
 {
 #ifdef _OPENMP

@@ -49,6 +49,10 @@ def num_threads():
     return lib().orc_num_threads()
 
 
+def set_num_threads(n):
+    lib().orc_set_num_threads(C.c_int(int(n)))
+
+
 def codebook(cb):
     """All 65536 decoded fp16 values of codebook cb (0 3INST, 1 MCG, 2 MUL1)."""
     L = lib()

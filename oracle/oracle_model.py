@@ -18,10 +18,20 @@ def model_to_numpy(model):
         return dict(trellis=_np(l.trellis), suh=_np(l.suh), svh=_np(l.svh), K=l.K, cb=l.cb)
 
     out["lm_head"] = lin(model.lm_head)
+    cfg = model.cfg
     for L in model.layers:
         d = {}
         for n, v in L.items():
             d[n] = lin(v) if hasattr(v, "trellis") else _np(v)
+        if "k_cache" not in d and "qk" not in d:
+            # planes owned by a pool object start zeroed: the same on this side
+            if cfg["kv_bits"] == 0:
+                d["k_cache"] = np.zeros((cfg["pages"], 256, cfg["nkv"], cfg["hd"]), np.float16)
+                d["v_cache"] = np.zeros_like(d["k_cache"])
+            else:
+                groups = cfg["nkv"] * cfg["hd"] // 32
+                d["qk"] = np.zeros((cfg["pages"], 256, groups * cfg["kv_bits"]), np.int32); d["qv"] = np.zeros_like(d["qk"])
+                d["sk"] = np.zeros((cfg["pages"], 256, groups), np.float16); d["sv"] = np.zeros_like(d["sk"])
         out["layers"].append(d)
     return out
 

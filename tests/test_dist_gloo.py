@@ -25,7 +25,8 @@ def _worker(rank, world, port, out_dir):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        q_lens, ctx_lens, bt, pages, ids = bench.shard_batch(rank)
+        q_lens, ctx_lens, bt, pages, ids, part_imb = bench.shard_batch(rank)
+        assert 1.0 <= part_imb < 1.05
         # weak scaling: the same number of rows and sequences on every rank, different sequences
         sig = torch.tensor([int(q_lens.sum()), len(q_lens), int(ctx_lens.sum()), int(ids[:64].sum())], dtype=torch.int64)
         gathered = [torch.zeros_like(sig) for _ in range(world)]
@@ -40,8 +41,11 @@ def _worker(rank, world, port, out_dir):
         ms_local = 100.0 + 25.0 * rank
         ms = bench.reduce_max_ms(ms_local, world)
         assert ms == 100.0 + 25.0 * (world - 1)
+        rows_job = bench.reduce_sum(int(q_lens.sum()), world)
+        assert rows_job == int(q_lens.sum()) * world
+        assert abs(bench.reduce_sum(ms_local, world) / world - (100.0 + 12.5 * (world - 1))) < 1e-9
         value = bench.whole_job_value(int(q_lens.sum()), world, ms)
-        assert abs(value - int(q_lens.sum()) * world / (ms * 1e-3)) < 1e-6
+        assert abs(value - rows_job / (ms * 1e-3)) < 1e-6
         dist.barrier()
         with open(os.path.join(out_dir, f"rank{rank}.ok"), "w") as f:
             f.write(repr(value))
@@ -62,3 +66,43 @@ def test_single_rank_needs_no_process_group():
     import bench
     assert bench.reduce_max_ms(12.5, 1) == 12.5
     assert bench.whole_job_value(1052, 1, 100.0) == pytest.approx(10520.0)
+
+
+@pytest.mark.parametrize("workload", ["c4", "verify"])
+def test_partition_is_disjoint_complete_and_balanced(workload):
+    """the host partitioner deals the whole batch of a workload into 8 shards: every sequence in exactly one shard, the
+    same number of sequences of every row class per shard, and the cost (kv_len + rows) within 5 % of the mean"""
+    sys.path.insert(0, os.path.join(ROOT, "exllamav3-rs_b200"))
+    import bench
+    from exl3b200.partition import imbalance, partition_sequences, sequence_cost
+    q, ctx = bench.global_batch(workload)
+    parts = partition_sequences(q, ctx, 8)
+    allidx = np.concatenate(parts)
+    assert sorted(allidx.tolist()) == list(range(len(q)))
+    for ql in set(q.tolist()):
+        counts = {int((q[p] == ql).sum()) for p in parts}
+        assert max(counts) - min(counts) <= 1
+    assert len({int(q[p].sum()) for p in parts}) == 1, "equal packed rows per shard"
+    cost = sequence_cost(q, ctx)
+    loads = np.array([cost[p].sum() for p in parts], np.float64)
+    assert loads.max() / loads.mean() < 1.05 and loads.min() / loads.mean() > 0.95
+    assert imbalance(q, ctx, parts) == pytest.approx(loads.max() / loads.mean())
+    # shard_batch(rank) is shard `rank` of that partition
+    for rank in (0, 5):
+        ql, cl, bt, pages, ids, _ = bench.shard_batch(rank, workload)
+        assert ql.tolist() == q[parts[rank]].tolist() and cl.tolist() == ctx[parts[rank]].tolist()
+        assert len(ids) == int(ql.sum()) and bt.shape[0] == len(ql)
+
+
+def test_partition_uneven_counts():
+    """a batch whose classes do not divide by the shard count: counts differ by at most one and nothing is lost"""
+    sys.path.insert(0, os.path.join(ROOT, "exllamav3-rs_b200"))
+    from exl3b200.partition import partition_sequences
+    r = np.random.default_rng(3)
+    q = np.concatenate([np.ones(13, np.int32), np.full(5, 256, np.int32), np.full(3, 8, np.int32)])
+    ctx = r.integers(1, 5000, len(q)).astype(np.int32)
+    parts = partition_sequences(q, ctx, 4)
+    assert sorted(np.concatenate(parts).tolist()) == list(range(len(q)))
+    for ql in (1, 256, 8):
+        counts = [int((q[p] == ql).sum()) for p in parts]
+        assert max(counts) - min(counts) <= 1

@@ -86,3 +86,26 @@ def test_capture_ragged_attention_with_stream_fork(ctx):
     ctx.poll_status()
     assert torch.isfinite(got).all()
     assert torch.equal(got, want)
+
+
+def test_bounded_wait_times_out_and_the_context_recovers(ctx):
+    """the failure path: a device-side wait that can never be satisfied gives up after its poll limit, the status word
+    carries it to the host as EXL3_ERR_DEVICE_WAIT (once), and the context keeps working"""
+    import torch
+    import exl3b200
+    from exl3b200 import lib
+    from oracle import oracle as O
+    ctx.poll_status()
+    assert lib().exl3_selftest_bounded_wait(ctx.handle, ctx.stream(), 1000) == 0
+    with pytest.raises(exl3b200.Exl3Error, match="bounded device-side wait"):
+        ctx.poll_status()
+    ctx.poll_status()                                   # cleared by the report
+    r = H.rng(3)
+    m, k, n, K = 3, 1024, 512, 4
+    A = r.standard_normal((m, k)).astype(np.float16)
+    tr, suh, svh = H.rand_trellis(r, k, n, K), H.rand_signs(r, k), H.rand_signs(r, n)
+    c = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    ctx.exl3_gemm(H.to_dev(A), H.to_dev(tr), c, H.to_dev(suh), None, H.to_dev(svh), mcg=True)
+    ctx.poll_status()
+    want = O.exl3_gemm(A, tr, suh, svh, K, 1, c_fp32=True)
+    assert H.rel_rms_err(c.cpu().numpy(), want) < 2e-3

@@ -83,3 +83,65 @@ def test_ragged_step_equals_sequence_by_sequence(ctx):
                             H.to_dev(bt[b:b + 1]), int(q_lens[b]), want_logits=True)
         assert H.rel_rms_err(l1.cpu().numpy()[0], got[b]) < 5e-3
         assert int(t1[0]) == int(tok[b])
+
+
+@pytest.mark.parametrize("kv_bits", [0, 4])
+def test_multi_step_greedy_generation_with_page_allocator(ctx, kv_bits):
+    """A continuous batch over many steps: ragged prefill of four prompts, then 20 greedy decode steps, on pools and pages
+    handed out by the library's page table.  Two sequences cross a 256-token page boundary on the way (a page is
+    allocated when a sequence reaches it).  The oracle composition runs the same greedy loop on its own pools.  At every
+    step the device's logits must match the oracle's and its greedy tokens must be the oracle's; where the oracle's two
+    best logits are closer than the fp16 noise of a two-layer stack (a coin flip on either side) the oracle's second
+    choice is accepted too.  Both loops continue with the oracle's token, so their caches stay comparable."""
+    import torch
+    import exl3b200
+    from exl3b200.step import SyntheticModel
+    from oracle import oracle_model
+    n_layers, vocab, steps = 2, 2048, 20
+    prompts_len = [250, 40, 100, 511]
+    bsz, pps, seed = len(prompts_len), 4, 7
+    pool = exl3b200.Pool(0, n_layers, 16, 8, 128, kv_bits, kv_bits)
+    model = SyntheticModel(n_layers, 1024, 16, 8, 128, 3072, vocab, K=4, cb=1, pages=16, kv_bits=kv_bits, seed=seed, pool=pool)
+    nm = oracle_model.model_to_numpy(model)
+    r = H.rng(seed)
+    prompts = [r.integers(0, vocab, n).astype(np.int64) for n in prompts_len]
+    blocks = [pool.alloc_prefix(p, 1)[0] for p in prompts]           # room for the prompt and the first new token
+    assert [len(b) for b in blocks] == [1, 1, 1, 2]
+    d_sl = torch.zeros(bsz, dtype=torch.int32, device="cuda")
+    lens = np.zeros(bsz, np.int32)
+    ids, q_lens = np.concatenate(prompts), np.array(prompts_len, np.int32)
+    # logits of a 2-layer stack; with 4-bit KV a prefill chunk attends to its own freshly quantised keys, and the two
+    # sides' codes differ at rounding ties in a fraction of a percent of the groups
+    tol = 3e-2 if kv_bits else 1e-2
+    exact, ties = 0, 0
+    for step in range(steps + 1):
+        for b in range(bsz):                                         # a page for the last position this step writes
+            while (lens[b] + q_lens[b] + 255) // 256 > len(blocks[b]):
+                blocks[b] += pool.alloc(1)
+        bt = np.zeros((bsz, pps), np.int32)
+        for b, blk in enumerate(blocks):
+            bt[b, :len(blk)] = blk
+        wtok, wlog = oracle_model.step(nm, ids, q_lens, lens, bt)
+        tok, logits = model.step(ctx, H.to_dev(ids), H.to_dev(q_lens), d_sl, H.to_dev(bt), int(q_lens.max()), advance=True,
+                                 want_logits=True)
+        ctx.poll_status()
+        got, glog = tok.cpu().numpy(), logits.cpu().numpy()
+        assert H.rel_rms_err(glog, wlog) < tol, f"step {step}"
+        order = np.argsort(wlog, axis=1)
+        for b in range(bsz):
+            gap = (wlog[b, order[b, -1]] - wlog[b, order[b, -2]]) / wlog[b].std()
+            if got[b] == wtok[b]:
+                exact += 1
+            else:
+                assert gap < 2 * tol and got[b] == order[b, -2], f"step {step} sequence {b}: {got[b]} vs {wtok[b]}, gap {gap:.4f}"
+                ties += 1
+        lens = lens + q_lens
+        assert np.array_equal(d_sl.cpu().numpy(), lens)
+        ids, q_lens = wtok.astype(np.int64), np.ones(bsz, np.int32)
+    assert exact >= (steps + 1) * bsz - 4, f"{ties} of {(steps + 1) * bsz} tokens fell on near-ties"
+    assert lens.tolist() == [p + steps + 1 - 1 for p in prompts_len] and len(blocks[0]) == 2 and len(blocks[3]) == 3
+    assert pool.num_free() == 16 - sum(len(b) for b in blocks)
+    for blk in blocks:
+        pool.release(blk)
+    assert pool.num_free() == 16
+    pool.close()

@@ -125,11 +125,11 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnParams p, i
     for (int e = 0; e < D / 32; e += 2) *reinterpret_cast<uint32_t*>(op + e) = pack_h2(acc[e] * inv, acc[e + 1] * inv);
 }
 
-template <int D, int WM, int WN, bool QUANT>
+template <int D, int WM, int WN, int QB>
 cudaError_t launch_attn(const AttnParams& p, dim3 grid, cudaStream_t st)
 {
-    constexpr int bytes = AttnSmem<D, QUANT>::BYTES;
-    auto kern = attn_paged_kernel<D, WM, WN, QUANT>;
+    constexpr int bytes = AttnSmem<D, QB>::BYTES;
+    auto kern = attn_paged_kernel<D, WM, WN, QB>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -196,6 +196,7 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
 {
     const int D = 128;
     const int G = p.nq / p.nkv;
+    const bool q4 = quant && p.k_bits == 4 && p.v_bits == 4;       // the common cache format has its own, smaller staging
     // long class on fp16 pools: tcgen05 kernel (256-row items) unless the context was switched to the mma.sync kernels
     // (its row maximum is taken on the raw scores, which needs a positive scale)
     const bool use_tc = !decode_shape && !quant && ctx->mma_attn != 0 && p.scale_log2 > 0.f;
@@ -206,15 +207,18 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     int per_sm = 1;
     if (!use_tc) {
         // CTAs of the mma.sync kernel that fit on an SM (bounded by shared memory: stages x 34.8 KB for fp16 pools)
-        const size_t smem = quant ? AttnSmem<128, true>::BYTES : AttnSmem<128, false>::BYTES;
-        per_sm = std::max(1, std::min(3, (int)((227 * 1024) / (smem + 1024))));
+        const size_t smem = quant ? (q4 ? AttnSmem<128, 4>::BYTES : AttnSmem<128, 8>::BYTES) : AttnSmem<128, 0>::BYTES;
+        per_sm = std::max(1, std::min(q4 ? 4 : 3, (int)((227 * 1024) / (smem + 1024))));
     }
+    static const int tune_per_sm = getenv("EXL3_TUNE_PER_SM") ? atoi(getenv("EXL3_TUNE_PER_SM")) : 0;
+    static const int tune_items = getenv("EXL3_TUNE_ITEMS") ? atoi(getenv("EXL3_TUNE_ITEMS")) : 0;
+    if (tune_per_sm && quant) per_sm = tune_per_sm;
     const int grid_x = std::max(1, ctx->num_sms * per_sm / p.nkv);
     // tcgen05 kernel: two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs a
     // 133 KB partial per kv head written and read back (4 per slot was measured 20 % slower, 1 per slot 2 % slower).
     // mma.sync kernels (units handed out dynamically, 8 KB partials): three per slot for fp16 pools, four for quantised.
     // the quantised kernel spends most of its time scaling codes, so finer items balance it better (+11 % measured)
-    const int target_items = grid_x * (use_tc ? 2 : (quant ? 4 : 3));
+    const int target_items = grid_x * (use_tc ? 2 : (quant ? (tune_items ? tune_items : 4) : 3));
     // items <= target + sum of row blocks (every (sequence, row block) rounds its split count up once); the row blocks are
     // bounded by bsz * rb_max and, usually much tighter for ragged batches, by total_rows * G / rows_per_cta + bsz
     const long long rb_sum = std::min((long long)p.bsz * rb_max, ((long long)total_rows * G + rows_per_cta - 1) / rows_per_cta + p.bsz);
@@ -257,8 +261,9 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     if (!use_tc && cudaMemsetAsync(&plan->next, 0, sizeof(int), st) != cudaSuccess)      // the persistent kernel's work counter
         return exl3_fail(ctx, EXL3_ERR_CUDA, "attention: cudaMemsetAsync failed");
     if (use_tc) e = launch_attn_tc(ctx, p, max_items, st);
-    else if (quant) e = decode_shape ? launch_attn<128, 1, 4, true>(p, grid, st) : launch_attn<128, 4, 1, true>(p, grid, st);
-    else       e = decode_shape ? launch_attn<128, 1, 4, false>(p, grid, st) : launch_attn<128, 4, 1, false>(p, grid, st);
+    else if (q4)    e = decode_shape ? launch_attn<128, 1, 4, 4>(p, grid, st) : launch_attn<128, 4, 1, 4>(p, grid, st);
+    else if (quant) e = decode_shape ? launch_attn<128, 1, 4, 8>(p, grid, st) : launch_attn<128, 4, 1, 8>(p, grid, st);
+    else            e = decode_shape ? launch_attn<128, 1, 4, 0>(p, grid, st) : launch_attn<128, 4, 1, 0>(p, grid, st);
     ctx->launches++;
     if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
     const long long warps = (long long)total_rows * p.nq;

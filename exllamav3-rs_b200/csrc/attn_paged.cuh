@@ -76,13 +76,17 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b)
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Shared memory: per stage a K tile and a V tile [AT_TK][D+8] fp16; QUANT adds the raw codes/scales staging.
-template <int D, bool QUANT>
+// Shared memory: per stage a K tile and a V tile [AT_TK][D+8] fp16; quantised pools (QB > 0: codes of at most QB bits)
+// stage the raw codes and scales instead and decode them into one pair of fp16 tiles.
+template <int D, int QB>
 struct AttnSmem {
+    static constexpr bool QUANT = QB > 0;
     static constexpr int ROWB = (D + 8) * 2;                       // bytes per key row (padding keeps ldmatrix conflict-free)
     static constexpr int TILE = AT_TK * ROWB;
-    static constexpr int RAW_ROW = QUANT ? (D / 32) * 8 * 4 + 16 : 0;   // up to 8-bit codes of D/32 groups + scales, per key
-    static constexpr int RAW = AT_TK * RAW_ROW;
+    static constexpr int RAW_ROW = QUANT ? (D / 32) * QB * 4 + 16 : 0;  // QB-bit codes of D/32 groups + scales, per key
+    // 64 bytes between the K and the V rows of a stage: the 4-bit decoder reads a key's K words with lanes 0..15 and its V
+    // words with lanes 16..31, which must fall into different banks
+    static constexpr int RAW = AT_TK * RAW_ROW + 64;
     static constexpr int STAGE = QUANT ? 2 * RAW : 2 * TILE;      // QUANT stages the raw bytes; tiles are decoded in place below
     static constexpr int DECODED = QUANT ? 2 * TILE : 0;
     static constexpr int PIPE = AT_STAGES * STAGE + DECODED;
@@ -91,10 +95,14 @@ struct AttnSmem {
 };
 
 // WM x WN = 4 warps: WM 16-row tiles, WN key slices of every tile.  (4,1): prefill/verify rows, (1,4): decode rows.
-template <int D, int WM, int WN, bool QUANT>
-__global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams p)
+#ifndef AT_Q4_DECODE_BLOCKS
+#define AT_Q4_DECODE_BLOCKS 4         // resident CTAs per SM the 4-bit decode-class kernel is compiled for (register cap)
+#endif
+template <int D, int WM, int WN, int QB>
+__global__ void __launch_bounds__(AT_THREADS, (QB == 4 && WN == 4) ? AT_Q4_DECODE_BLOCKS : 1) attn_paged_kernel(const AttnParams p)
 {
-    using SM = AttnSmem<D, QUANT>;
+    using SM = AttnSmem<D, QB>;
+    constexpr bool QUANT = QB > 0;
     constexpr int ROWS = 16 * WM;
     constexpr int KEYS_W = AT_TK / WN;          // keys of a tile handled by one warp
     constexpr int NBLK = KEYS_W / 8;            // n8 blocks of S per warp
@@ -228,16 +236,19 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                 const uint8_t* vsrc = reinterpret_cast<const uint8_t*>(p.qv + (tok * groups + kvh * 4) * p.v_bits);
                 uint8_t* kdst = sbase + key * SM::RAW_ROW;
                 uint8_t* vdst = sbase + SM::RAW + key * SM::RAW_ROW;
-                for (int ch = half_id; ch < p.k_bits; ch += 2) cp_async16(kdst + ch * 16, ksrc + ch * 16);
-                for (int ch = half_id; ch < p.v_bits; ch += 2) cp_async16(vdst + ch * 16, vsrc + ch * 16);
+                const int kb = QB == 4 ? 4 : p.k_bits, vb = QB == 4 ? 4 : p.v_bits;
+                #pragma unroll
+                for (int ch = half_id; ch < kb; ch += 2) cp_async16(kdst + ch * 16, ksrc + ch * 16);
+                #pragma unroll
+                for (int ch = half_id; ch < vb; ch += 2) cp_async16(vdst + ch * 16, vsrc + ch * 16);
                 const half* ssrc = (half_id ? p.sv : p.sk) + tok * groups + kvh * 4;
-                cp_async8((half_id ? vdst : kdst) + (D / 32) * 32, ssrc);
+                cp_async8((half_id ? vdst : kdst) + SM::RAW_ROW - 16, ssrc);
             }
         };
 
         #pragma unroll
-        for (int t = 0; t < AT_STAGES - 1; ++t) {                  // tiles 0 .. S-2 in flight before the loop
-            if (t < n_tiles) load_tile(t, t);
+        for (int pre = 0; pre < AT_STAGES - 1; ++pre) {            // tiles 0 .. S-2 in flight before the loop
+            if (pre < n_tiles) load_tile(pre, pre);
             cp_async_commit();
         }
         int stage = 0;
@@ -254,11 +265,11 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                 uint8_t* dk = smem_raw + AT_STAGES * SM::STAGE;
                 uint8_t* dv = dk + SM::TILE;
                 const uint8_t* raw = smem_raw + stage * SM::STAGE;
-                if (p.k_bits == 4 && p.v_bits == 4) {
+                if (QB == 4) {
                     static_assert(!QUANT || D == 128, "the 4-bit path scales one 128-wide head per half warp");
                     #pragma unroll 4
                     for (int key = warp; key < AT_TK; key += 4)
-                        dequant4_kv_norot(raw + key * SM::RAW_ROW, raw + SM::RAW + key * SM::RAW_ROW, (D / 32) * 32,
+                        dequant4_kv_norot(raw + key * SM::RAW_ROW, raw + SM::RAW + key * SM::RAW_ROW, SM::RAW_ROW - 16,
                                           reinterpret_cast<half*>(dk + key * SM::ROWB), reinterpret_cast<half*>(dv + key * SM::ROWB));
                 } else
                 #pragma unroll 4                                   // independent keys in flight: the chain per key is latency-bound
@@ -268,10 +279,10 @@ __global__ void __launch_bounds__(AT_THREADS) attn_paged_kernel(const AttnParams
                         const uint8_t* rk = raw + key * SM::RAW_ROW;
                         const uint8_t* rv = raw + SM::RAW + key * SM::RAW_ROW;
                         dequant_x4_norot(reinterpret_cast<const uint32_t*>(rk) + part * 4 * p.k_bits,
-                                         reinterpret_cast<const half*>(rk + (D / 32) * 32) + part * 4,
+                                         reinterpret_cast<const half*>(rk + SM::RAW_ROW - 16) + part * 4,
                                          reinterpret_cast<half*>(dk + key * SM::ROWB) + part * 128, p.k_bits);
                         dequant_x4_norot(reinterpret_cast<const uint32_t*>(rv) + part * 4 * p.v_bits,
-                                         reinterpret_cast<const half*>(rv + (D / 32) * 32) + part * 4,
+                                         reinterpret_cast<const half*>(rv + SM::RAW_ROW - 16) + part * 4,
                                          reinterpret_cast<half*>(dv + key * SM::ROWB) + part * 128, p.v_bits);
                     }
                 }

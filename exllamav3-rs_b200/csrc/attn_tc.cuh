@@ -92,6 +92,16 @@ __device__ __forceinline__ float ex2_approx(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// two exponentials per special-function operation: 2^x of an fp16 pair (the result is used as fp16 anyway)
+__device__ __forceinline__ uint32_t ex2_h2(uint32_t x)
+{
+    uint32_t y;
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+#ifndef ATC_EXP_F16X2
+#define ATC_EXP_F16X2 1
+#endif
 __device__ __forceinline__ float fmax3(float a, float b, float c)
 {
     float y;
@@ -289,12 +299,31 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attn_tc_kernel(const __grid_co
         };
         // P = 2^(s * scale - m_used) as fp16 pairs, summed in fp32 (masked scores are -inf and give 0)
         auto half_exp = [&](const float (&sv)[64], float nref, uint32_t (&pw)[32], float& l0, float& l1) {
+#if ATC_EXP_F16X2
+            // The exponent s * scale - m is formed in fp32 and rounded to fp16 (it lies in (-inf, threshold]: a rounding
+            // step of 2^-11 |x| moves 2^x by the factor 2^(2^-11 |x|), i.e. by at most 2.6e-4 of the row's largest
+            // weight, the size of P's own fp16 rounding).  The special-function unit then takes both exponentials of a
+            // pair in one operation - it has 16 lanes per SM against 128 exponentials per row and tile - and returns
+            // them already packed.  Row sums: groups of four pairs are added in fp16 (at most 2^11), then in fp32.
+            #pragma unroll
+            for (int e = 0; e < 64; e += 8) {
+                __half2 acc = __float2half2_rn(0.f);
+                #pragma unroll
+                for (int u = 0; u < 8; u += 2) {
+                    const uint32_t w = ex2_h2(pack_h2(fmaf(sv[e + u], scale, nref), fmaf(sv[e + u + 1], scale, nref)));
+                    pw[(e + u) >> 1] = w;
+                    acc = __hadd2(acc, *reinterpret_cast<const __half2*>(&w));
+                }
+                l0 += __low2float(acc); l1 += __high2float(acc);
+            }
+#else
             #pragma unroll
             for (int e = 0; e < 64; e += 2) {
                 const float e0 = ex2_approx(fmaf(sv[e], scale, nref)), e1 = ex2_approx(fmaf(sv[e + 1], scale, nref));
                 l0 += e0; l1 += e1;
                 pw[e >> 1] = pack_h2(e0, e1);
             }
+#endif
         };
         for (int j = 0; j < n_tiles; ++j) {
             if (!mbar_wait_warp(&s_full[blk], j & 1)) { failed = true; break; }

@@ -90,6 +90,16 @@ struct GemmDecodeParams {
     int* status;
     int m, k, c_fp32;
     int aligned;                       // 1: every CTA owns whole column blocks (no block is shared), 0: stream-K over units
+    // Table mode (the kernel's MULTI form, exl3_mgemm): `slots` products over tensors picked from device-resident tables.
+    // Slot j uses tensor indices[j] (j itself when indices is NULL; a negative entry leaves the slot untouched), reads
+    // the activations a_frag[0] + j * slot stride and writes C[0] + j * m * n, scaled by weights[j] when given.  All
+    // tensors have n[0] columns; the column blocks of slot j are blocks [j * n/128, (j + 1) * n/128).
+    const uint32_t* const* trellis_tab;
+    const half* const* svh_tab;
+    const int64_t* indices;
+    const half* weights;
+    int slots;
+    long long c_slot_stride;           // elements between the outputs of consecutive slots
 };
 
 __device__ __forceinline__ void gd_tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
@@ -162,23 +172,20 @@ __device__ __forceinline__ void gd_slot(const uint32_t* __restrict__ sb, int ch,
 // k = 64 kslot + 16 r + 2 t + (w & 1) + 8 (w >> 1), duplicated into both halves.
 struct GemmDecodePrologueArgs { const half* suh[GD_MAX_SEG]; uint32_t* a_frag[GD_MAX_SEG]; float* rowsum[GD_MAX_SEG]; };
 
-__global__ void __launch_bounds__(256) gemm_decode_prologue_kernel(const half* __restrict__ A, const GemmDecodePrologueArgs args,
-                                                                   int m, int k)
+// one CTA: batch-row slot b of one tensor's activations
+__device__ __forceinline__ void gd_prologue_row(const half* __restrict__ Arow, const half* __restrict__ suh, uint32_t* __restrict__ out,
+                                                float* __restrict__ rowsum, int b, bool valid, int k)
 {
     __shared__ float sh[8];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.x, seg = blockIdx.y;
-    const half* __restrict__ suh = args.suh[seg];
-    uint32_t* __restrict__ out = args.a_frag[seg];
     const int set = b >> 3, g = b & 7;
     const int q = lane & 3;                                  // position of the lane's 4 values inside a 16-k tile row
     const int t0 = 2 * (q & 1), w0 = 2 * (q >> 1);
     float part = 0.0f;
     for (int blk = warp; blk < k / 128; blk += 8) {
         uint32_t h0 = 0, h1 = 0, h2 = 0, h3 = 0;
-        if (b < m) {
-            uint2 raw = reinterpret_cast<const uint2*>(A + (size_t)b * k + blk * 128)[lane];
+        if (valid) {
+            uint2 raw = reinterpret_cast<const uint2*>(Arow + blk * 128)[lane];
             half2 x = *reinterpret_cast<half2*>(&raw.x), y = *reinterpret_cast<half2*>(&raw.y);
             if (suh) {
                 uint2 sr = reinterpret_cast<const uint2*>(suh + blk * 128)[lane];
@@ -217,15 +224,38 @@ __global__ void __launch_bounds__(256) gemm_decode_prologue_kernel(const half* _
     if (threadIdx.x == 0) {
         float s = 0.0f;
         for (int w = 0; w < 8; ++w) s += sh[w];
-        args.rowsum[seg][b] = s;
+        rowsum[b] = s;
     }
+}
+
+static __global__ void __launch_bounds__(256) gemm_decode_prologue_kernel(const half* __restrict__ A, const GemmDecodePrologueArgs args,
+                                                                   int m, int k)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int b = blockIdx.x, seg = blockIdx.y;
+    gd_prologue_row(A + (size_t)b * k, args.suh[seg], args.a_frag[seg], args.rowsum[seg], b, b < m, k);
+}
+
+// Table mode: grid (row slots, product slots).  Slot j transforms rows of A[j] (or of A[0] when a_slot_stride is 0) with
+// the sign vector of the tensor it uses; an unused slot (negative index) gets zeros.
+static __global__ void __launch_bounds__(256) gemm_decode_prologue_multi_kernel(const half* __restrict__ A, size_t a_slot_stride,
+                                                                         const half* const* __restrict__ suh_tab,
+                                                                         const int64_t* __restrict__ indices, uint32_t* a_frag,
+                                                                         float* rowsum, int rows_per_slot, int m, int k)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int b = blockIdx.x, j = blockIdx.y;
+    const int mat = indices ? (int)indices[j] : j;
+    const half* suh = mat >= 0 ? suh_tab[mat] : nullptr;
+    gd_prologue_row(A + j * a_slot_stride + (size_t)b * k, suh, a_frag + (size_t)j * (rows_per_slot / 8) * (k / 64) * 4 * 32 * 4,
+                    rowsum + (size_t)j * rows_per_slot, b, b < m && mat >= 0, k);
 }
 
 // Output transform of one row of a 128-column block held by a warp (lane = 4 consecutive columns): codebook-2 affine
 // map, 128-point Hadamard, svh, store.
 template <int CB>
 __device__ __forceinline__ void gd_store_row(float4 v, int lane, float rowsum, const half* __restrict__ svh, void* Cout, size_t off,
-                                             int col0, int c_fp32)
+                                             int col0, int c_fp32, float r128 = GD_R128)
 {
     if constexpr (CB == 2) {
         const float rs = rowsum * GD_MUL1_DELTA;
@@ -243,7 +273,7 @@ __device__ __forceinline__ void gd_store_row(float4 v, int lane, float rowsum, c
             v.x = (up ? -v.x : v.x) + p0; v.y = (up ? -v.y : v.y) + p1;
             v.z = (up ? -v.z : v.z) + p2; v.w = (up ? -v.w : v.w) + p3;
         }
-        v.x *= GD_R128; v.y *= GD_R128; v.z *= GD_R128; v.w *= GD_R128;
+        v.x *= r128; v.y *= r128; v.z *= r128; v.w *= r128;
         uint2 sr = *reinterpret_cast<const uint2*>(svh + col0 + lane * 4);
         half2 sa2 = *reinterpret_cast<half2*>(&sr.x), sb2 = *reinterpret_cast<half2*>(&sr.y);
         if (c_fp32) {
@@ -272,7 +302,7 @@ __device__ __forceinline__ void gd_store_row(float4 v, int lane, float rowsum, c
 // where the block is shared, transforms and stores, and then hands the tile back (an mbarrier the other warps test before
 // their next drop, several units later).  While that warp waits on the arrival counter of the exchange, the other warps
 // of its scheduler use its issue slots.
-template <int K, int CB, int MT>
+template <int K, int CB, int MT, bool MULTI = false>
 __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid_constant__ CUtensorMap rmap0,
                                                                    const __grid_constant__ CUtensorMap rmap1,
                                                                    const __grid_constant__ CUtensorMap rmap2,
@@ -298,8 +328,18 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
     const int nunits = (int)(u1 - u0);
     const int mrows = p.m;
     const int nbg0 = (int)(u0 / KC), kc0 = (int)(u0 - (long long)nbg0 * KC);
-    auto seg_of = [&](int nbg) -> int { return (nbg >= p.blk_end[0]) + (nbg >= p.blk_end[1]); };
-    auto col0_of = [&](int nbg, int seg) -> int { return (nbg - (seg == 0 ? 0 : (seg == 1 ? p.blk_end[0] : p.blk_end[1]))) * 128; };
+    const int bpm = p.n[0] >> 7;                                       // column blocks per tensor (table mode)
+    auto seg_of = [&](int nbg) -> int {
+        if constexpr (MULTI) return nbg / bpm;
+        else return (nbg >= p.blk_end[0]) + (nbg >= p.blk_end[1]);
+    };
+    auto col0_of = [&](int nbg, int seg) -> int {
+        if constexpr (MULTI) return (nbg - seg * bpm) * 128;
+        else return (nbg - (seg == 0 ? 0 : (seg == 1 ? p.blk_end[0] : p.blk_end[1]))) * 128;
+    };
+    // table mode: the tensor a slot uses, or -1
+    auto mat_of = [&](int seg) -> int { return p.indices ? (int)p.indices[seg] : seg; };
+    const size_t afrag_slot = (size_t)MT * (p.k / 64) * GD_SLOT_ROWS * 32;        // uint4 per slot of activations (table mode)
 
     GD_STAMP(0);
 #ifdef GD_TRACE
@@ -340,17 +380,30 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
             const bool go = i < nunits && (round == 0 || mbar_try_wait(&eb[slot], (round - 1) & 1));
             if (go) {
                 const uint32_t bar = fb + 8u * slot;
-                if (kc * GD_UNIT_K + ks * (GD_SLOT_ROWS * 16) < p.k) {
-                    const int seg = seg_of(nbg);
-                    const CUtensorMap* rmap = seg == 0 ? &rmap0 : (seg == 1 ? &rmap1 : &rmap2);
+                const int seg = seg_of(nbg);
+                const int mat = MULTI ? mat_of(seg) : 0;
+                if (kc * GD_UNIT_K + ks * (GD_SLOT_ROWS * 16) < p.k && mat >= 0) {
                     const uint32_t dst = ring + slot * SM::SLOT_BYTES;
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)SM::SLOT_BYTES) : "memory");
-                    gd_tma_load_2d(dst, rmap, (col0_of(nbg, seg) >> 4) * 4 * K, kc * (GD_UNIT_K / 16) + ks * GD_SLOT_ROWS, bar);
+                    if constexpr (MULTI) {
+                        // the tensor comes out of a device table: four row copies of 8 tiles each instead of one tiled box
+                        const uint32_t* src = p.trellis_tab[mat] +
+                            ((size_t)(kc * (GD_UNIT_K / 16) + ks * GD_SLOT_ROWS) * (p.n[0] >> 4) + (col0_of(nbg, seg) >> 4)) * 8 * K;
+                        #pragma unroll
+                        for (int r = 0; r < GD_SLOT_ROWS; ++r)
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                         ::"r"(dst + (uint32_t)(r * (SM::CODE_BYTES / GD_SLOT_ROWS))), "l"(src + (size_t)r * (p.n[0] >> 4) * 8 * K),
+                                           "r"((uint32_t)(SM::CODE_BYTES / GD_SLOT_ROWS)), "r"(bar) : "memory");
+                    } else {
+                        const CUtensorMap* rmap = seg == 0 ? &rmap0 : (seg == 1 ? &rmap1 : &rmap2);
+                        gd_tma_load_2d(dst, rmap, (col0_of(nbg, seg) >> 4) * 4 * K, kc * (GD_UNIT_K / 16) + ks * GD_SLOT_ROWS, bar);
+                    }
                     if constexpr (SM::ACT_BYTES > 0) {
                         // The launch may overlap the tail of the kernel that writes the activations (programmatic dependent
                         // launch): the codes above do not depend on it, the activations do.
                         if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
-                        const uint4* afr = (seg == 0 ? p.a_frag[0] : (seg == 1 ? p.a_frag[1] : p.a_frag[2]));
+                        const uint4* afr = MULTI ? p.a_frag[0] + (size_t)seg * afrag_slot
+                                                 : (seg == 0 ? p.a_frag[0] : (seg == 1 ? p.a_frag[1] : p.a_frag[2]));
                         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                                      ::"r"(dst + (uint32_t)SM::CODE_BYTES), "l"(afr + (size_t)(kc * GD_KSL + ks) * kslot_stride),
                                        "r"((uint32_t)SM::ACT_BYTES), "r"(bar) : "memory");
@@ -392,13 +445,14 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
         #pragma unroll 1
         for (int i = 0; i < nunits; ++i) {
             if (++kc == KC) { kc = 0; ++nbg; }
-            const bool active = kc * GD_UNIT_K + ks * (GD_SLOT_ROWS * 16) < p.k;
+            const bool active = kc * GD_UNIT_K + ks * (GD_SLOT_ROWS * 16) < p.k && (!MULTI || mat_of(seg_of(nbg)) >= 0);
             if (!failed) {
                 uint4 af[MT][GD_SLOT_ROWS];
                 if (SM::ACT_BYTES == 0 && active) {
                     // batch rows 8 set + g, k = 64 kslot + 16 r + {2t, 2t+1, 2t+8, 2t+9}
                     const int seg = seg_of(nbg);
-                    const uint4* afr = (seg == 0 ? p.a_frag[0] : (seg == 1 ? p.a_frag[1] : p.a_frag[2]));
+                    const uint4* afr = MULTI ? p.a_frag[0] + (size_t)seg * afrag_slot
+                                             : (seg == 0 ? p.a_frag[0] : (seg == 1 ? p.a_frag[1] : p.a_frag[2]));
                     const int kslot = kc * GD_KSL + ks;
                     #pragma unroll
                     for (int s = 0; s < MT; ++s)
@@ -452,8 +506,19 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
             const int n0 = col0_of(nbg, seg);
             const half* svh = seg == 0 ? p.svh[0] : (seg == 1 ? p.svh[1] : p.svh[2]);
             void* Cout = seg == 0 ? p.C[0] : (seg == 1 ? p.C[1] : p.C[2]);
-            const int n = seg == 0 ? p.n[0] : (seg == 1 ? p.n[1] : p.n[2]);
+            int n = seg == 0 ? p.n[0] : (seg == 1 ? p.n[1] : p.n[2]);
             const float* rsum = seg == 0 ? p.rowsum[0] : (seg == 1 ? p.rowsum[1] : p.rowsum[2]);
+            float r128 = GD_R128;
+            bool store = true;
+            if constexpr (MULTI) {
+                const int mat = mat_of(seg);
+                store = mat >= 0;                         // an unused slot's rows of C are left as they are
+                n = p.n[0];
+                svh = store ? p.svh_tab[mat] : nullptr;
+                Cout = p.c_fp32 ? (void*)((float*)p.C[0] + (size_t)seg * p.c_slot_stride) : (void*)((half*)p.C[0] + (size_t)seg * p.c_slot_stride);
+                rsum = p.rowsum[0] + (size_t)seg * SM::ROWS;
+                if (p.weights) r128 *= __half2float(p.weights[seg]);
+            }
             // sum of the 8 k-slices of one row, in slice order; lane = 4 consecutive columns
             auto row_sum = [&](int row) -> float4 {
                 float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -473,8 +538,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
             }
             const int ncontrib = c_last - c_first + 1;
             if (ncontrib == 1) {
-                for (int row = 0; row < mrows; ++row)
-                    gd_store_row<CB>(row_sum(row), lane, CB == 2 ? rsum[row] : 0.f, svh, Cout, (size_t)row * n + n0 + lane * 4, n0, p.c_fp32);
+                for (int row = 0; row < mrows && store; ++row)
+                    gd_store_row<CB>(row_sum(row), lane, CB == 2 ? rsum[row] : 0.f, svh, Cout, (size_t)row * n + n0 + lane * 4, n0, p.c_fp32, r128);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_red_free);
             } else {
@@ -516,8 +581,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
                         }
                         #pragma unroll
                         for (int r = 0; r < 8; ++r)
-                            if (row0 + r < mrows)
-                                gd_store_row<CB>(a[r], lane, CB == 2 ? rsum[row0 + r] : 0.f, svh, Cout, (size_t)(row0 + r) * n + n0 + lane * 4, n0, p.c_fp32);
+                            if (row0 + r < mrows && store)
+                                gd_store_row<CB>(a[r], lane, CB == 2 ? rsum[row0 + r] : 0.f, svh, Cout, (size_t)(row0 + r) * n + n0 + lane * 4, n0, p.c_fp32, r128);
                     }
                 }
             }

@@ -54,7 +54,8 @@ extern "C" int exl3_linear_forward(exl3_ctx* ctx, exl3_stream stream, const exl3
     if (in_last < k) need += (((size_t)rows * k * 2) + 255) & ~(size_t)255;
     if (post) need += (((size_t)rows * n * 2) + 255) & ~(size_t)255;
     if (need > ctx->ws_bytes / 2) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "linear_forward: context scratch too small");
-    uint8_t* top = ctx->ws + ctx->ws_bytes - ((need + 255) & ~(size_t)255);
+    const size_t lower = (ctx->ws_bytes - need) & ~(size_t)255;      // what stays for the GEMM, 256-byte aligned
+    uint8_t* top = ctx->ws + lower;
     const half* xin = (const half*)x;
     if (in_last < k) {
         half* xp = (half*)top; top += (((size_t)rows * k * 2) + 255) & ~(size_t)255;
@@ -66,7 +67,7 @@ extern "C" int exl3_linear_forward(exl3_ctx* ctx, exl3_stream stream, const exl3
     half* yp = post ? (half*)top : (half*)y;
     // the GEMM must not reach into the scratch taken above: lend it the lower part only
     const size_t ws_saved = ctx->ws_bytes;
-    ctx->ws_bytes = ws_saved - ((need + 255) & ~(size_t)255);
+    ctx->ws_bytes = lower;
     int rc;
     if (L->w.trellis)
         rc = exl3_gemm(ctx, stream, xin, L->w.trellis, yp, L->w.suh, nullptr, L->w.svh, rows, k, n, L->w.K, 0, L->w.cb == 1, L->w.cb == 2);

@@ -24,6 +24,12 @@ class Linear(C.Structure):
                 ("k", C.c_int), ("n", C.c_int), ("K", C.c_int), ("cb", C.c_int)]
 
 
+class LinearLayer(C.Structure):
+    """exl3_linear_layer (include/exl3_abi.h): one linear layer with its padding, bias, trim and soft-cap policy."""
+    _fields_ = [("w", Linear), ("dense", C.c_void_p), ("bias", C.c_void_p), ("in_unpadded", C.c_int),
+                ("out_unpadded", C.c_int), ("trim_padded_out", C.c_int), ("softcap", C.c_float)]
+
+
 _lib = None
 
 
@@ -234,6 +240,48 @@ class Ctx:
         _chk(x, torch.float16, "x"); _chk(y, torch.float16, "y"); _chk(z, torch.float16, "z")
         self.check(lib().exl3_silu_mul(self._h, self.stream(stream), _ptr(x), _ptr(y), _ptr(z), C.c_float(act_limit),
                                        C.c_int64(x.numel())), "silu_mul")
+
+    def gelu_mul(self, x, y, z, act_limit=0.0, stream=None):
+        """src/ffi.rs:126."""
+        _chk(x, torch.float16, "x"); _chk(y, torch.float16, "y"); _chk(z, torch.float16, "z")
+        self.check(lib().exl3_gelu_mul(self._h, self.stream(stream), _ptr(x), _ptr(y), _ptr(z), C.c_float(act_limit),
+                                       C.c_int64(x.numel())), "gelu_mul")
+
+    def relu2_mul(self, x, y, z, act_limit=0.0, stream=None):
+        """src/ffi.rs:127."""
+        _chk(x, torch.float16, "x"); _chk(y, torch.float16, "y"); _chk(z, torch.float16, "z")
+        self.check(lib().exl3_relu2_mul(self._h, self.stream(stream), _ptr(x), _ptr(y), _ptr(z), C.c_float(act_limit),
+                                        C.c_int64(x.numel())), "relu2_mul")
+
+    def softcap(self, x, y, factor, stream=None):
+        """src/ffi.rs:136: y = tanh(x / factor) * factor, fp16 or fp32 (in place when y is x)."""
+        _chk(x, (torch.float16, torch.float32), "x"); _chk(y, x.dtype, "y")
+        self.check(lib().exl3_softcap(self._h, self.stream(stream), _ptr(x), _ptr(y), C.c_float(factor),
+                                      C.c_int64(x.numel()), int(x.dtype == torch.float32)), "softcap")
+
+    def exl3_mgemm(self, a, trellis_tab, c, suh_tab, svh_tab, K, indices=None, weights=None, mcg=False, mul1=False,
+                   num_tokens=1, a_had=None, stream=None):
+        """src/ffi.rs:28-42.  a [bszm_in, m, k] fp16, c [bszm_out, m, n] fp16|fp32; *_tab int64 device tensors of device
+        pointers (one per tensor of the table); indices int64 [bszm] and weights fp16 [bszm] on the device, or None."""
+        _chk(a, torch.float16, "a"); _chk(c, (torch.float16, torch.float32), "c")
+        for t, nm in ((trellis_tab, "trellis_tab"), (suh_tab, "suh_tab"), (svh_tab, "svh_tab")):
+            _chk(t, torch.int64, nm)
+        if indices is not None:
+            _chk(indices, torch.int64, "indices")
+        if weights is not None:
+            _chk(weights, torch.float16, "weights")
+        bszm_in, m, k = a.shape
+        bszm_out, _, n = c.shape
+        self.check(lib().exl3_mgemm(self._h, self.stream(stream), _ptr(a), _ptr(trellis_tab), _ptr(c), _ptr(suh_tab),
+                                    _ptr(a_had), _ptr(svh_tab), _ptr(indices), _ptr(weights), bszm_in, bszm_out, m, k, n,
+                                    K, int(c.dtype == torch.float32), int(mcg), int(mul1), num_tokens), "exl3_mgemm")
+
+    def linear_forward(self, layer, x, y, stream=None):
+        """Linear::forward (src/modules.rs:183-252): x [rows, in_last] fp16 -> y [rows, out] fp16; `layer` a LinearLayer."""
+        _chk(x, torch.float16, "x"); _chk(y, torch.float16, "y")
+        rows, in_last = x.shape
+        self.check(lib().exl3_linear_forward(self._h, self.stream(stream), C.byref(layer), _ptr(x), in_last, _ptr(y), rows),
+                   "linear_forward")
 
     def add(self, x, y, z, stream=None):
         _chk(x, torch.float16, "x"); _chk(y, torch.float16, "y"); _chk(z, torch.float16, "z")

@@ -330,8 +330,8 @@ EXL3_API int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_mod
                                void* scratch, size_t scratch_bytes, int64_t* out_tokens, float* logits);
 
 /* ------------------------------------------------------------------------------- the rest of the op surface
- * Every remaining exl3_shim_* symbol of src/ffi.rs has an entry point so that the crate links.  softcap, gelu_mul and
- * relu2_mul are implemented; the others return EXL3_ERR_UNSUPPORTED (with a message in exl3_last_error) until built:
+ * Every remaining exl3_shim_* symbol of src/ffi.rs has an entry point so that the crate links.  mgemm, softcap, gelu_mul
+ * and relu2_mul are implemented; the others return EXL3_ERR_UNSUPPORTED (with a message in exl3_last_error) until built:
  * they serve other model families (mixture-of-experts routing, gated-delta-net layers, vision towers) or the sampler. */
 
 /* exl3_shim_softcap (src/ffi.rs:123 -> kernels/softcap.cu:55-97): y = factor * tanh(x / factor), fp16 or fp32, in place allowed */
@@ -340,11 +340,14 @@ EXL3_API int exl3_softcap(exl3_ctx* ctx, exl3_stream stream, const void* x, void
  * act_limit != 0 clamps y to [-limit, limit] and act(x) to <= limit before the product */
 EXL3_API int exl3_gelu_mul(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* y, void* z, float act_limit, int64_t numel);
 EXL3_API int exl3_relu2_mul(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* y, void* z, float act_limit, int64_t numel);
-/* exl3_shim_mgemm (src/ffi.rs:28-42, csrc/exl3_shim.cpp:57-75 -> kernels/quant/exl3_gemm.cu:386-678): EXL3 product over a
- * device table of tensors chosen by device-resident indices.  A [bszm_in, m, k] fp16 (bszm_in = 1: every slot reads the
- * same rows), C [bszm_out, m, n]; trellis/suh/svh: device arrays of device pointers, one per matrix; indices int64
- * [bszm] (-1 = slot unused) or NULL (slot j uses matrix j); weights fp16 [bszm] or NULL: slot scales, after which the
- * slots of each of the num_tokens groups are summed into that group's row.  Not built. */
+/* exl3_shim_mgemm (src/ffi.rs:28-42, csrc/exl3_shim.cpp:57-75 -> kernels/quant/exl3_gemm.cu:386-678): EXL3 products over a
+ * device table of tensors chosen by device-resident indices (the MoE decode path; no routing readback).  There are
+ * bszm = max(bszm_in, bszm_out) slots.  Slot j multiplies A[j] (A [bszm_in, m, k] fp16; bszm_in = 1: every slot reads
+ * A[0]) with tensor indices[j] (int64 [bszm], device; NULL: tensor j; a negative entry skips the slot and leaves its rows
+ * of C untouched) into C[j] (C [bszm, m, n] fp16 or fp32).  trellis/suh/svh: device arrays of device pointers, one per
+ * tensor, all tensors k x n at K bits with one codebook.  weights (fp16 [bszm], device) or NULL: slot j is scaled by
+ * weights[j], and afterwards the bszm / num_tokens consecutive slots of each token are added in slot order (in C's
+ * precision, unused slots skipped) into C[t] for token t.  A_had is accepted and ignored. */
 EXL3_API int exl3_mgemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const void* const* trellis, void* C,
                         const void* const* suh, void* A_had, const void* const* svh, const int64_t* indices,
                         const void* weights, int bszm_in, int bszm_out, int m, int k, int n, int K, int c_fp32, int mcg,

@@ -188,8 +188,8 @@ void orc_had_r_128(const void* x, void* y, const uint16_t* pre, const uint16_t* 
  * multiplies by svh in fp16, fp32 C multiplies by float(svh)).  The accumulation here is in double: the reference's
  * own summation order is not defined (stream-K slices), and every fp32 order lies within ~1e-6 relative of this.
  * suh == NULL skips the input transform, svh == NULL the output transform (exl3_gemm.cu:138-152). */
-void orc_exl3_gemm(const uint16_t* A, const uint16_t* trellis, void* C, int c_fp32, const uint16_t* suh,
-                   const uint16_t* svh, int m, int k, int n, int K, int cb)
+static void exl3_gemm_impl(const uint16_t* A, const uint16_t* trellis, void* C, int c_fp32, const uint16_t* suh,
+                           const uint16_t* svh, int m, int k, int n, int K, int cb, float out_scale)
 {
     const float rs = 0.088388347648f;
     float* Ah = (float*)malloc((size_t)m * k * sizeof(float));
@@ -248,13 +248,28 @@ void orc_exl3_gemm(const uint16_t* A, const uint16_t* trellis, void* C, int c_fp
         for (int c0 = 0; c0 < n; c0 += 128) {
             float v[128];
             for (int i = 0; i < 128; ++i) v[i] = acc[(size_t)r * n + c0 + i];
-            if (svh) { fwht(v, 128); for (int i = 0; i < 128; ++i) v[i] *= rs; }
+            const float os = rs * out_scale;      /* the expert weight of exl3_mgemm folds into the transform's scale */
+            if (svh) { fwht(v, 128); for (int i = 0; i < 128; ++i) v[i] *= os; }
             for (int i = 0; i < 128; ++i) {
                 if (c_fp32) ((float*)C)[(size_t)r * n + c0 + i] = svh ? v[i] * h2f(svh[c0 + i]) : v[i];
                 else { uint16_t h = f2h(v[i]); ((uint16_t*)C)[(size_t)r * n + c0 + i] = svh ? hmul(h, svh[c0 + i]) : h; }
             }
         }
     free(acc);
+}
+
+void orc_exl3_gemm(const uint16_t* A, const uint16_t* trellis, void* C, int c_fp32, const uint16_t* suh,
+                   const uint16_t* svh, int m, int k, int n, int K, int cb)
+{
+    exl3_gemm_impl(A, trellis, C, c_fp32, suh, svh, m, k, n, K, cb, 1.0f);
+}
+
+/* One slot of exl3_mgemm (kernels/quant/exl3_gemm_kernel.cuh:146-247): the same product with the output transform's scale
+ * multiplied by the slot's weight (scale = 0.0884 * float(weight), :236-237). */
+void orc_exl3_gemm_scaled(const uint16_t* A, const uint16_t* trellis, void* C, int c_fp32, const uint16_t* suh,
+                          const uint16_t* svh, int m, int k, int n, int K, int cb, float out_scale)
+{
+    exl3_gemm_impl(A, trellis, C, c_fp32, suh, svh, m, k, n, K, cb, out_scale);
 }
 
 /* Dense fp16 GEMM with fp32-class accumulation, C fp16 or fp32.  kernels/hgemm.cu:19-78 (cublasGemmEx,

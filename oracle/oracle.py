@@ -98,6 +98,39 @@ def exl3_gemm(A, trellis, suh, svh, K, cb, c_fp32=False):
     return Cm
 
 
+def exl3_mgemm(A, trellis_list, suh_list, svh_list, C_init, K, cb, indices=None, weights=None, num_tokens=1):
+    """exl3_mgemm (kernels/quant/exl3_gemm.cu:386-678, exl3_gemm_kernel.cuh:88-314 with min/max_index = -1).
+    A [bszm_in, m, k] fp16; C_init [bszm, m, n] fp16 or fp32 (slots that are skipped keep their contents);
+    indices int64 [bszm] or None; weights fp16 [bszm] or None.  Returns the new C."""
+    A = _c(A, np.float16)
+    Cm = np.array(C_init, copy=True)
+    c_fp32 = Cm.dtype == np.float32
+    bszm = Cm.shape[0]
+    m, k = A.shape[1], A.shape[2]
+    n = Cm.shape[2]
+    for j in range(bszm):
+        mat = j if indices is None else int(indices[j])
+        if mat < 0:
+            continue
+        a = A[0] if A.shape[0] == 1 else A[j]
+        tr = _c(trellis_list[mat], np.int16)
+        out = np.empty((m, n), Cm.dtype)
+        w = 1.0 if weights is None else float(np.float16(weights[j]))
+        lib().orc_exl3_gemm_scaled(_p(_c(a, np.float16)), _p(tr), _p(out), C.c_int(c_fp32), _p(_c(suh_list[mat], np.float16)),
+                                   _p(_c(svh_list[mat], np.float16)), C.c_int(m), C.c_int(k), C.c_int(n), C.c_int(K),
+                                   C.c_int(cb), C.c_float(w))
+        Cm[j] = out
+    if weights is not None:
+        stride = bszm // num_tokens
+        for t in range(num_tokens):
+            acc = np.zeros((m, n), Cm.dtype)
+            for j in range(stride):
+                if indices is None or int(indices[t * stride + j]) >= 0:
+                    acc = (acc + Cm[t * stride + j]).astype(Cm.dtype)        # sequential adds in C's own precision
+            Cm[t] = acc
+    return Cm
+
+
 def hgemm(A, B, c_fp32=False):
     A = _c(A, np.float16)
     B = _c(B, np.float16)
@@ -145,6 +178,60 @@ def silu_mul(x, y):
     z = np.empty_like(x)
     lib().orc_silu_mul(_p(x), _p(y), _p(z), C.c_int64(x.size))
     return z
+
+
+def _act_mul(a32, y, act_limit):
+    a = a32.astype(np.float16)
+    y = _c(y, np.float16)
+    if act_limit != 0.0:
+        lim = np.float16(act_limit)
+        y = np.minimum(np.maximum(y, -lim), lim)
+        a = np.minimum(a, lim)
+    return (a * y).astype(np.float16)              # numpy's fp16 product: fp32 product rounded once
+
+
+def gelu_mul(x, y, act_limit=0.0):
+    """z = gelu_tanh(x) * y (kernels/activation_kernels.cuh:40-50,142-186): the activation in fp32, rounded to fp16; the
+    optional clamps and the product in fp16."""
+    a = _c(x, np.float16).astype(np.float32)
+    c = np.float32(0.797884560803)
+    g = np.float32(0.5) * a * (np.float32(1.0) + np.tanh(c * (a + np.float32(0.044715) * a * a * a)))
+    return _act_mul(g.astype(np.float32), y, act_limit)
+
+
+def relu2_mul(x, y, act_limit=0.0):
+    """z = relu(x)^2 * y (kernels/activation_kernels.cuh:52-58,142-186)."""
+    a = np.maximum(_c(x, np.float16).astype(np.float32), np.float32(0.0))
+    return _act_mul(a * a, y, act_limit)
+
+
+def softcap(x, factor):
+    """y = tanh(x / factor) * factor (kernels/softcap.cu:10-52): fp32 arithmetic, rounded to x's type."""
+    x = np.ascontiguousarray(x)
+    v = x.astype(np.float32) / np.float32(factor)
+    return (np.tanh(v) * np.float32(factor)).astype(x.dtype)
+
+
+def linear_forward(x, K, cb, k, n, trellis=None, suh=None, svh=None, dense=None, bias=None, out_unpadded=None,
+                   trim_padded_out=False, softcap_factor=0.0):
+    """Linear::forward (src/modules.rs:183-252): zero-extend x [rows, in_last] to the padded k, multiply (EXL3 tensor or a
+    dense fp16 weight [k, n]), add the bias, trim to the unpadded width, soft-cap; each step rounds to fp16 like the
+    tensor ops of the reference."""
+    x = _c(x, np.float16)
+    rows, in_last = x.shape
+    if in_last < k:
+        x = np.concatenate([x, np.zeros((rows, k - in_last), np.float16)], axis=1)
+    y = hgemm(x, dense) if dense is not None else exl3_gemm(x, trellis, suh, svh, K, cb)
+    if bias is not None:
+        y = (y + _c(bias, np.float16)[None, :]).astype(np.float16)
+    if trim_padded_out and out_unpadded is not None and out_unpadded < n:
+        y = np.ascontiguousarray(y[:, :out_unpadded])
+    if softcap_factor != 0.0:
+        f = np.float16(softcap_factor)
+        t = (y / f).astype(np.float16)                                   # fp16 division
+        t = np.tanh(t.astype(np.float32)).astype(np.float16)
+        y = (t * f).astype(np.float16)
+    return y
 
 
 def add(x, y):

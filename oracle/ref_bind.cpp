@@ -19,6 +19,7 @@
 #include "attention.cuh"
 #include "activation.cuh"
 #include "add.cuh"
+#include "softcap.cuh"
 #include "quant/exl3_gemm.cuh"
 #include "quant/hadamard.cuh"
 #include "quant/reconstruct.cuh"
@@ -60,6 +61,27 @@ int ref_exl3_gemm(const void* A, const void* B, void* C, const void* suh, void* 
         auto c = wrap(C, {m, n}, c_fp32 ? at::kFloat : at::kHalf);
         tag = exl3_gemm(a, b, c, owrap(suh, {k}, at::kHalf), owrap(A_had, {m, k}, at::kHalf),
                         owrap(svh, {n}, at::kHalf), force_shape_idx, mcg != 0, mul1 != 0, 0);
+    });
+    return rc ? rc : tag;
+}
+
+// exl3_shim_mgemm (csrc/exl3_shim.cpp:57-75): tables are int64 tensors of device pointers; indices int64 [1, bszm],
+// weights fp16 [1, bszm] (both optional)
+int ref_exl3_mgemm(const void* A, const void* B_tab, void* C, const void* suh_tab, void* A_had, const void* svh_tab,
+                   const void* indices, const void* weights, int num_mats, int bszm_in, int bszm_out, int m, int k, int n,
+                   int K, int c_fp32, int mcg, int mul1, int num_tokens)
+{
+    int tag = -1;
+    int rc = guarded([&] {
+        const int bszm = bszm_in > bszm_out ? bszm_in : bszm_out;
+        auto a = wrap(A, {bszm_in, m, k}, at::kHalf);
+        auto b = wrap(B_tab, {num_mats}, at::kLong);
+        auto c = wrap(C, {bszm_out, m, n}, c_fp32 ? at::kFloat : at::kHalf);
+        auto su = wrap(suh_tab, {num_mats}, at::kLong);
+        auto sv = wrap(svh_tab, {num_mats}, at::kLong);
+        auto ah = wrap(A_had, {bszm, m, k}, at::kHalf);
+        tag = exl3_mgemm(a, b, c, su, ah, sv, owrap(indices, {1, bszm}, at::kLong), owrap(weights, {1, bszm}, at::kHalf), K, -1,
+                         mcg != 0, mul1 != 0, -1, -1, 0, num_tokens, {}, {});
     });
     return rc ? rc : tag;
 }
@@ -194,6 +216,23 @@ int ref_silu_mul(const void* x, const void* y, void* z, int64_t rows, int64_t co
     return guarded([&] {
         auto tz = wrap(z, {rows, cols}, at::kHalf);
         silu_mul(wrap(x, {rows, cols}, at::kHalf), wrap(y, {rows, cols}, at::kHalf), tz, 0.0f);
+    });
+}
+
+// act: 0 gelu_mul, 1 relu2_mul (kernels/activation.cu:246-333)
+int ref_act_mul(int act, const void* x, const void* y, void* z, float act_limit, int64_t rows, int64_t cols)
+{
+    return guarded([&] {
+        auto tz = wrap(z, {rows, cols}, at::kHalf);
+        if (act == 0) gelu_mul(wrap(x, {rows, cols}, at::kHalf), wrap(y, {rows, cols}, at::kHalf), tz, act_limit);
+        else relu2_mul(wrap(x, {rows, cols}, at::kHalf), wrap(y, {rows, cols}, at::kHalf), tz, act_limit);
+    });
+}
+
+int ref_softcap(const void* x, void* y, float factor, int64_t rows, int64_t cols, int fp32)
+{
+    return guarded([&] {
+        softcap(wrap(x, {rows, cols}, fp32 ? at::kFloat : at::kHalf), wrap(y, {rows, cols}, fp32 ? at::kFloat : at::kHalf), factor);
     });
 }
 

@@ -2,6 +2,7 @@
 #include <algorithm>
 #include "attn_paged.cuh"
 #include "attn_tc.cuh"
+#include "attn_q4.cuh"
 
 namespace {
 
@@ -190,6 +191,38 @@ cudaError_t launch_attn_tc(exl3_ctx* ctx, const AttnParams& p, int max_items, cu
     return cudaPeekAtLastError();
 }
 
+// decode-class kernel over 4-bit pools: tensor maps over the code planes ([tokens][nkv * 16] words) and the scale planes
+// ([tokens][nkv * 4] halves, copied in 16-byte pairs of heads)
+cudaError_t launch_attn_q4(const AttnParams& p, dim3 grid, cudaStream_t st)
+{
+    EncodeTiledFn enc = attn_encode_tiled();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap maps[4];
+    const void* planes[4] = {p.qk, p.qv, p.sk, p.sv};
+    const cuuint64_t tokens = (cuuint64_t)p.pages * EXL3_PAGE;
+    for (int i = 0; i < 4; ++i) {
+        const bool codes = i < 2;
+        cuuint64_t dims[2] = {(cuuint64_t)p.nkv * (codes ? 16 : 4), tokens};
+        cuuint64_t strides[1] = {(cuuint64_t)p.nkv * (codes ? 64 : 8)};
+        cuuint32_t box[2] = {codes ? 16u : 8u, (cuuint32_t)AQ_TK};
+        cuuint32_t estr[2] = {1, 1};
+        if (enc(&maps[i], codes ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(planes[i]),
+                dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_q4_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AQ_SMEM);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    attn_q4_decode_kernel<<<grid, AQ_THREADS, AQ_SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], p);
+    return cudaPeekAtLastError();
+}
+
 // One pass = plan + attention + combine over the sequences whose packed row count lies in (rows_lo, rows_hi].
 int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int max_rows, int rows_lo, int rows_hi,
               bool decode_shape, bool quant, size_t* ws_off)
@@ -199,26 +232,30 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     const bool q4 = quant && p.k_bits == 4 && p.v_bits == 4;       // the common cache format has its own, smaller staging
     // long class on fp16 pools: tcgen05 kernel (256-row items) unless the context was switched to the mma.sync kernels
     // (its row maximum is taken on the raw scores, which needs a positive scale)
+    // (sequences with 17..128 packed rows - speculative verify - stay on it too: on 32 sequences x 8 query rows x 5 heads
+    // the 64-row mma.sync kernel measured 228 us against 224 us, at 16 and 24 query rows 373 / 383 us against 233 / 241 us)
     const bool use_tc = !decode_shape && !quant && ctx->mma_attn != 0 && p.scale_log2 > 0.f;
     const int rows_per_cta = decode_shape ? 16 : (use_tc ? ATC_CTA_ROWS : 64);
     const int rb_max = (max_rows + rows_per_cta - 1) / rows_per_cta;
     // resident CTAs per SM over all kv heads: about 3 for the mma.sync kernels, 1 for the tcgen05 kernel (all of TMEM)
     // (rounded down: one CTA more than fits would run alone in a second wave after all the others have finished)
+    // 4-bit pools, decode class: the kernel that builds the K operand from the codes (its scale copies are 16 bytes wide =
+    // two heads, so the kv head count must be even and the planes 16-byte aligned)
+    static const bool no_q4 = getenv("EXL3_B200_NO_Q4_ATTN") != nullptr;
+    const bool use_q4 = q4 && decode_shape && !no_q4 && p.nkv % 2 == 0 && aligned16(p.qk) && aligned16(p.qv) && aligned16(p.sk) && aligned16(p.sv);
     int per_sm = 1;
-    if (!use_tc) {
+    if (use_q4) per_sm = 3;
+    else if (!use_tc) {
         // CTAs of the mma.sync kernel that fit on an SM (bounded by shared memory: stages x 34.8 KB for fp16 pools)
         const size_t smem = quant ? (q4 ? AttnSmem<128, 4>::BYTES : AttnSmem<128, 8>::BYTES) : AttnSmem<128, 0>::BYTES;
         per_sm = std::max(1, std::min(q4 ? 4 : 3, (int)((227 * 1024) / (smem + 1024))));
     }
-    static const int tune_per_sm = getenv("EXL3_TUNE_PER_SM") ? atoi(getenv("EXL3_TUNE_PER_SM")) : 0;
-    static const int tune_items = getenv("EXL3_TUNE_ITEMS") ? atoi(getenv("EXL3_TUNE_ITEMS")) : 0;
-    if (tune_per_sm && quant) per_sm = tune_per_sm;
     const int grid_x = std::max(1, ctx->num_sms * per_sm / p.nkv);
     // tcgen05 kernel: two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs a
     // 133 KB partial per kv head written and read back (4 per slot was measured 20 % slower, 1 per slot 2 % slower).
-    // mma.sync kernels (units handed out dynamically, 8 KB partials): three per slot for fp16 pools, four for quantised.
-    // the quantised kernel spends most of its time scaling codes, so finer items balance it better (+11 % measured)
-    const int target_items = grid_x * (use_tc ? 2 : (quant ? (tune_items ? tune_items : 4) : 3));
+    // mma.sync kernels (units handed out dynamically, 8 KB partials): three per slot (two and four to eight measured
+    // 1 to 7 % slower on 64 decode sequences over 4-bit pools).
+    const int target_items = grid_x * (use_tc ? 2 : 3);
     // items <= target + sum of row blocks (every (sequence, row block) rounds its split count up once); the row blocks are
     // bounded by bsz * rb_max and, usually much tighter for ragged batches, by total_rows * G / rows_per_cta + bsz
     const long long rb_sum = std::min((long long)p.bsz * rb_max, ((long long)total_rows * G + rows_per_cta - 1) / rows_per_cta + p.bsz);
@@ -261,6 +298,7 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     if (!use_tc && cudaMemsetAsync(&plan->next, 0, sizeof(int), st) != cudaSuccess)      // the persistent kernel's work counter
         return exl3_fail(ctx, EXL3_ERR_CUDA, "attention: cudaMemsetAsync failed");
     if (use_tc) e = launch_attn_tc(ctx, p, max_items, st);
+    else if (use_q4) e = launch_attn_q4(p, grid, st);
     else if (q4)    e = decode_shape ? launch_attn<128, 1, 4, 4>(p, grid, st) : launch_attn<128, 4, 1, 4>(p, grid, st);
     else if (quant) e = decode_shape ? launch_attn<128, 1, 4, 8>(p, grid, st) : launch_attn<128, 4, 1, 8>(p, grid, st);
     else            e = decode_shape ? launch_attn<128, 1, 4, 0>(p, grid, st) : launch_attn<128, 4, 1, 0>(p, grid, st);

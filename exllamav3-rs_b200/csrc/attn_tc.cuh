@@ -100,7 +100,7 @@ __device__ __forceinline__ uint32_t ex2_h2(uint32_t x)
     return y;
 }
 #ifndef ATC_EXP_F16X2
-#define ATC_EXP_F16X2 1
+#define ATC_EXP_F16X2 0
 #endif
 __device__ __forceinline__ float fmax3(float a, float b, float c)
 {

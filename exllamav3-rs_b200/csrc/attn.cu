@@ -253,9 +253,10 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     const int grid_x = std::max(1, ctx->num_sms * per_sm / p.nkv);
     // tcgen05 kernel: two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs a
     // 133 KB partial per kv head written and read back (4 per slot was measured 20 % slower, 1 per slot 2 % slower).
-    // mma.sync kernels (units handed out dynamically, 8 KB partials): three per slot (two and four to eight measured
-    // 1 to 7 % slower on 64 decode sequences over 4-bit pools).
-    const int target_items = grid_x * (use_tc ? 2 : 3);
+    // mma.sync kernels (units handed out dynamically, 8 KB partials): three per slot; four for the generic quantised
+    // kernel, which spends most of its time scaling codes and balances better on finer items (8-bit pools, 64 decode
+    // sequences: 510 us against 598 us).
+    const int target_items = grid_x * (use_tc ? 2 : ((quant && !use_q4) ? 4 : 3));
     // items <= target + sum of row blocks (every (sequence, row block) rounds its split count up once); the row blocks are
     // bounded by bsz * rb_max and, usually much tighter for ragged batches, by total_rows * G / rows_per_cta + bsz
     const long long rb_sum = std::min((long long)p.bsz * rb_max, ((long long)total_rows * G + rows_per_cta - 1) / rows_per_cta + p.bsz);

@@ -266,21 +266,33 @@ def peaks():
 
 def time_gemm_op(ctx, torch, lins, x, y, reps=1):
     """Average device time of exl3_gemm over the given tensors in turn (each call reads weights no earlier call of the
-    last len(lins) - 1 touched: L2-cold when their total size exceeds L2).  Returns (seconds per call, launches per call)."""
+    last len(lins) - 1 touched: L2-cold when their total size exceeds L2).  The calls are captured once into a CUDA graph
+    on the context's side stream and the graph is replayed between two events on that stream, so that host launch cost
+    (two launches and a tensor-map encode per call, more than a 26 us kernel leaves room for) stays out of the kernel's
+    time.  Returns (seconds per call, launches per call)."""
+    import exl3b200
+    side = torch.cuda.ExternalStream(exl3b200.lib().exl3_side_stream(ctx.handle))
+    torch.cuda.synchronize()
     for l in lins[:3]:
-        ctx.exl3_gemm(x, l.trellis, y, l.suh, None, l.svh, mcg=True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
+        ctx.exl3_gemm(x, l.trellis, y, l.suh, None, l.svh, mcg=True, stream=side)
+    exl3b200.lib().exl3_sync_side_stream(ctx.handle)
     g0 = ctx.launch_count()
-    cur = torch.cuda.current_stream()
-    e0.record(cur)
+    gr = exl3b200.CudaGraph(ctx)
+    gr.capture_begin()
+    for l in lins:
+        ctx.exl3_gemm(x, l.trellis, y, l.suh, None, l.svh, mcg=True, stream=side)
+    gr.capture_end()
+    launches = (ctx.launch_count() - g0) // len(lins)
+    gr.replay()
+    exl3b200.lib().exl3_sync_side_stream(ctx.handle)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(side)
     for _ in range(reps):
-        for l in lins:
-            ctx.exl3_gemm(x, l.trellis, y, l.suh, None, l.svh, mcg=True)
-    e1.record(cur)
-    torch.cuda.synchronize()
-    n = reps * len(lins)
-    return e0.elapsed_time(e1) * 1e-3 / n, (ctx.launch_count() - g0) // n
+        gr.replay()
+    e1.record(side)
+    exl3b200.lib().exl3_sync_side_stream(ctx.handle)
+    ctx.poll_status()
+    return e0.elapsed_time(e1) * 1e-3 / (reps * len(lins)), launches
 
 
 def gemm_alg_bytes(m, k, n, K):

@@ -161,6 +161,114 @@ __global__ void __launch_bounds__(256) gemm_prologue_plain_kernel(const half* __
     }
 }
 
+
+// The same transform with the butterflies on the tensor core, for rows with an even number of 128-blocks: a warp takes
+// two blocks at a time.  H128 = H8 (x) H16 on the index i = 16 a + b: X[a][b] of both blocks goes through shared memory
+// into transposed MMA fragments (ldmatrix.trans), D0 = (H8 (+) H8) X contracts over a with the sign matrix as the A
+// operand, D0 - kept exact as an fp16 pair hi + lo - becomes the A operand of the second product Y = D0 H16, whose
+// columns are ordered so that a lane ends up with four consecutive outputs.  About a quarter of the instructions of the
+// shuffle version (which needs 20 shuffles per 4 values); sums are formed in another order than
+// hadamard_inner.cuh:93-147 does, so single results may differ from the shuffle version's by one fp16 step where the
+// fp32 value sits on a rounding boundary.
+__device__ __forceinline__ void gp_ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ uint32_t sign_pair(int i, int j0, int j1)
+{
+    const uint32_t lo = (__popc(i & j0) & 1) ? 0xBC00u : 0x3C00u, hi = (__popc(i & j1) & 1) ? 0xBC00u : 0x3C00u;
+    return lo | (hi << 16);
+}
+
+constexpr int GP_PAIRS = 4;          // block pairs per warp: their loads are all in flight before the first is used
+
+__global__ void __launch_bounds__(256) gemm_prologue_mma_kernel(const half* __restrict__ A, const ProloguePlainArgs args, int k,
+                                                                long long pairs_total)
+{
+    __shared__ __align__(16) uint8_t stage[8][512];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const long long pair0 = ((long long)blockIdx.x * 8 + warp) * GP_PAIRS;
+    if (pair0 >= pairs_total) return;
+    const int ppr = k / 256;                                   // block pairs per row
+    const half* __restrict__ suh = args.suh[blockIdx.y];
+    half* __restrict__ a_had = args.a_had[blockIdx.y];
+
+    // constant operands: H8 (+) H8 as A of the first product, H16 with permuted columns as B of the second
+    const uint32_t h8 = sign_pair(g, 2 * t, 2 * t + 1);
+    uint32_t hb[2][2];
+    #pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+        const int bp = 4 * (g >> 1) + 2 * nb + (g & 1);        // output column b' of MMA column g in column block nb
+        hb[nb][0] = sign_pair(bp, 2 * t, 2 * t + 1);
+        hb[nb][1] = sign_pair(bp, 2 * t + 8, 2 * t + 9);
+    }
+
+    // (x o suh) of every pair: lane = 8 consecutive values of the 256
+    uint4 xs[GP_PAIRS];
+    size_t base[GP_PAIRS];
+    #pragma unroll
+    for (int u = 0; u < GP_PAIRS; ++u) {
+        const long long pair = pair0 + u < pairs_total ? pair0 + u : pairs_total - 1;       // the tail repeats the last pair
+        const size_t row = (size_t)(pair / ppr);
+        const int col0 = (int)(pair - (long long)row * ppr) * 256;
+        base[u] = row * k + col0;
+        xs[u] = reinterpret_cast<const uint4*>(A + base[u])[lane];
+        const uint4 sg = reinterpret_cast<const uint4*>(suh + col0)[lane];
+        half2* xh = reinterpret_cast<half2*>(&xs[u]);
+        const half2* sh = reinterpret_cast<const half2*>(&sg);
+        #pragma unroll
+        for (int e = 0; e < 4; ++e) xh[e] = __hmul2(xh[e], sh[e]);
+    }
+    #pragma unroll
+    for (int u = 0; u < GP_PAIRS; ++u) {
+        if (pair0 + u >= pairs_total) break;                   // warp-uniform
+        *reinterpret_cast<uint4*>(stage[warp] + lane * 16) = xs[u];
+        __syncwarp();
+        // four 8x8 matrices, transposed on the way out: (block 0, b 0..7), (block 0, b 8..15), (block 1, ...), (block 1, ...)
+        uint32_t r0, r1, r2, r3;
+        {
+            const int mat = lane >> 3, rr = lane & 7;          // row a = rr of matrix mat
+            gp_ldsm_x4_t(r0, r1, r2, r3, stage[warp] + (mat >> 1) * 256 + rr * 32 + (mat & 1) * 16);
+        }
+        __syncwarp();                                          // the staging buffer is free for the next pair
+        float d0[2][4];
+        #pragma unroll
+        for (int bh = 0; bh < 2; ++bh) {
+            d0[bh][0] = d0[bh][1] = d0[bh][2] = d0[bh][3] = 0.f;
+            gd_mma(d0[bh], h8, 0u, 0u, h8, bh ? r1 : r0, bh ? r3 : r2);
+        }
+        // D0[(block, a')][b] -> A operand of the second product, as hi + lo
+        uint32_t ahi[4], alo[4];
+        #pragma unroll
+        for (int bh = 0; bh < 2; ++bh)
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float p = d0[bh][2 * h], q = d0[bh][2 * h + 1];
+                const half2 hi = __floats2half2_rn(p, q);
+                const half2 lo = __floats2half2_rn(p - __low2float(hi), q - __high2float(hi));
+                ahi[2 * bh + h] = *reinterpret_cast<const uint32_t*>(&hi);
+                alo[2 * bh + h] = *reinterpret_cast<const uint32_t*>(&lo);
+            }
+        float y[2][4];
+        #pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+            y[nb][0] = y[nb][1] = y[nb][2] = y[nb][3] = 0.f;
+            gd_mma(y[nb], ahi[0], ahi[1], ahi[2], ahi[3], hb[nb][0], hb[nb][1]);
+            gd_mma(y[nb], alo[0], alo[1], alo[2], alo[3], hb[nb][0], hb[nb][1]);
+        }
+        // lane holds, for row a' = g of block 0 ([0], [1]) and of block 1 ([2], [3]), the outputs b' = 4t .. 4t+3
+        #pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            const half2 p = __floats2half2_rn(y[0][2 * blk] * GS_R128, y[0][2 * blk + 1] * GS_R128);
+            const half2 q = __floats2half2_rn(y[1][2 * blk] * GS_R128, y[1][2 * blk + 1] * GS_R128);
+            uint2 o; o.x = *reinterpret_cast<const uint32_t*>(&p); o.y = *reinterpret_cast<const uint32_t*>(&q);
+            *reinterpret_cast<uint2*>(a_had + base[u] + blk * 128 + 16 * g + 4 * t) = o;
+        }
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -278,7 +386,13 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
         p.trellis[i] = (const uint32_t*)trellis[j]; p.C[i] = C[j]; p.svh[i] = svh[j]; p.n[i] = n[j];
         p.blk_end[i] = i < nseg ? blocks : 0x7fffffff;
     }
-    gemm_prologue_plain_kernel<<<dim3(m, nseg), 256, 0, st>>>(A, pa, k);
+    bool all_signed = true;
+    for (int i = 0; i < nseg; ++i) all_signed = all_signed && pa.suh[i] != nullptr;
+    if (k % 256 == 0 && all_signed) {
+        const long long pairs = (long long)m * (k / 256);
+        gemm_prologue_mma_kernel<<<dim3((unsigned)((pairs + 8 * GP_PAIRS - 1) / (8 * GP_PAIRS)), nseg), 256, 0, st>>>(A, pa, k, pairs);
+    } else
+        gemm_prologue_plain_kernel<<<dim3(m, nseg), 256, 0, st>>>(A, pa, k);
     ctx->launches++;
     p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
     cudaError_t e = launch_tc_k(K, cb, ctx->use_pair != 0, amap, rmap, p, blocks, st);

@@ -103,27 +103,6 @@ extern "C" int exl3_gated_rms_norm(exl3_ctx* ctx, exl3_stream, const void*, cons
                                    int, int)
 { return not_built(ctx, "gated_rms_norm"); }
 
-extern "C" int exl3_apply_rep_pens(exl3_ctx* ctx, exl3_stream, const void*, void*, const int64_t*, float, int, int, int, int, int)
-{ return not_built(ctx, "apply_rep_pens"); }
-
-extern "C" int exl3_apply_pres_freq_pens(exl3_ctx* ctx, exl3_stream, const void*, void*, const int64_t*, float, float, int, int, int, int, int)
-{ return not_built(ctx, "apply_pres_freq_pens"); }
-
-extern "C" int exl3_gumbel_sample(exl3_ctx* ctx, exl3_stream, const void*, int, int64_t*, int, int, int, uint32_t)
-{ return not_built(ctx, "gumbel_sample"); }
-
-extern "C" int exl3_gumbel_noise_f32(exl3_ctx* ctx, exl3_stream, const float*, float*, int64_t, uint32_t)
-{ return not_built(ctx, "gumbel_noise_f32"); }
-
-extern "C" int exl3_cache_rotate(exl3_ctx* ctx, exl3_stream, void*, const int32_t*, void*, int, int, size_t)
-{ return not_built(ctx, "cache_rotate"); }
-
-extern "C" int exl3_mul_sigmoid_(exl3_ctx* ctx, exl3_stream, void*, const void*, int64_t)
-{ return not_built(ctx, "mul_sigmoid_"); }
-
-extern "C" int exl3_deinterleave_qg(exl3_ctx* ctx, exl3_stream, const void*, void*, void*, int, int, int)
-{ return not_built(ctx, "deinterleave_qg"); }
-
 extern "C" int exl3_gdn_fused_op_2(exl3_ctx* ctx, exl3_stream, const void*, const void*, const void*, const void*, void*, void*, float,
                                    int, int, int)
 { return not_built(ctx, "gdn_fused_op_2"); }

@@ -295,6 +295,59 @@ class Ctx:
                                             int(logits.dtype == torch.float32), _ptr(ids), rows, n, max_logit),
                    "argmax_sample")
 
+    def apply_rep_pens(self, in_logits, out_logits, past_ids, rep_p, sustain_range, decay_range, stream=None):
+        """src/ffi.rs:513-515: in_logits [1, vocab] fp16|fp32, out_logits fp32, past_ids int64 [1, past_len]."""
+        _chk(in_logits, (torch.float16, torch.float32), "in_logits"); _chk(out_logits, torch.float32, "out_logits")
+        _chk(past_ids, torch.int64, "past_ids")
+        self.check(lib().exl3_apply_rep_pens(self._h, self.stream(stream), _ptr(in_logits), int(in_logits.dtype == torch.float32),
+                                             _ptr(out_logits), _ptr(past_ids), C.c_float(rep_p), sustain_range, decay_range,
+                                             in_logits.shape[0], in_logits.shape[1], past_ids.numel()), "apply_rep_pens")
+
+    def apply_pres_freq_pens(self, in_logits, out_logits, past_ids, pres_p, freq_p, sustain_range, decay_range, stream=None):
+        """src/ffi.rs:518-520."""
+        _chk(in_logits, (torch.float16, torch.float32), "in_logits"); _chk(out_logits, torch.float32, "out_logits")
+        _chk(past_ids, torch.int64, "past_ids")
+        self.check(lib().exl3_apply_pres_freq_pens(self._h, self.stream(stream), _ptr(in_logits),
+                                                   int(in_logits.dtype == torch.float32), _ptr(out_logits), _ptr(past_ids),
+                                                   C.c_float(pres_p), C.c_float(freq_p), sustain_range, decay_range,
+                                                   in_logits.shape[0], in_logits.shape[1], past_ids.numel()), "apply_pres_freq_pens")
+
+    def gumbel_sample(self, logits, ids, max_logit=0, random=0, stream=None):
+        """src/ffi.rs:528-530: logits [rows, n] fp16|fp32, ids int64 [rows] or [rows, 1]."""
+        _chk(logits, (torch.float16, torch.float32), "logits"); _chk(ids, torch.int64, "ids")
+        rows, n = logits.shape
+        self.check(lib().exl3_gumbel_sample(self._h, self.stream(stream), _ptr(logits), int(logits.dtype == torch.float32),
+                                            _ptr(ids), rows, n, max_logit, C.c_uint32(random)), "gumbel_sample")
+
+    def gumbel_noise_f32(self, logits_in, logits_out, random=0, stream=None):
+        """src/ffi.rs:533-535."""
+        _chk(logits_in, torch.float32, "logits_in"); _chk(logits_out, torch.float32, "logits_out")
+        self.check(lib().exl3_gumbel_noise_f32(self._h, self.stream(stream), _ptr(logits_in), _ptr(logits_out),
+                                               C.c_int64(logits_in.numel()), C.c_uint32(random)), "gumbel_noise_f32")
+
+    def cache_rotate(self, cache, order, temp, stream=None):
+        """src/ffi.rs:538-540: cache [pages, ...] contiguous, order int32 [2 n], temp one page of scratch."""
+        _chk(order, torch.int32, "order")
+        pages = cache.shape[0]
+        page_bytes = cache.numel() * cache.element_size() // pages
+        if temp.numel() * temp.element_size() != page_bytes:
+            raise Exl3Error("cache_rotate: temp must hold exactly one page")
+        self.check(lib().exl3_cache_rotate(self._h, self.stream(stream), _ptr(cache), _ptr(order), _ptr(temp), pages,
+                                           order.numel() // 2, C.c_size_t(page_bytes)), "cache_rotate")
+
+    def mul_sigmoid_(self, x, y, stream=None):
+        """src/ffi.rs:616-618: x *= sigmoid(y) in place."""
+        _chk(x, torch.float16, "x"); _chk(y, torch.float16, "y")
+        self.check(lib().exl3_mul_sigmoid_(self._h, self.stream(stream), _ptr(x), _ptr(y), C.c_int64(x.numel())), "mul_sigmoid_")
+
+    def deinterleave_qg(self, qg, q, g, head_dim, stream=None):
+        """src/ffi.rs:622-624: qg [rows, heads * 2 * head_dim] -> q, g [rows, heads * head_dim]."""
+        _chk(qg, torch.float16, "qg"); _chk(q, torch.float16, "q"); _chk(g, torch.float16, "g")
+        rows = qg.shape[0]
+        heads = qg.shape[-1] // (2 * head_dim)
+        self.check(lib().exl3_deinterleave_qg(self._h, self.stream(stream), _ptr(qg), _ptr(q), _ptr(g), rows, heads, head_dim),
+                   "deinterleave_qg")
+
     def embed(self, ids, table, out, stream=None):
         _chk(ids, torch.int64, "ids"); _chk(table, torch.float16, "table"); _chk(out, torch.float32, "out")
         self.check(lib().exl3_embed(self._h, self.stream(stream), _ptr(ids), _ptr(table), _ptr(out), ids.numel(),
@@ -467,6 +520,81 @@ class Pool:
         arr = (C.c_int32 * max(len(pages), 1))(*pages)
         if lib().exl3_pool_release(self._h, arr, len(pages)) != 0:
             raise Exl3Error("release failed")
+
+
+class Checkpoint:
+    """A safetensors file opened through exl3_checkpoint_* (src/safetensors.rs): header index, tensor reads into device
+    memory, and Linear::load (src/modules.rs:97-165) as `linear()`."""
+
+    def __init__(self, path):
+        L = lib()
+        L.exl3_checkpoint_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+        L.exl3_checkpoint_close.argtypes = [C.c_void_p]
+        L.exl3_checkpoint_error.argtypes = [C.c_void_p]; L.exl3_checkpoint_error.restype = C.c_char_p
+        L.exl3_checkpoint_count.argtypes = [C.c_void_p]
+        L.exl3_checkpoint_name.argtypes = [C.c_void_p, C.c_int]; L.exl3_checkpoint_name.restype = C.c_char_p
+        L.exl3_checkpoint_has.argtypes = [C.c_void_p, C.c_char_p]
+        L.exl3_checkpoint_info.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p, C.c_int, C.POINTER(C.c_int64), C.c_int,
+                                           C.POINTER(C.c_int), C.POINTER(C.c_uint64)]
+        L.exl3_checkpoint_read.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.exl3_linear_load.argtypes = [C.c_void_p, C.c_void_p, C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_float,
+                                       C.POINTER(LinearLayer)]
+        L.exl3_linear_free.argtypes = [C.POINTER(LinearLayer)]
+        h = C.c_void_p()
+        rc = L.exl3_checkpoint_open(os.fsencode(path), C.byref(h))
+        self._h = h
+        if rc != 0:
+            msg = L.exl3_checkpoint_error(h).decode() if h else "out of memory"
+            self.close()
+            raise Exl3Error(f"checkpoint {path}: {msg} (code {rc})")
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().exl3_checkpoint_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc, what):
+        if rc != 0:
+            raise Exl3Error(f"{what}: {lib().exl3_checkpoint_error(self._h).decode()} (code {rc})")
+
+    def names(self):
+        L = lib()
+        return [L.exl3_checkpoint_name(self._h, i).decode() for i in range(L.exl3_checkpoint_count(self._h))]
+
+    def has(self, name):
+        return bool(lib().exl3_checkpoint_has(self._h, name.encode()))
+
+    def info(self, name):
+        """(dtype string, shape tuple, bytes)"""
+        dt = C.create_string_buffer(16)
+        shape = (C.c_int64 * 8)()
+        nd, nb = C.c_int(), C.c_uint64()
+        self._check(lib().exl3_checkpoint_info(self._h, name.encode(), dt, 16, shape, 8, C.byref(nd), C.byref(nb)), name)
+        return dt.value.decode(), tuple(shape[i] for i in range(nd.value)), nb.value
+
+    def read(self, name, out, stream=None):
+        """the tensor's bytes into the CUDA tensor `out` (same byte size)"""
+        st = C.c_void_p(stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream)
+        self._check(lib().exl3_checkpoint_read(self._h, name.encode(), _ptr(out), out.numel() * out.element_size(), st), name)
+        return out
+
+    def linear(self, key, in_features, out_features, alt_key=None, trim_padded_out=False, softcap=0.0, stream=None):
+        """Linear::load -> LinearLayer (free it with `free_linear`)."""
+        layer = LinearLayer()
+        st = C.c_void_p(stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream)
+        self._check(lib().exl3_linear_load(self._h, st, key.encode(), alt_key.encode() if alt_key else None, in_features,
+                                           out_features, int(trim_padded_out), softcap, C.byref(layer)), key)
+        return layer
+
+    @staticmethod
+    def free_linear(layer):
+        lib().exl3_linear_free(C.byref(layer))
 
 
 class CudaGraph:

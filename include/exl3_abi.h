@@ -314,6 +314,31 @@ typedef struct {
 EXL3_API int exl3_linear_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_linear_layer* layer, const void* x, int in_last,
                                  void* y, int rows);
 
+/* ---- on-disk EXL3 checkpoints (src/safetensors.rs, Linear::load src/modules.rs:97-165)
+ * A safetensors file: 8-byte little-endian header size, a JSON header {name: {dtype, shape, data_offsets}}, the data.
+ * exl3_checkpoint_open parses and validates the header the way the reference does before any field can size a read
+ * (header size 1..100 MiB and inside the file; shapes non-negative integers; offsets ordered and inside the file; span =
+ * product(shape) * element size for the known dtypes).  On failure *out still receives an object whose
+ * exl3_checkpoint_error says why; close it in either case.  Host-only: no device is needed until a tensor is read. */
+typedef struct exl3_checkpoint exl3_checkpoint;
+EXL3_API int  exl3_checkpoint_open(const char* path, exl3_checkpoint** out);
+EXL3_API void exl3_checkpoint_close(exl3_checkpoint* ck);
+EXL3_API const char* exl3_checkpoint_error(const exl3_checkpoint* ck);
+EXL3_API int  exl3_checkpoint_count(const exl3_checkpoint* ck);
+EXL3_API const char* exl3_checkpoint_name(const exl3_checkpoint* ck, int index);      /* header order */
+EXL3_API int  exl3_checkpoint_has(const exl3_checkpoint* ck, const char* name);
+EXL3_API int  exl3_checkpoint_info(const exl3_checkpoint* ck, const char* name, char* dtype, int dtype_cap, int64_t* shape,
+                                   int shape_cap, int* ndim, uint64_t* bytes);
+/* the tensor's bytes as stored, into device memory of at least `capacity` bytes (positional reads through a pinned
+ * staging buffer; returns when the data is on the device) */
+EXL3_API int  exl3_checkpoint_read(exl3_checkpoint* ck, const char* name, void* dst_device, size_t capacity, exl3_stream stream);
+/* Linear::load: fills `out` from <key>.trellis/.suh/.svh (+ .mcg / .mul1 marker tensors, + .bias) or from <key>.weight
+ * [out, in] (+ .bias), trying alt_key (may be NULL) when key has neither; features are padded to multiples of 128 like
+ * the reference pads them.  The layer owns one device allocation; release it with exl3_linear_free. */
+EXL3_API int  exl3_linear_load(exl3_checkpoint* ck, exl3_stream stream, const char* key, const char* alt_key, int in_features,
+                               int out_features, int trim_padded_out, float softcap, exl3_linear_layer* out);
+EXL3_API void exl3_linear_free(exl3_linear_layer* layer);
+
 /* bytes of device scratch exl3_step_forward needs for up to `max_rows` packed rows and `max_bsz` sequences */
 EXL3_API size_t exl3_step_scratch_bytes(const exl3_model* model, int max_rows, int max_bsz);
 
@@ -358,23 +383,37 @@ EXL3_API int exl3_bighead_attn(exl3_ctx* ctx, exl3_stream stream, const void* q,
 /* exl3_shim_gated_rms_norm (src/ffi.rs:118-122).  Not built. */
 EXL3_API int exl3_gated_rms_norm(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* w, void* y, const void* g, float eps,
                                  float constant_bias, int w_groups, int gate_first, int gate_act, int rows, int dim);
-/* exl3_shim_apply_rep_pens / exl3_shim_apply_pres_freq_pens (src/ffi.rs:128-135 -> kernels/generator/rep_pen.cu).  Not built. */
-EXL3_API int exl3_apply_rep_pens(exl3_ctx* ctx, exl3_stream stream, const void* in_logits, void* out_logits, const int64_t* past_ids,
-                                 float rep_p, int sustain_range, int decay_range, int rows, int vocab, int past_len);
-EXL3_API int exl3_apply_pres_freq_pens(exl3_ctx* ctx, exl3_stream stream, const void* in_logits, void* out_logits,
+/* exl3_shim_apply_rep_pens / exl3_shim_apply_pres_freq_pens (src/ffi.rs:128-135 -> kernels/generator/rep_pen.cu:24-245):
+ * penalties over the token history past_ids (int64 [past_len], device) of ONE row of logits (rows must be 1, like the
+ * reference); in_logits fp16 or fp32 [1, vocab], out_logits fp32 [1, vocab].  A history position at distance d from the
+ * end weighs 1 for d <= sustain_range, then falls linearly to 0 over decay_range.  rep_p divides positive logits and
+ * multiplies negative ones, blended by the largest weight of the token; pres_p (largest weight) and freq_p (sum of
+ * weights) are subtracted; both must be >= 0. */
+EXL3_API int exl3_apply_rep_pens(exl3_ctx* ctx, exl3_stream stream, const void* in_logits, int in_fp32, void* out_logits,
+                                 const int64_t* past_ids, float rep_p, int sustain_range, int decay_range, int rows, int vocab,
+                                 int past_len);
+EXL3_API int exl3_apply_pres_freq_pens(exl3_ctx* ctx, exl3_stream stream, const void* in_logits, int in_fp32, void* out_logits,
                                        const int64_t* past_ids, float pres_p, float freq_p, int sustain_range, int decay_range,
                                        int rows, int vocab, int past_len);
-/* exl3_shim_gumbel_sample / exl3_shim_gumbel_noise_f32 (src/ffi.rs:137-138 -> kernels/generator/gumbel.cu).  Not built. */
+/* exl3_shim_gumbel_sample / exl3_shim_gumbel_noise_f32 (src/ffi.rs:137-138 -> kernels/generator/sampling_basic.cu:93-129,
+ * gumbel.cu:47-66): Gumbel noise -log(-log(u)) from the reference's Philox4x32-10 stream (seed `random`), added to fp32
+ * logits element by element (noise), or added and followed by the row argmax over the first max_logit columns (sample;
+ * 0 = all; logits fp16 or fp32 [rows, n], ids int64 [rows]; every row sees the same noise, as in the reference). */
 EXL3_API int exl3_gumbel_sample(exl3_ctx* ctx, exl3_stream stream, const void* logits, int fp32, int64_t* ids, int rows, int n,
                                 int max_logit, uint32_t random);
 EXL3_API int exl3_gumbel_noise_f32(exl3_ctx* ctx, exl3_stream stream, const float* logits_in, float* logits_out, int64_t numel,
                                    uint32_t random);
-/* exl3_shim_cache_rotate (src/ffi.rs:139 -> kernels/generator/cache.cu:11-85): permute pages of a pool.  Not built. */
+/* exl3_shim_cache_rotate (src/ffi.rs:139 -> kernels/generator/cache.cu:11-85): for i in 0..n_order:
+ * (page order[2i] or temp) <- (page order[2i+1] or temp), -1 standing for `temp` (one page of device scratch); order is
+ * a device array of 2 * n_order int32; pages of page_bytes (a multiple of 16) bytes each. */
 EXL3_API int exl3_cache_rotate(exl3_ctx* ctx, exl3_stream stream, void* cache, const int32_t* order, void* temp, int pages,
                                int n_order, size_t page_bytes);
-/* hybrid-architecture ops (src/ffi.rs:163-191 -> kernels/gdn.cu, gdn_chunk.cu, activation.cu).  Not built. */
+/* exl3_shim_mul_sigmoid_ (src/ffi.rs:166 -> kernels/activation.cu:532-568): x *= sigmoid(y) in place, fp16, numel even.
+ * exl3_shim_deinterleave_qg (src/ffi.rs:167 -> kernels/activation.cu:721-784): qg [rows, heads, 2, head_dim] fp16 ->
+ * q, g [rows, heads, head_dim]; head_dim a multiple of 8. */
 EXL3_API int exl3_mul_sigmoid_(exl3_ctx* ctx, exl3_stream stream, void* x, const void* y, int64_t numel);
 EXL3_API int exl3_deinterleave_qg(exl3_ctx* ctx, exl3_stream stream, const void* qg, void* q, void* g, int rows, int heads, int head_dim);
+/* hybrid-architecture ops (src/ffi.rs:163-191 -> kernels/gdn.cu, gdn_chunk.cu).  Not built. */
 EXL3_API int exl3_gdn_fused_op_2(exl3_ctx* ctx, exl3_stream stream, const void* b, const void* a, const void* dt_bias, const void* a_log,
                                  void* beta, void* g, float beta_scale, int bsz, int seq, int heads);
 EXL3_API int exl3_gdn_chunk_wy(exl3_ctx* ctx, exl3_stream stream, const void* k, const void* v, const void* beta, const void* a_log,

@@ -234,6 +234,111 @@ def linear_forward(x, K, cb, k, n, trellis=None, suh=None, svh=None, dense=None,
     return y
 
 
+def _history_weights(past_len, sustain, decay):
+    """weight of history position i (distance past_len - i from the end): kernels/generator/rep_pen.cu:48-69"""
+    dist = (past_len - np.arange(past_len)).astype(np.float32)
+    if decay > 0:
+        f = np.float32(1.0) - (dist - np.float32(sustain)) / np.float32(decay)
+    else:
+        f = np.ones(past_len, np.float32)
+    f = np.clip(f, 0.0, 1.0).astype(np.float32)
+    f[dist <= sustain] = 1.0
+    f[np.arange(past_len) <= past_len - sustain - decay] = 0.0
+    return f
+
+
+def apply_rep_pens(logits, past_ids, rep_p, sustain, decay):
+    """kernels/generator/rep_pen.cu:24-91: logits [1, vocab] fp16|fp32 -> fp32"""
+    v = np.asarray(logits, np.float32).reshape(-1).copy()
+    past = np.asarray(past_ids, np.int64).reshape(-1)
+    f = np.zeros(v.size, np.float32)
+    np.maximum.at(f, past, _history_weights(past.size, sustain, decay))
+    w = np.where(v > 0, v / np.float32(rep_p), v * np.float32(rep_p)).astype(np.float32)
+    f = f + np.float32(1e-30)
+    f1 = (np.float32(1.0) - f) + np.float32(1e-30)
+    return (v * f1 + w * f).astype(np.float32).reshape(1, -1)
+
+
+def apply_pres_freq_pens(logits, past_ids, pres_p, freq_p, sustain, decay):
+    """kernels/generator/rep_pen.cu:135-210"""
+    v = np.asarray(logits, np.float32).reshape(-1).copy()
+    past = np.asarray(past_ids, np.int64).reshape(-1)
+    wts = _history_weights(past.size, sustain, decay)
+    freq = np.zeros(v.size, np.float32)
+    pres = np.zeros(v.size, np.float32)
+    np.add.at(freq, past, wts * np.float32(freq_p))
+    np.maximum.at(pres, past, wts * np.float32(pres_p))
+    return ((v - freq) - pres).astype(np.float32).reshape(1, -1)
+
+
+def philox_uniform(seed, subsequence, draw):
+    """Philox4x32-10 (Salmon et al., SC'11) consumed the way kernels/generator/gumbel.cu:47-66 does through its random
+    number library: key (seed, 0), counter (draw // 4, 0, subsequence, 0), word draw % 4, uniform = w * 2^-32 + 2^-33."""
+    sub = np.asarray(subsequence, np.uint64)
+    draw = np.broadcast_to(np.asarray(draw, np.uint64), sub.shape)
+    c = [draw >> np.uint64(2), np.zeros_like(sub), sub.copy(), np.zeros_like(sub)]
+    k0, k1 = np.uint64(seed & 0xFFFFFFFF), np.uint64(0)
+    M0, M1, mask = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57), np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0, p1 = M0 * c[0], M1 * c[2]
+        c = [((p1 >> np.uint64(32)) ^ c[1] ^ k0) & mask, p1 & mask, ((p0 >> np.uint64(32)) ^ c[3] ^ k1) & mask, p0 & mask]
+        k0, k1 = (k0 + np.uint64(0x9E3779B9)) & mask, (k1 + np.uint64(0xBB67AE85)) & mask
+    words = np.stack(c, 0)
+    w = np.take_along_axis(words, (draw & np.uint64(3)).astype(np.int64)[None], 0)[0]
+    return (w.astype(np.float32) * np.float32(2.3283064e-10) + np.float32(1.1641532e-10)).astype(np.float32)
+
+
+def gumbel_of(u):
+    u = np.minimum(u, np.float32(0.99999994))
+    inner = np.maximum(-np.log(np.maximum(u, np.float32(1e-20)).astype(np.float64)), 1e-20)
+    return (-np.log(inner)).astype(np.float32)
+
+
+def gumbel_noise_f32(logits, seed):
+    """kernels/generator/gumbel.cu:47-66: element i takes the first draw of subsequence i"""
+    x = np.asarray(logits, np.float32)
+    idx = np.arange(x.size, dtype=np.uint64)
+    return (x.reshape(-1) + gumbel_of(philox_uniform(seed, idx, 0))).astype(np.float32).reshape(x.shape)
+
+
+def gumbel_sample_noisy(logits, seed, max_logit=0):
+    """kernels/generator/sampling_basic.cu:93-129: the noisy logits whose row argmax is the sample.  Column c takes draw
+    2 (c // 2048) + (c & 1) of subsequence (c // 2) % 1024; every row sees the same noise."""
+    x = np.asarray(logits).astype(np.float32)
+    n = x.shape[1]
+    lim = n if max_logit == 0 or max_logit > n else max_logit
+    end = min(n, lim + 1)
+    c = np.arange(end, dtype=np.uint64)
+    g = gumbel_of(philox_uniform(seed, (c >> np.uint64(1)) & np.uint64(1023), np.uint64(2) * (c >> np.uint64(11)) + (c & np.uint64(1))))
+    out = x[:, :end] + g[None, :]
+    # the reference admits columns pair by pair (sampling_basic.cu:38-62): (c, c + 1), c even: first if c < lim - 1, second if c < lim
+    ci = np.arange(end)
+    bad = np.where(ci % 2 == 1, ci - 1 >= lim, ci >= lim - 1)
+    out[:, bad] = -np.inf
+    return out
+
+
+def cache_rotate(cache, order, temp):
+    """kernels/generator/cache.cu:11-85 on numpy pages, in place"""
+    order = np.asarray(order, np.int32).reshape(-1, 2)
+    for a, b in order:
+        src = cache[b].copy() if b >= 0 else temp.copy()
+        if a >= 0:
+            cache[a] = src
+        else:
+            temp[...] = src
+    return cache
+
+
+def mul_sigmoid(x, y):
+    """x * sigmoid(y) with every step rounded to fp16 (kernels/activation_kernels.cuh:132-139,300-315)"""
+    x, y = _c(x, np.float16), _c(y, np.float16)
+    e = np.exp(-y.astype(np.float64)).astype(np.float16)
+    s = (np.float16(1.0) + e).astype(np.float16)
+    r = (1.0 / s.astype(np.float64)).astype(np.float16)
+    return (x * r).astype(np.float16)
+
+
 def add(x, y):
     x = _c(x, np.float16)
     y = _c(y, np.float16)

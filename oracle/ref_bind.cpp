@@ -25,6 +25,8 @@
 #include "quant/reconstruct.cuh"
 #include "generator/cache.cuh"
 #include "generator/sampling_basic.cuh"
+#include "generator/rep_pen.cuh"
+#include "generator/gumbel.cuh"
 #include "cache/q_cache.cuh"
 
 extern "C" void exl3_set_mma_attn(int on);
@@ -233,6 +235,62 @@ int ref_softcap(const void* x, void* y, float factor, int64_t rows, int64_t cols
 {
     return guarded([&] {
         softcap(wrap(x, {rows, cols}, fp32 ? at::kFloat : at::kHalf), wrap(y, {rows, cols}, fp32 ? at::kFloat : at::kHalf), factor);
+    });
+}
+
+int ref_apply_rep_pens(const void* in, int in_fp32, void* out, const void* past, float rep_p, int sustain, int decay, int vocab, int past_len)
+{
+    return guarded([&] {
+        apply_rep_pens(wrap(in, {1, vocab}, in_fp32 ? at::kFloat : at::kHalf), wrap(out, {1, vocab}, at::kFloat),
+                       wrap(past, {1, past_len}, at::kLong), rep_p, sustain, decay);
+    });
+}
+
+int ref_apply_pres_freq_pens(const void* in, int in_fp32, void* out, const void* past, float pres_p, float freq_p, int sustain,
+                             int decay, int vocab, int past_len)
+{
+    return guarded([&] {
+        apply_pres_freq_pens(wrap(in, {1, vocab}, in_fp32 ? at::kFloat : at::kHalf), wrap(out, {1, vocab}, at::kFloat),
+                             wrap(past, {1, past_len}, at::kLong), pres_p, freq_p, sustain, decay);
+    });
+}
+
+int ref_gumbel_noise_f32(const void* in, void* out, int64_t numel, uint32_t random)
+{
+    return guarded([&] {
+        auto to = wrap(out, {numel}, at::kFloat);
+        gumbel_noise_f32(wrap(in, {numel}, at::kFloat), to, random);
+    });
+}
+
+int ref_gumbel_sample(const void* logits, void* ids, int rows, int n, int max_logit, uint32_t random)
+{
+    return guarded([&] {
+        auto ti = wrap(ids, {rows, 1}, at::kLong);
+        gumbel_sample(wrap(logits, {rows, n}, at::kHalf), ti, max_logit, random);
+    });
+}
+
+int ref_cache_rotate(void* cache, const void* order, void* temp, int pages, int n_order, int64_t page_bytes)
+{
+    return guarded([&] {
+        cache_rotate(wrap(cache, {pages, page_bytes}, at::kByte), wrap(order, {2 * n_order}, at::kInt), wrap(temp, {page_bytes}, at::kByte));
+    });
+}
+
+int ref_mul_sigmoid_(void* x, const void* y, int64_t numel)
+{
+    return guarded([&] {
+        auto tx = wrap(x, {numel}, at::kHalf);
+        mul_sigmoid_(tx, wrap(y, {numel}, at::kHalf));
+    });
+}
+
+int ref_deinterleave_qg(const void* qg, void* q, void* g, int rows, int heads, int head_dim)
+{
+    return guarded([&] {
+        auto tq = wrap(q, {rows, heads * head_dim}, at::kHalf), tg = wrap(g, {rows, heads * head_dim}, at::kHalf);
+        deinterleave_qg(wrap(qg, {rows, heads * 2 * head_dim}, at::kHalf), tq, tg, head_dim);
     });
 }
 

@@ -84,3 +84,33 @@ def gemm_mismatch(got, want, tol, fp16_out, steps=1):
     if fp16_out:
         allowed = np.maximum(allowed, fp16_ulp(want) * (steps + 0.001))
     return float((np.abs(got - want) / allowed).max())
+
+
+_ST_DTYPES = {"float16": "F16", "float32": "F32", "int16": "I16", "int32": "I32", "int64": "I64", "uint8": "U8", "int8": "I8"}
+
+
+def write_safetensors(path, tensors, metadata=None, raw_header=None):
+    """A safetensors file from {name: numpy array} (bf16 as ("BF16", uint16 array)); `raw_header` replaces the JSON text
+    (for malformed-header tests) while the data section is still written."""
+    import json
+    import struct
+    header, blobs, off = {}, [], 0
+    if metadata:
+        header["__metadata__"] = metadata
+    for name, a in tensors.items():
+        dt = None
+        if isinstance(a, tuple):
+            dt, a = a
+        a = np.ascontiguousarray(a)
+        b = a.tobytes()
+        header[name] = {"dtype": dt or _ST_DTYPES[a.dtype.name], "shape": list(a.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    text = (raw_header if raw_header is not None else json.dumps(header, separators=(",", ":"))).encode()
+    text += b" " * (-len(text) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(text)))
+        f.write(text)
+        for b in blobs:
+            f.write(b)
+    return header

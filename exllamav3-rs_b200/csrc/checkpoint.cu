@@ -309,9 +309,14 @@ extern "C" int exl3_checkpoint_read(exl3_checkpoint* ck, const char* name, void*
 // as in the reference's port); the presence of <k>.mcg / <k>.mul1 selects the codebook; <k>.bias is optional.  A dense
 // layer is <k>.weight [out, in] (F16, BF16 or F32), stored transposed and zero-padded as fp16 [in_pad, out_pad].  All
 // device memory of the layer is one allocation owned by it (exl3_linear_free).
-extern "C" int exl3_linear_load(exl3_checkpoint* ck, exl3_stream stream, const char* key, const char* alt_key, int in_features,
-                                int out_features, int trim_padded_out, float softcap, exl3_linear_layer* out)
+namespace {
+
+// `find(name)` returns the opened file that holds tensor `name`, or NULL; errors are reported into `rep`'s buffer
+template <typename Find>
+int linear_load_impl(Find find, exl3_checkpoint* rep, exl3_stream stream, const char* key, const char* alt_key, int in_features,
+                     int out_features, int trim_padded_out, float softcap, exl3_linear_layer* out)
 {
+    exl3_checkpoint* ck = rep;
     if (!ck || !key || !out || in_features <= 0 || out_features <= 0) return EXL3_ERR_INVALID;
     memset(out, 0, sizeof(*out));
     const int inf = (in_features + 127) / 128 * 128, outf = (out_features + 127) / 128 * 128;
@@ -320,34 +325,41 @@ extern "C" int exl3_linear_load(exl3_checkpoint* ck, exl3_stream stream, const c
     for (const char* k : keys) {
         if (!k) continue;
         const std::string base(k);
-        auto has = [&](const char* suf) { return ck->entries.count(base + suf) != 0; };
-        auto bytes_of = [&](const char* suf) { const Entry& e = ck->entries.at(base + suf); return (size_t)(e.end - e.begin); };
+        auto has = [&](const char* suf) { return find(base + suf) != nullptr; };
+        auto entry = [&](const char* suf) -> const Entry& { return find(base + suf)->entries.at(base + suf); };
+        auto bytes_of = [&](const char* suf) { const Entry& e = entry(suf); return (size_t)(e.end - e.begin); };
+        auto read = [&](const char* suf, void* dst, size_t cap) {
+            exl3_checkpoint* src = find(base + suf);
+            const int rc = exl3_checkpoint_read(src, (base + suf).c_str(), dst, cap, stream);
+            if (rc && src != ck) ck_fail(ck, rc, src->err);
+            return rc;
+        };
         auto align = [](size_t x) { return (x + 255) & ~(size_t)255; };
         if (has(".trellis")) {
-            const Entry& tr = ck->entries.at(base + ".trellis");
+            const Entry& tr = entry(".trellis");
             if (tr.dtype != "I16" || tr.shape.size() != 3 || tr.shape[2] % 16 != 0 || tr.shape[2] < 16 || tr.shape[2] > 128)
                 return ck_fail(ck, EXL3_ERR_INVALID, base + ".trellis: expected I16 [k/16, n/16, 16 K]");
             if (tr.shape[0] * 16 != inf || tr.shape[1] * 16 != outf)
                 return ck_fail(ck, EXL3_ERR_INVALID, base + ".trellis does not match the padded features");
             if (!has(".suh")) return ck_fail(ck, EXL3_ERR_UNSUPPORTED, base + ": only unpacked suh/svh supported");
             if (!has(".svh")) return ck_fail(ck, EXL3_ERR_INVALID, base + ".svh missing");
-            const Entry& su = ck->entries.at(base + ".suh"); const Entry& sv = ck->entries.at(base + ".svh");
+            const Entry& su = entry(".suh"); const Entry& sv = entry(".svh");
             if (su.dtype != "F16" || sv.dtype != "F16" || bytes_of(".suh") != (size_t)inf * 2 || bytes_of(".svh") != (size_t)outf * 2)
                 return ck_fail(ck, EXL3_ERR_INVALID, base + ": suh/svh must be F16 of the padded sizes");
             if (has(".mcg") && has(".mul1")) return ck_fail(ck, EXL3_ERR_INVALID, base + ": both mcg and mul1");
             const bool bias = has(".bias");
-            if (bias && (ck->entries.at(base + ".bias").dtype != "F16" || bytes_of(".bias") > (size_t)outf * 2))
+            if (bias && (entry(".bias").dtype != "F16" || bytes_of(".bias") > (size_t)outf * 2))
                 return ck_fail(ck, EXL3_ERR_INVALID, base + ".bias: expected F16 of at most the padded width");
             const size_t o_tr = 0, o_su = align(bytes_of(".trellis")), o_sv = o_su + align((size_t)inf * 2), o_b = o_sv + align((size_t)outf * 2);
             const size_t total = o_b + (bias ? align((size_t)outf * 2) : 0);
             uint8_t* mem = nullptr;
             if (cudaMalloc(&mem, total) != cudaSuccess) { cudaGetLastError(); return ck_fail(ck, EXL3_ERR_NOMEM, "device memory for " + base); }
-            int rc = exl3_checkpoint_read(ck, (base + ".trellis").c_str(), mem + o_tr, bytes_of(".trellis"), stream);
-            if (!rc) rc = exl3_checkpoint_read(ck, (base + ".suh").c_str(), mem + o_su, (size_t)inf * 2, stream);
-            if (!rc) rc = exl3_checkpoint_read(ck, (base + ".svh").c_str(), mem + o_sv, (size_t)outf * 2, stream);
+            int rc = read(".trellis", mem + o_tr, bytes_of(".trellis"));
+            if (!rc) rc = read(".suh", mem + o_su, (size_t)inf * 2);
+            if (!rc) rc = read(".svh", mem + o_sv, (size_t)outf * 2);
             if (!rc && bias) {
                 if (cudaMemsetAsync(mem + o_b, 0, (size_t)outf * 2, st) != cudaSuccess) rc = EXL3_ERR_CUDA;
-                if (!rc) rc = exl3_checkpoint_read(ck, (base + ".bias").c_str(), mem + o_b, (size_t)outf * 2, stream);
+                if (!rc) rc = read(".bias", mem + o_b, (size_t)outf * 2);
             }
             if (rc) { cudaFree(mem); return rc; }
             out->w.trellis = mem + o_tr; out->w.suh = mem + o_su; out->w.svh = mem + o_sv;
@@ -359,20 +371,20 @@ extern "C" int exl3_linear_load(exl3_checkpoint* ck, exl3_stream stream, const c
             return EXL3_OK;
         }
         if (has(".weight")) {
-            const Entry& w = ck->entries.at(base + ".weight");
+            const Entry& w = entry(".weight");
             const int es = dtype_size(w.dtype);
             if (w.shape.size() != 2 || !(w.dtype == "F16" || w.dtype == "BF16" || w.dtype == "F32") || w.shape[0] > outf || w.shape[1] > inf)
                 return ck_fail(ck, EXL3_ERR_INVALID, base + ".weight: expected a float matrix [out, in] within the padded sizes");
             const int wo = (int)w.shape[0], wi = (int)w.shape[1];
             const bool bias = has(".bias");
-            const Entry* be = bias ? &ck->entries.at(base + ".bias") : nullptr;
+            const Entry* be = bias ? &entry(".bias") : nullptr;
             if (bias && (!(be->dtype == "F16" || be->dtype == "BF16" || be->dtype == "F32") || be->shape.size() != 1 || be->shape[0] > outf))
                 return ck_fail(ck, EXL3_ERR_INVALID, base + ".bias: expected a float vector of at most the padded width");
             const size_t o_w = 0, o_b = align((size_t)inf * outf * 2), o_raw = o_b + align((size_t)outf * 2);
             const size_t raw_bytes = std::max(bytes_of(".weight"), bias ? bytes_of(".bias") : (size_t)0);
             uint8_t* mem = nullptr;
             if (cudaMalloc(&mem, o_raw + align(raw_bytes)) != cudaSuccess) { cudaGetLastError(); return ck_fail(ck, EXL3_ERR_NOMEM, "device memory for " + base); }
-            int rc = exl3_checkpoint_read(ck, (base + ".weight").c_str(), mem + o_raw, raw_bytes, stream);
+            int rc = read(".weight", mem + o_raw, raw_bytes);
             if (!rc) {
                 const dim3 grid((outf + 31) / 32, (inf + 31) / 32);
                 if (es == 4) transpose_pad_kernel<float><<<grid, 256, 0, st>>>((const float*)(mem + o_raw), (half*)(mem + o_w), wo, wi, inf, outf);
@@ -381,7 +393,7 @@ extern "C" int exl3_linear_load(exl3_checkpoint* ck, exl3_stream stream, const c
                 if (cudaStreamSynchronize(st) != cudaSuccess) rc = EXL3_ERR_CUDA;
             }
             if (!rc && bias) {
-                rc = exl3_checkpoint_read(ck, (base + ".bias").c_str(), mem + o_raw, raw_bytes, stream);
+                rc = read(".bias", mem + o_raw, raw_bytes);
                 if (!rc) {
                     const int nb = (int)be->shape[0];
                     if (be->dtype == "F32") to_half_pad_kernel<float><<<(outf + 255) / 256, 256, 0, st>>>((const float*)(mem + o_raw), (half*)(mem + o_b), nb, outf);
@@ -401,6 +413,16 @@ extern "C" int exl3_linear_load(exl3_checkpoint* ck, exl3_stream stream, const c
     return ck_fail(ck, EXL3_ERR_INVALID, std::string("No supported quant tensors for ") + key);
 }
 
+}  // namespace
+
+extern "C" int exl3_linear_load(exl3_checkpoint* ck, exl3_stream stream, const char* key, const char* alt_key, int in_features,
+                                int out_features, int trim_padded_out, float softcap, exl3_linear_layer* out)
+{
+    if (!ck) return EXL3_ERR_INVALID;
+    auto find = [ck](const std::string& name) -> exl3_checkpoint* { return ck->entries.count(name) ? ck : nullptr; };
+    return linear_load_impl(find, ck, stream, key, alt_key, in_features, out_features, trim_padded_out, softcap, out);
+}
+
 extern "C" void exl3_linear_free(exl3_linear_layer* layer)
 {
     if (!layer) return;
@@ -409,3 +431,158 @@ extern "C" void exl3_linear_free(exl3_linear_layer* layer)
     if (base) cudaFree(base);
     memset(layer, 0, sizeof(*layer));
 }
+
+// ---------------------------------------------------------------------------------------------- whole dense model
+// Model::load for the dense transformer family of the step runner (src/model.rs:262-420, src/modules.rs:470-490,985-1000):
+// <pfx>.embed_tokens.weight, <pfx>.layers.<i>.{input_layernorm, post_attention_layernorm}.weight,
+// .self_attn.{q,k,v,o}_proj, .self_attn.{q,k}_norm.weight (optional), .mlp.{gate,up,down}_proj, <pfx>.norm.weight, lm_head.
+// Projections must be EXL3 tensors (the step runner has no dense projection path); vectors and the embedding table may
+// be F16, BF16 or F32 and are kept as fp16.  Tensors may be spread over several files.
+struct exl3_loaded_model {
+    exl3_model model;
+    std::vector<exl3_layer> layers;
+    std::vector<exl3_linear_layer> linears;      // owners of the projections' device memory
+    std::vector<void*> buffers;                  // norms, embedding, rotary frequencies
+    char err[256] = {0};
+};
+
+namespace {
+
+struct Shards {
+    exl3_checkpoint* const* ck; int n;
+    exl3_checkpoint* find(const std::string& name) const
+    {
+        for (int i = 0; i < n; ++i) if (ck[i] && ck[i]->entries.count(name)) return ck[i];
+        return nullptr;
+    }
+};
+
+int lm_fail(exl3_loaded_model* m, int code, const std::string& msg)
+{
+    strncpy(m->err, msg.c_str(), sizeof(m->err) - 1); m->err[sizeof(m->err) - 1] = 0;
+    return code;
+}
+
+// a float tensor of exactly `numel` elements as fp16 on the device
+int load_half(exl3_loaded_model* m, const Shards& sh, cudaStream_t st, const std::string& name, size_t numel, void** out)
+{
+    exl3_checkpoint* ck = sh.find(name);
+    if (!ck) return lm_fail(m, EXL3_ERR_INVALID, "missing tensor " + name);
+    const Entry& e = ck->entries.at(name);
+    const int es = dtype_size(e.dtype);
+    if (!(e.dtype == "F16" || e.dtype == "BF16" || e.dtype == "F32") || (size_t)(e.end - e.begin) != numel * es)
+        return lm_fail(m, EXL3_ERR_INVALID, name + ": expected " + std::to_string(numel) + " float elements");
+    uint8_t* dst = nullptr;
+    const size_t half_bytes = (numel * 2 + 255) & ~(size_t)255;
+    if (cudaMalloc(&dst, half_bytes + (e.dtype == "F16" ? 0 : numel * es)) != cudaSuccess) { cudaGetLastError(); return lm_fail(m, EXL3_ERR_NOMEM, "device memory for " + name); }
+    m->buffers.push_back(dst);
+    int rc = exl3_checkpoint_read(ck, name.c_str(), e.dtype == "F16" ? dst : dst + half_bytes, numel * es, (exl3_stream)st);
+    if (rc) return lm_fail(m, rc, ck->err);
+    if (e.dtype != "F16") {
+        if (numel > 0x7fffffffull) return lm_fail(m, EXL3_ERR_UNSUPPORTED, name + ": too large to convert");
+        const unsigned grid = (unsigned)((numel + 255) / 256);
+        if (e.dtype == "F32") to_half_pad_kernel<float><<<grid, 256, 0, st>>>((const float*)(dst + half_bytes), (half*)dst, (int)numel, (int)numel);
+        else to_half_pad_kernel<uint16_t><<<grid, 256, 0, st>>>((const uint16_t*)(dst + half_bytes), (half*)dst, (int)numel, (int)numel);
+        if (cudaStreamSynchronize(st) != cudaSuccess) { cudaGetLastError(); return lm_fail(m, EXL3_ERR_CUDA, "conversion of " + name + " failed"); }
+    }
+    *out = dst;
+    return EXL3_OK;
+}
+
+int load_proj(exl3_loaded_model* m, const Shards& sh, cudaStream_t st, const std::string& key, int in_f, int out_f, exl3_linear* out)
+{
+    exl3_checkpoint* ck = sh.find(key + ".trellis");
+    if (!ck) return lm_fail(m, sh.find(key + ".weight") ? EXL3_ERR_UNSUPPORTED : EXL3_ERR_INVALID,
+                            key + ": the step runner needs an EXL3 tensor here");
+    if (in_f % 128 || out_f % 128) return lm_fail(m, EXL3_ERR_UNSUPPORTED, key + ": features must be multiples of 128");
+    exl3_linear_layer L;
+    auto find = [&sh](const std::string& name) { return sh.find(name); };
+    const int rc = linear_load_impl(find, ck, (exl3_stream)st, key.c_str(), nullptr, in_f, out_f, 0, 0.0f, &L);
+    if (rc) return lm_fail(m, rc, ck->err);
+    m->linears.push_back(L);
+    if (L.bias) return lm_fail(m, EXL3_ERR_UNSUPPORTED, key + ": projections with a bias are not supported by the step runner");
+    *out = L.w;
+    return EXL3_OK;
+}
+
+}  // namespace
+
+extern "C" int exl3_model_load(exl3_checkpoint* const* shards, int n_shards, exl3_stream stream, const char* prefix, int n_layers,
+                               int hidden, int nq, int nkv, int hd, int inter, int vocab, float norm_eps, float rope_theta,
+                               const exl3_pool* pool, exl3_loaded_model** out)
+{
+    if (!shards || n_shards <= 0 || !prefix || !pool || !out) return EXL3_ERR_INVALID;
+    if (n_layers <= 0 || hidden <= 0 || nq <= 0 || nkv <= 0 || hd <= 0 || hd % 2 || inter <= 0 || vocab <= 0 || rope_theta <= 0.0f)
+        return EXL3_ERR_INVALID;
+    exl3_loaded_model* m = new (std::nothrow) exl3_loaded_model;
+    if (!m) return EXL3_ERR_NOMEM;
+    *out = m;                                        // kept on failure for exl3_model_error; free it in either case
+    memset(&m->model, 0, sizeof(m->model));
+    const Shards sh{shards, n_shards};
+    cudaStream_t st = (cudaStream_t)stream;
+    const std::string pfx(prefix);
+    int k_bits = 0, v_bits = 0;
+    exl3_pool_kv_bits(pool, &k_bits, &v_bits);
+    if (k_bits != v_bits) return lm_fail(m, EXL3_ERR_UNSUPPORTED, "the step runner needs equal K and V code widths");
+    m->layers.resize(n_layers);
+    m->linears.reserve((size_t)n_layers * 7 + 1);
+    int rc;
+    void* p = nullptr;
+    if ((rc = load_half(m, sh, st, pfx + ".embed_tokens.weight", (size_t)vocab * hidden, &p))) return rc;
+    m->model.embed = p;
+    for (int i = 0; i < n_layers; ++i) {
+        const std::string key = pfx + ".layers." + std::to_string(i);
+        exl3_layer& L = m->layers[i];
+        memset(&L, 0, sizeof(L));
+        if ((rc = load_half(m, sh, st, key + ".input_layernorm.weight", hidden, &p))) return rc;
+        L.attn_norm = p;
+        if ((rc = load_half(m, sh, st, key + ".post_attention_layernorm.weight", hidden, &p))) return rc;
+        L.mlp_norm = p;
+        if (sh.find(key + ".self_attn.q_norm.weight")) {
+            if ((rc = load_half(m, sh, st, key + ".self_attn.q_norm.weight", hd, &p))) return rc;
+            L.q_norm = p;
+            if ((rc = load_half(m, sh, st, key + ".self_attn.k_norm.weight", hd, &p))) return rc;
+            L.k_norm = p;
+        }
+        if ((rc = load_proj(m, sh, st, key + ".self_attn.q_proj", hidden, nq * hd, &L.q_proj))) return rc;
+        if ((rc = load_proj(m, sh, st, key + ".self_attn.k_proj", hidden, nkv * hd, &L.k_proj))) return rc;
+        if ((rc = load_proj(m, sh, st, key + ".self_attn.v_proj", hidden, nkv * hd, &L.v_proj))) return rc;
+        if ((rc = load_proj(m, sh, st, key + ".self_attn.o_proj", nq * hd, hidden, &L.o_proj))) return rc;
+        if ((rc = load_proj(m, sh, st, key + ".mlp.gate_proj", hidden, inter, &L.gate_proj))) return rc;
+        if ((rc = load_proj(m, sh, st, key + ".mlp.up_proj", hidden, inter, &L.up_proj))) return rc;
+        if ((rc = load_proj(m, sh, st, key + ".mlp.down_proj", inter, hidden, &L.down_proj))) return rc;
+        void *k = nullptr, *v = nullptr, *sk = nullptr, *sv = nullptr;
+        if (exl3_pool_layer(pool, i, &k, &v, &sk, &sv) != EXL3_OK) return lm_fail(m, EXL3_ERR_INVALID, "the pool has fewer layers than the model");
+        if (k_bits == 0) { L.k_cache = k; L.v_cache = v; }
+        else { L.qk = k; L.qv = v; L.sk = sk; L.sv = sv; }
+    }
+    if ((rc = load_half(m, sh, st, pfx + ".norm.weight", hidden, &p))) return rc;
+    m->model.final_norm = p;
+    if ((rc = load_proj(m, sh, st, "lm_head", hidden, vocab, &m->model.lm_head))) return rc;
+    // rotary frequencies theta^(-2i/hd), i < hd/2 (src/rope.rs:82-86)
+    std::vector<float> inv(hd / 2);
+    for (int i = 0; i < hd / 2; ++i) inv[i] = 1.0f / powf(rope_theta, (float)(2 * i) / (float)hd);
+    float* dinv = nullptr;
+    if (cudaMalloc(&dinv, inv.size() * 4) != cudaSuccess) { cudaGetLastError(); return lm_fail(m, EXL3_ERR_NOMEM, "device memory for the rotary table"); }
+    m->buffers.push_back(dinv);
+    if (cudaMemcpyAsync(dinv, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess) {
+        cudaGetLastError();
+        return lm_fail(m, EXL3_ERR_CUDA, "copy of the rotary table failed");
+    }
+    exl3_model& M = m->model;
+    M.n_layers = n_layers; M.hidden = hidden; M.nq = nq; M.nkv = nkv; M.hd = hd; M.inter = inter; M.vocab = vocab;
+    M.kv_bits = k_bits; M.pages = exl3_pool_num_pages(pool); M.norm_eps = norm_eps; M.attn_factor = 1.0f;
+    M.rope_mode = EXL3_ROPE_NEOX; M.n_freq = hd / 2; M.inv_freq = dinv; M.layers = m->layers.data();
+    return EXL3_OK;
+}
+
+extern "C" const exl3_model* exl3_model_get(const exl3_loaded_model* m) { return m ? &m->model : nullptr; }
+extern "C" const char* exl3_model_error(const exl3_loaded_model* m) { return m ? m->err : "null model"; }
+extern "C" void exl3_model_free(exl3_loaded_model* m)
+{
+    if (!m) return;
+    for (auto& L : m->linears) exl3_linear_free(&L);
+    for (void* b : m->buffers) cudaFree(b);
+    delete m;
+}
+

@@ -132,6 +132,11 @@ extern "C" int exl3_pool_layer(const exl3_pool* p, int layer, void** k, void** v
 }
 
 extern "C" int exl3_pool_num_pages(const exl3_pool* p) { return p ? p->pages : 0; }
+extern "C" void exl3_pool_kv_bits(const exl3_pool* p, int* k_bits, int* v_bits)
+{
+    if (k_bits) *k_bits = p ? p->k_bits : 0;
+    if (v_bits) *v_bits = p ? p->v_bits : 0;
+}
 extern "C" int exl3_pool_num_free(const exl3_pool* p) { return p ? p->num_free() : 0; }
 extern "C" int exl3_pool_refcount(const exl3_pool* p, int page) { return (p && page >= 0 && page < p->pages) ? (int)p->rc[page] : -1; }
 extern "C" void exl3_pool_set_dedup(exl3_pool* p, int on) { if (p) p->dedup = on ? 1 : 0; }

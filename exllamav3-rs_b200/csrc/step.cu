@@ -65,7 +65,7 @@ struct Scratch {
     float* logits;
 };
 
-size_t carve(const exl3_model* m, int max_rows, int max_bsz, uint8_t* base, Scratch* s)
+size_t carve(const exl3_model* m, int max_rows, int max_bsz, int head_rows, uint8_t* base, Scratch* s)
 {
     size_t off = 0;
     auto take = [&](size_t bytes) -> void* {
@@ -92,7 +92,7 @@ size_t carve(const exl3_model* m, int max_rows, int max_bsz, uint8_t* base, Scra
     t.act = (half*)take(R * m->inter * 2);
     t.pend_last = (half*)take(B * m->hidden * 2);
     t.y_last = (half*)take(B * m->hidden * 2);
-    t.logits = (float*)take(B * (size_t)m->vocab * 4);
+    t.logits = (float*)take((size_t)head_rows * (size_t)m->vocab * 4);
     if (s) *s = t;
     return (off + 255) & ~(size_t)255;
 }
@@ -104,10 +104,10 @@ int linear(exl3_ctx* ctx, exl3_stream st, const exl3_linear& w, const void* x, v
 
 }  // namespace
 
-extern "C" size_t exl3_step_scratch_bytes(const exl3_model* model, int max_rows, int max_bsz)
+extern "C" size_t exl3_step_scratch_bytes(const exl3_model* model, int max_rows, int max_bsz, int all_rows)
 {
     if (!model || max_rows <= 0 || max_bsz <= 0) return 0;
-    return carve(model, max_rows, max_bsz, nullptr, nullptr);
+    return carve(model, max_rows, max_bsz, all_rows ? max_rows : max_bsz, nullptr, nullptr);
 }
 
 extern "C" int exl3_step_build_descriptors(exl3_ctx* ctx, exl3_stream stream, const int32_t* q_lens,
@@ -133,7 +133,7 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
     EXL3_REQUIRE(aligned16(scratch), "step_forward: scratch must be 16-byte aligned");
     EXL3_REQUIRE(m->kv_bits == 0 || (m->kv_bits >= 2 && m->kv_bits <= 8), "step_forward: kv_bits must be 0 or 2..8");
     Scratch s;
-    const size_t need = carve(m, b->rows, b->bsz, (uint8_t*)scratch, &s);
+    const size_t need = carve(m, b->rows, b->bsz, b->all_rows ? b->rows : b->bsz, (uint8_t*)scratch, &s);
     // attention work lists are built by the first layer and kept for the others; the flag drops on every way out
     struct PlanKeep {
         exl3_ctx* c;
@@ -180,6 +180,20 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
         pending = s.proj;
     }
 
+    if (b->all_rows) {
+        // head over every packed row (the speculative verify round reads the argmax after each draft token,
+        // src/generator.rs:1649-1790): final norm into the free activation buffer, lm_head, argmax per row
+        STEP_TRY(exl3_rms_norm_res_in(ctx, stream, pending, 0, m->final_norm, s.a_in, 0, s.resid, m->norm_eps, 0.f, 1.f, rows, hidden));
+        float* lga = logits ? logits : s.logits;
+        STEP_TRY(linear(ctx, stream, m->lm_head, s.a_in, lga, rows, 1));
+        STEP_TRY(exl3_argmax_sample(ctx, stream, lga, 1, out_tokens, rows, m->vocab, 0));
+        if (b->advance) {
+            advance_kernel<<<(bsz + 255) / 256, 256, 0, st>>>(b->cache_seqlens, b->q_lens, bsz);
+            ctx->launches++;
+            STEP_TRY(exl3_check_launch(ctx, "step advance"));
+        }
+        return EXL3_OK;
+    }
     // head: only the last row of every sequence (src/model.rs:1038-1050 last_only), logits in fp32
     {
         const long long it = (long long)bsz * (hidden * 4 / 16);

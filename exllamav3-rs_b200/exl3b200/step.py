@@ -26,7 +26,7 @@ class Model(C.Structure):
 class Batch(C.Structure):
     _fields_ = [("ids", C.c_void_p), ("q_lens", C.c_void_p), ("cache_seqlens", C.c_void_p), ("block_table", C.c_void_p),
                 ("bsz", C.c_int), ("rows", C.c_int), ("max_q_len", C.c_int), ("pages_per_seq", C.c_int),
-                ("advance", C.c_int)]
+                ("advance", C.c_int), ("all_rows", C.c_int)]
 
 
 def _randint16(shape, gen, device):
@@ -144,24 +144,74 @@ class SyntheticModel:
         return b
 
     def step(self, ctx, ids, q_lens, cache_seqlens, block_table, max_q_len, advance=False, want_logits=False, stream=None,
-             tokens_out=None):
+             tokens_out=None, all_rows=False):
         """ids int64 [rows], q_lens/cache_seqlens int32 [bsz], block_table int32 [bsz,pps] (device).  Returns tokens
-        (int64 [bsz]) and, if asked, fp32 logits [bsz, vocab].  `tokens_out` (int64 [bsz], device) makes the call
-        allocation-free once the scratch exists, which is what a CUDA-graph capture of the step needs."""
+        (int64 [bsz]) and, if asked, fp32 logits [bsz, vocab]; with `all_rows` one token (and logits row) per packed row.
+        `tokens_out` (int64, device) makes the call allocation-free once the scratch exists, which is what a CUDA-graph
+        capture of the step needs."""
         L = lib()
         L.exl3_step_scratch_bytes.restype = C.c_size_t
-        L.exl3_step_scratch_bytes.argtypes = [C.POINTER(Model), C.c_int, C.c_int]
+        L.exl3_step_scratch_bytes.argtypes = [C.POINTER(Model), C.c_int, C.c_int, C.c_int]
         bsz, rows = q_lens.numel(), ids.numel()
-        need = L.exl3_step_scratch_bytes(C.byref(self.struct), rows, bsz)
+        need = L.exl3_step_scratch_bytes(C.byref(self.struct), rows, bsz, int(all_rows))
         if self._scratch is None or self._scratch.numel() < need:
             self._scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
-        tokens = tokens_out if tokens_out is not None else torch.empty(bsz, dtype=torch.int64, device=self.device)
-        logits = torch.empty(bsz, self.cfg["vocab"], dtype=torch.float32, device=self.device) if want_logits else None
+        n_out = rows if all_rows else bsz
+        tokens = tokens_out if tokens_out is not None else torch.empty(n_out, dtype=torch.int64, device=self.device)
+        logits = torch.empty(n_out, self.cfg["vocab"], dtype=torch.float32, device=self.device) if want_logits else None
         batch = Batch(ids.data_ptr(), q_lens.data_ptr(), cache_seqlens.data_ptr(), block_table.data_ptr(), bsz, rows,
-                      max_q_len, block_table.shape[1], int(advance))
+                      max_q_len, block_table.shape[1], int(advance), int(all_rows))
         rc = L.exl3_step_forward(ctx.handle, ctx.stream(stream), C.byref(self.struct), C.byref(batch),
                                  C.c_void_p(self._scratch.data_ptr()), C.c_size_t(self._scratch.numel()),
                                  C.c_void_p(tokens.data_ptr()), C.c_void_p(0 if logits is None else logits.data_ptr()))
         if rc != 0:
             raise Exl3Error(f"exl3_step_forward failed ({rc}): {L.exl3_last_error(ctx.handle).decode()}")
         return tokens, logits
+
+
+class LoadedModel:
+    """A dense model read from safetensors files by exl3_model_load (Model::load, src/model.rs:262-420) into device memory
+    owned by the library; KV planes come from `pool`.  `step` is SyntheticModel.step."""
+
+    def __init__(self, paths, pool, n_layers, hidden, nq, nkv, hd, inter, vocab, norm_eps=1e-6, rope_theta=1e6,
+                 prefix="model", device="cuda", stream=None):
+        from .ffi import Checkpoint
+        L = lib()
+        L.exl3_model_load.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_char_p] + [C.c_int] * 7 + \
+                                     [C.c_float, C.c_float, C.c_void_p, C.POINTER(C.c_void_p)]
+        L.exl3_model_get.argtypes = [C.c_void_p]; L.exl3_model_get.restype = C.POINTER(Model)
+        L.exl3_model_error.argtypes = [C.c_void_p]; L.exl3_model_error.restype = C.c_char_p
+        L.exl3_model_free.argtypes = [C.c_void_p]
+        self.device, self.pool, self._scratch, self._h = device, pool, None, None
+        cks = [Checkpoint(p) for p in paths]
+        try:
+            arr = (C.c_void_p * len(cks))(*[c._h for c in cks])
+            h = C.c_void_p()
+            st = C.c_void_p(stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream)
+            rc = L.exl3_model_load(arr, len(cks), st, prefix.encode(), n_layers, hidden, nq, nkv, hd, inter, vocab,
+                                   norm_eps, rope_theta, pool._h, C.byref(h))
+            self._h = h
+            if rc != 0:
+                msg = L.exl3_model_error(h).decode() if h else "out of memory"
+                self.close()
+                raise Exl3Error(f"exl3_model_load: {msg} (code {rc})")
+        finally:
+            for c in cks:
+                c.close()
+        self.struct = L.exl3_model_get(self._h).contents
+        self.cfg = dict(n_layers=n_layers, hidden=hidden, nq=nq, nkv=nkv, hd=hd, inter=inter, vocab=vocab,
+                        pages=self.struct.pages, kv_bits=self.struct.kv_bits)
+
+    def close(self):
+        if self._h:
+            lib().exl3_model_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    step = SyntheticModel.step
+

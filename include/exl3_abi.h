@@ -37,6 +37,7 @@ extern "C" {
 #endif
 
 typedef struct exl3_ctx exl3_ctx;
+typedef struct exl3_pool exl3_pool;       /* KV pools + page table, see the end of this file */
 typedef void* exl3_stream;
 
 enum {
@@ -282,6 +283,7 @@ typedef struct {
     int32_t* cache_seqlens;     /* [bsz] tokens already cached; advanced by q_lens at the end of the step when `advance` */
     const int32_t* block_table; /* [bsz, pages_per_seq] */
     int bsz, rows, max_q_len, pages_per_seq, advance;
+    int all_rows;               /* 0: sample the last row of every sequence; 1: sample every packed row (speculative verify) */
 } exl3_batch;
 
 /* exl3_shim_hgemm (src/ffi.rs:66, csrc/exl3_shim.cpp:93 -> kernels/hgemm.cu:19-78): C[m,n] = A[m,k] . B[k,n],
@@ -339,8 +341,23 @@ EXL3_API int  exl3_linear_load(exl3_checkpoint* ck, exl3_stream stream, const ch
                                int out_features, int trim_padded_out, float softcap, exl3_linear_layer* out);
 EXL3_API void exl3_linear_free(exl3_linear_layer* layer);
 
-/* bytes of device scratch exl3_step_forward needs for up to `max_rows` packed rows and `max_bsz` sequences */
-EXL3_API size_t exl3_step_scratch_bytes(const exl3_model* model, int max_rows, int max_bsz);
+/* Model::load for the dense transformer family of exl3_step_forward (src/model.rs:262-420): reads, from one or more
+ * opened files, <prefix>.embed_tokens.weight, per layer <prefix>.layers.<i>.input_layernorm.weight,
+ * .post_attention_layernorm.weight, .self_attn.{q,k,v,o}_proj, .self_attn.{q,k}_norm.weight (optional),
+ * .mlp.{gate,up,down}_proj, then <prefix>.norm.weight and lm_head; NEOX rotary table from rope_theta; KV planes from
+ * `pool` (which must outlive the model).  Projections must be EXL3 tensors without bias and with features that are
+ * multiples of 128.  On failure *out still receives an object whose exl3_model_error says why; free it in either case. */
+typedef struct exl3_loaded_model exl3_loaded_model;
+EXL3_API int  exl3_model_load(exl3_checkpoint* const* shards, int n_shards, exl3_stream stream, const char* prefix, int n_layers,
+                              int hidden, int nq, int nkv, int hd, int inter, int vocab, float norm_eps, float rope_theta,
+                              const exl3_pool* pool, exl3_loaded_model** out);
+EXL3_API const exl3_model* exl3_model_get(const exl3_loaded_model* model);
+EXL3_API const char* exl3_model_error(const exl3_loaded_model* model);
+EXL3_API void exl3_model_free(exl3_loaded_model* model);
+
+/* bytes of device scratch exl3_step_forward needs for up to `max_rows` packed rows and `max_bsz` sequences (all_rows:
+ * for batches that sample every row, whose logits take max_rows * vocab floats) */
+EXL3_API size_t exl3_step_scratch_bytes(const exl3_model* model, int max_rows, int max_bsz, int all_rows);
 
 /* Device-side descriptor build (replaces the host loops of src/generator.rs:1548-1571): from q_lens/cache_seqlens it
  * writes cu_q [bsz+1], row_pos [rows] (RoPE position of every packed row) and last_row [bsz] (row whose logits are
@@ -350,7 +367,10 @@ EXL3_API int exl3_step_build_descriptors(exl3_ctx* ctx, exl3_stream stream, cons
                                          int32_t* row_pos, int32_t* last_row);
 
 /* One forward step over the packed batch.  Writes the greedy token of every sequence to out_tokens [bsz] (int64,
- * device; 0 for empty sequences) and, when logits != NULL, the fp32 logits [bsz, vocab] of the sampled rows. */
+ * device; 0 for empty sequences) and, when logits != NULL, the fp32 logits [bsz, vocab] of the sampled rows.  With
+ * batch->all_rows every packed row is sampled: out_tokens [rows], logits [rows, vocab] - row r of a sequence carries the
+ * model's choice after its first r + 1 tokens of this step, which is what a speculative verify round compares with the
+ * draft (src/generator.rs:1649-1790). */
 EXL3_API int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_model* model, const exl3_batch* batch,
                                void* scratch, size_t scratch_bytes, int64_t* out_tokens, float* logits);
 
@@ -435,7 +455,6 @@ EXL3_API int exl3_causal_conv1d_update(exl3_ctx* ctx, exl3_stream stream, const 
  * sequences through chained content hashes (least recently released hashed pages are repurposed when the free list is
  * empty).  A host that has no tensor library gets the same objects here; the page table is host state, the planes are
  * device memory owned by the pool. */
-typedef struct exl3_pool exl3_pool;
 /* k_bits = v_bits = 0: fp16 planes [pages,256,nkv,hd]; 2..8: int32 codes [pages,256,groups*bits] + fp16 scales
  * [pages,256,groups], groups = nkv*hd/32.  All planes start zeroed.  EXL3_ERR_NOMEM when the device cannot hold them.
  * n_layers = 0 creates the page table alone (no device memory, no device needed). */
@@ -444,6 +463,7 @@ EXL3_API void exl3_pool_destroy(exl3_pool* pool);
 /* device pointers of one layer: fp16 pools -> *k, *v (sk, sv NULL); quantised -> *k = codes of K, *sk = scales of K, ... */
 EXL3_API int  exl3_pool_layer(const exl3_pool* pool, int layer, void** k, void** v, void** sk, void** sv);
 EXL3_API int  exl3_pool_num_pages(const exl3_pool* pool);
+EXL3_API void exl3_pool_kv_bits(const exl3_pool* pool, int* k_bits, int* v_bits);
 /* pages that can be handed out: free + unreferenced hashed ones (PageTable::num_free) */
 EXL3_API int  exl3_pool_num_free(const exl3_pool* pool);
 EXL3_API int  exl3_pool_refcount(const exl3_pool* pool, int page);

@@ -167,3 +167,99 @@ def test_load_dense_layer_and_run_it(ctx, tmp_path, dtype):
     assert (got[:, out_f:] == 0).all(), "padded output columns carry neither weight nor bias"
     ck.free_linear(layer)
     ck.close()
+
+
+def _dump_model(model, tmp_path, shards=2, norm_dtype="F16"):
+    """The tensors of a SyntheticModel under the checkpoint's key scheme (src/model.rs:262-420), spread over `shards` files"""
+    c = model.cfg
+    t = {}
+
+    def vec(x):
+        a = x.cpu().numpy()
+        if norm_dtype == "F32":
+            return a.astype(np.float32)
+        if norm_dtype == "BF16":        # these values are not bf16-exact: the loader sees the truncated ones
+            return ("BF16", (a.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16))
+        return a
+
+    def lin(key, L, marker=True):
+        t[key + ".trellis"] = L.trellis.cpu().numpy()
+        t[key + ".suh"] = L.suh.cpu().numpy()
+        t[key + ".svh"] = L.svh.cpu().numpy()
+        if L.cb:
+            t[key + (".mcg" if L.cb == 1 else ".mul1")] = np.zeros(1, np.int32)
+
+    t["model.embed_tokens.weight"] = model.embed.cpu().numpy()
+    for i, L in enumerate(model.layers):
+        k = f"model.layers.{i}"
+        t[k + ".input_layernorm.weight"] = vec(L["attn_norm"])
+        t[k + ".post_attention_layernorm.weight"] = vec(L["mlp_norm"])
+        if L["q_norm"] is not None:
+            t[k + ".self_attn.q_norm.weight"] = vec(L["q_norm"])
+            t[k + ".self_attn.k_norm.weight"] = vec(L["k_norm"])
+        for n in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            lin(f"{k}.self_attn.{n}", L[n])
+        for n in ("gate_proj", "up_proj", "down_proj"):
+            lin(f"{k}.mlp.{n}", L[n])
+    t["model.norm.weight"] = vec(model.final_norm)
+    lin("lm_head", model.lm_head)
+    names = list(t)
+    paths = []
+    for s in range(shards):
+        part = {n: t[n] for n in names[s::shards]}
+        p = tmp_path / f"model-{s + 1:05d}-of-{shards:05d}.safetensors"
+        H.write_safetensors(p, part, metadata={"format": "pt"})
+        paths.append(str(p))
+    return paths
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kv_bits,norm_dtype", [(0, "F16"), (4, "F32")])
+def test_model_from_checkpoint_steps_like_the_model_in_memory(ctx, tmp_path, kv_bits, norm_dtype):
+    """a two-layer model written to two safetensors files, read back by exl3_model_load into a pool of its own, gives the
+    same tokens and logits as the in-memory model over a ragged prefill step and a decode step"""
+    import torch
+    import exl3b200
+    from exl3b200.step import LoadedModel, SyntheticModel
+    n_layers, hidden, nq, nkv, hd, inter, vocab, pages = 2, 1024, 16, 8, 128, 3072, 2048, 8
+    pool_a = exl3b200.Pool(0, n_layers, pages, nkv, hd, kv_bits, kv_bits)
+    pool_b = exl3b200.Pool(0, n_layers, pages, nkv, hd, kv_bits, kv_bits)
+    mem = SyntheticModel(n_layers, hidden, nq, nkv, hd, inter, vocab, K=4, cb=1, pages=pages, kv_bits=kv_bits, seed=3, pool=pool_a)
+    paths = _dump_model(mem, tmp_path, shards=2, norm_dtype=norm_dtype)
+    disk = LoadedModel(paths, pool_b, n_layers, hidden, nq, nkv, hd, inter, vocab)
+    assert disk.struct.n_layers == n_layers and disk.struct.kv_bits == kv_bits and disk.struct.pages == pages
+    r = H.rng(4)
+    q_lens = np.array([70, 1, 300], np.int32)
+    ids = r.integers(0, vocab, int(q_lens.sum())).astype(np.int64)
+    bt = np.array([[0, 0], [1, 0], [2, 3]], np.int32)
+    outs = []
+    for model in (mem, disk):
+        sl = torch.zeros(3, dtype=torch.int32, device="cuda")
+        tok, logits = model.step(ctx, H.to_dev(ids), H.to_dev(q_lens), sl, H.to_dev(bt), int(q_lens.max()), advance=True, want_logits=True)
+        tok2, logits2 = model.step(ctx, tok.clone(), H.to_dev(np.ones(3, np.int32)), sl, H.to_dev(bt), 1, advance=True, want_logits=True)
+        ctx.poll_status()
+        outs.append((tok.cpu().numpy(), logits.cpu().numpy(), tok2.cpu().numpy(), logits2.cpu().numpy()))
+    a, b = outs
+    # same weights and the same kernels; the rotary table is computed by two different pow() (torch's and libm's)
+    # (a last-bit difference in a rotation can move a 4-bit KV code by one step, hence the wider bar there)
+    scale = np.abs(a[1]).max()
+    tol = (2e-3 if kv_bits == 0 else 1e-2) * scale
+    assert np.abs(a[1] - b[1]).max() <= tol and np.abs(a[3] - b[3]).max() <= tol
+    for t_mem, t_disk, lg in ((a[0], b[0], a[1]), (a[2], b[2], a[3])):
+        for s in range(3):
+            if t_mem[s] != t_disk[s]:          # allowed only on a near-tie
+                assert abs(lg[s, t_mem[s]] - lg[s, t_disk[s]]) <= tol
+    disk.close()
+    pool_a.close(); pool_b.close()
+
+
+@pytest.mark.gpu
+def test_model_load_reports_what_is_missing(ctx, tmp_path):
+    import exl3b200
+    from exl3b200.step import LoadedModel
+    p = tmp_path / "empty.safetensors"
+    H.write_safetensors(p, {"model.embed_tokens.weight": np.zeros((256, 128), np.float16)})
+    pool = exl3b200.Pool(0, 1, 2, 1, 128, 0, 0)
+    with pytest.raises(exl3b200.Exl3Error, match="input_layernorm"):
+        LoadedModel([str(p)], pool, 1, 128, 1, 1, 128, 128, 256)
+    pool.close()

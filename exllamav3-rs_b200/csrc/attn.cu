@@ -106,20 +106,41 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnParams p, i
     const int packed = (row - row_base) * G + (head - kvh * G);
     const int rb = packed / rows_per_cta, lr = packed - rb * rows_per_cta;
     const int item0 = p.seq_base[b] + rb * splits;
+    // A sequence of a small batch can have dozens of splits; walked one after the other by every lane their loads form
+    // one long dependent chain (53 us per launch on 4 verify sequences).  So the lanes take the splits' maxima and sums
+    // side by side, and the rows themselves are fetched four splits at a time.
+    static_assert(D == 128, "a lane covers 4 dims as two 8-byte loads");
+    const size_t stride = (size_t)p.nkv * rows_per_cta * (D + 2);             // floats between consecutive splits
+    const float* base = p.partial + (((size_t)item0 * p.nkv + kvh) * rows_per_cta + lr) * (D + 2);
     float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s)
-        mm = fmaxf(mm, p.partial[(((size_t)(item0 + s) * p.nkv + kvh) * rows_per_cta + lr) * (D + 2) + D]);
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        const int s = s0 + lane;
+        if (s < splits) mm = fmaxf(mm, base[(size_t)s * stride + D]);
+    }
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
     float acc[D / 32], ll = 0.f;
     #pragma unroll
     for (int e = 0; e < D / 32; ++e) acc[e] = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float* pp = p.partial + (((size_t)(item0 + s) * p.nkv + kvh) * rows_per_cta + lr) * (D + 2);
-        const float ms = pp[D];
-        const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-        ll += pp[D + 1] * sc;
-        #pragma unroll
-        for (int e = 0; e < D / 32; ++e) acc[e] += pp[lane * (D / 32) + e] * sc;
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        const int s = s0 + lane;
+        float sc_l = 0.f;
+        if (s < splits) {
+            const float ms = base[(size_t)s * stride + D];
+            sc_l = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+            ll += base[(size_t)s * stride + D + 1] * sc_l;
+        }
+        const int cnt = min(32, splits - s0);
+        #pragma unroll 4
+        for (int j = 0; j < cnt; ++j) {
+            const float sc = __shfl_sync(0xffffffffu, sc_l, j);
+            const float* pp = base + (size_t)(s0 + j) * stride + lane * (D / 32);
+            const float2 v0 = *reinterpret_cast<const float2*>(pp), v1 = *reinterpret_cast<const float2*>(pp + 2);
+            acc[0] += v0.x * sc; acc[1] += v0.y * sc; acc[2] += v1.x * sc; acc[3] += v1.y * sc;
+        }
     }
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, o);
     const float inv = ll > 0.f ? 1.0f / ll : 0.f;
     half* op = p.o + ((size_t)row * p.nq + head) * D + lane * (D / 32);
     #pragma unroll
@@ -223,6 +244,8 @@ cudaError_t launch_attn_q4(const AttnParams& p, dim3 grid, cudaStream_t st)
     return cudaPeekAtLastError();
 }
 
+bool q4_decode_kernel_applies(const AttnParams& p, bool quant);
+
 // One pass = plan + attention + combine over the sequences whose packed row count lies in (rows_lo, rows_hi].
 int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int max_rows, int rows_lo, int rows_hi,
               bool decode_shape, bool quant, size_t* ws_off)
@@ -241,8 +264,7 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     // (rounded down: one CTA more than fits would run alone in a second wave after all the others have finished)
     // 4-bit pools, decode class: the kernel that builds the K operand from the codes (its scale copies are 16 bytes wide =
     // two heads, so the kv head count must be even and the planes 16-byte aligned)
-    static const bool no_q4 = getenv("EXL3_B200_NO_Q4_ATTN") != nullptr;
-    const bool use_q4 = q4 && decode_shape && !no_q4 && p.nkv % 2 == 0 && aligned16(p.qk) && aligned16(p.qv) && aligned16(p.sk) && aligned16(p.sv);
+    const bool use_q4 = decode_shape && q4_decode_kernel_applies(p, quant);
     int per_sm = 1;
     if (use_q4) per_sm = 3;
     else if (!use_tc) {
@@ -314,20 +336,32 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
 // Sequences with at most 16 packed (query, head) rows (decode, short verify) take the kernel that spreads the keys of a
 // tile over the four warps; longer ones (verify with many heads, prefill chunks) the one with a 16-row tile per warp.
 // A ragged batch that holds both kinds runs one pass for each.
+// true when attn_pass will take the 4-bit decode-class kernel for these pools
+bool q4_decode_kernel_applies(const AttnParams& p, bool quant)
+{
+    static const bool no_q4 = getenv("EXL3_B200_NO_Q4_ATTN") != nullptr;
+    return quant && p.k_bits == 4 && p.v_bits == 4 && !no_q4 && p.nkv % 2 == 0 && aligned16(p.qk) && aligned16(p.qv) &&
+           aligned16(p.sk) && aligned16(p.sv);
+}
+
 int attn_impl(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int max_q_len, bool quant)
 {
     const int G = p.nq / p.nkv;
     const int max_rows = max_q_len * G;
     size_t off = 0;
-    if (max_rows <= 16) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 16, true, quant, &off);
+    // Decode class = sequences with at most 16 packed rows.  Over 4-bit pools it also takes up to 48 rows (speculative
+    // verify: 8 query rows x 5 heads) as row blocks of 16 that each walk the codes again: the kernel that builds its
+    // operands from the codes is that much cheaper per key than the generic one (4 verify sequences: 90 us per layer there).
+    const int dec_rows = q4_decode_kernel_applies(p, quant) ? 48 : 16;
+    if (max_rows <= dec_rows) return attn_pass(ctx, st, p, total_rows, max_rows, 0, dec_rows, true, quant, &off);
     if (!p.cu_q) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 1 << 30, false, quant, &off);
     // Ragged batch with both classes: the decode-class pass (bound by HBM) runs on the context's second stream beside the
     // long-class pass (bound by the tensor core and the MUFU); they touch disjoint sequences and output rows, and each
     // has its own scratch.  Fork and join by events, which also works while the caller's stream is being captured.
     if (cudaEventRecord(ctx->ev_fork, st) != cudaSuccess || cudaStreamWaitEvent(ctx->aux_stream, ctx->ev_fork, 0) != cudaSuccess)
         return exl3_fail(ctx, EXL3_ERR_CUDA, "attention: stream fork failed");
-    int rc = attn_pass(ctx, ctx->aux_stream, p, total_rows, 16, 0, 16, true, quant, &off);
-    int rc2 = rc == EXL3_OK ? attn_pass(ctx, st, p, total_rows, max_rows, 16, 1 << 30, false, quant, &off) : rc;
+    int rc = attn_pass(ctx, ctx->aux_stream, p, total_rows, dec_rows, 0, dec_rows, true, quant, &off);
+    int rc2 = rc == EXL3_OK ? attn_pass(ctx, st, p, total_rows, max_rows, dec_rows, 1 << 30, false, quant, &off) : rc;
     // always join, also after an error, so that a capture in progress stays well-formed
     if (cudaEventRecord(ctx->ev_join, ctx->aux_stream) != cudaSuccess || cudaStreamWaitEvent(st, ctx->ev_join, 0) != cudaSuccess)
         return exl3_fail(ctx, EXL3_ERR_CUDA, "attention: stream join failed");

@@ -102,6 +102,11 @@ __device__ __forceinline__ uint32_t ex2_h2(uint32_t x)
 #ifndef ATC_EXP_F16X2
 #define ATC_EXP_F16X2 0
 #endif
+// registers of a softmax thread / of a service thread after the split: 256 x 184 + 128 x 120 <= 64 K.  (Holding all 128
+// scores of a row through the maximum and both exponential passes - one TMEM read and one wait per tile instead of
+// three - needs about 230 registers; at 184 it spills and ran at 278 us against 162 us on 4 x 256 query rows.)
+#define ATC_REG_SOFTMAX 184
+#define ATC_REG_SERVICE 120
 __device__ __forceinline__ float fmax3(float a, float b, float c)
 {
     float y;
@@ -169,8 +174,8 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attn_tc_kernel(const __grid_co
     const uint32_t tmem_base = *tmem_slot;             // S of block i: columns i*128 (P over its last 64); O of block i: 256 + i*128
     bool failed = false;
 
-    if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
-    else asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+    if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ATC_REG_SERVICE));
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(ATC_REG_SOFTMAX));
     if (warp == 8) {
         // ===== producer: K and V tiles by TMA out of the paged pools; ring item 2j = K of tile j, 2j+1 = V of tile j
         if (lane == 0) {

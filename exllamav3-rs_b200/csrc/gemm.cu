@@ -474,7 +474,7 @@ int gemm_decode_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, co
         const int j = i < nseg ? i : nseg - 1;              // unused slots repeat the last tensor (never selected)
         if (i < nseg) {
             pa.a_frag[i] = (uint32_t*)exl3_ws_take(ctx, &off, (size_t)mt * k * 32);
-            pa.rowsum[i] = (float*)exl3_ws_take(ctx, &off, (size_t)mt * 8 * 4);
+            pa.rowsum[i] = (float*)exl3_ws_take(ctx, &off, (size_t)GD_PRO_SPLIT * mt * 8 * 4);
             if (!pa.a_frag[i] || !pa.rowsum[i]) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the activations");
             pa.suh[i] = suh[i];
             blocks += n[i] / 128;
@@ -508,7 +508,8 @@ int gemm_decode_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, co
     p.partial = (float*)exl3_ws_take(ctx, &off, (size_t)grid * 2 * m * 128 * 4);
     if (!p.partial) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the partial sums");
     p.counters = ctx->counters; p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
-    gemm_decode_prologue_kernel<<<dim3(8 * mt, nseg), 256, 0, st>>>(A, pa, m, k);
+    p.rowsum_parts = GD_PRO_SPLIT;
+    gemm_decode_prologue_kernel<<<dim3(8 * mt, nseg, GD_PRO_SPLIT), 256, 0, st>>>(A, pa, m, k);
     ctx->launches++;
     cudaError_t e = launch_decode_k(K, cb, mt, rmap, p, grid, st);
     ctx->launches++;
@@ -545,6 +546,22 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
     if (m <= GD_MAX_M && ctx->use_decode) {
         const half* suh1 = (const half*)suh; const half* svh1 = (const half*)svh;
         return gemm_decode_rows(ctx, st, (const half*)A, 1, &trellis, &C, &suh1, &svh1, &n, m, k, K, c_fp32, cb);
+    }
+    // 17..32 rows on a tensor with few column slabs: the tcgen05 grid would be one CTA pair per 256-column slab, i.e. 20 of
+    // the 74 pair slots for n = 5120, each walking all of k at the decoders' pace (17408 x 5120: about 125 us), while the
+    // streaming kernel spreads (column block, k chunk) units over every SM.  Measured at 4 bpw: 17408 x 5120 takes 110 us in
+    // two passes against 126 us (92 us at 20 rows), but 5120 x 5120 takes 65 us against 44 us: the slab walk is short
+    // there.  So: few slabs and a long reduction dimension.
+    if (m <= 2 * GD_MAX_M && ctx->use_decode && (n + TC_BN - 1) / TC_BN <= ctx->num_sms / 4 && k >= 12288) {
+        const half* suh1 = (const half*)suh; const half* svh1 = (const half*)svh;
+        for (int r0 = 0; r0 < m; r0 += GD_MAX_M) {
+            const int rows = m - r0 < GD_MAX_M ? m - r0 : GD_MAX_M;
+            const void* a1 = (const half*)A + (size_t)r0 * k;
+            void* c1 = c_fp32 ? (void*)((float*)C + (size_t)r0 * n) : (void*)((half*)C + (size_t)r0 * n);
+            const int rc = gemm_decode_rows(ctx, st, (const half*)a1, 1, &trellis, &c1, &suh1, &svh1, &n, rows, k, K, c_fp32, cb);
+            if (rc != EXL3_OK) return rc;
+        }
+        return EXL3_OK;
     }
     int tc_rows = 0;
     if (m > TC_MAX_SMALL_M && (n % TC_BN == 0 || ctx->use_pair) && ctx->use_tc) {

@@ -80,7 +80,8 @@ template <int K, int MT> struct GdSmem {
 
 struct GemmDecodeParams {
     const uint4* a_frag[GD_MAX_SEG];   // [MT][k/64][4][32] uint4: activations in B-fragment order, duplicated halves
-    const float* rowsum[GD_MAX_SEG];   // [8*MT] sum over k of the transformed activations (codebook 2 only)
+    const float* rowsum[GD_MAX_SEG];   // [rowsum_parts][8*MT] partial sums over k of the transformed activations (codebook 2 only)
+    int rowsum_parts;                  // k ranges the input transform was split into (their sums are added in order)
     void* C[GD_MAX_SEG];               // [m][n] fp16 or fp32
     const half* svh[GD_MAX_SEG];       // [n] or NULL
     int n[GD_MAX_SEG];
@@ -173,8 +174,10 @@ __device__ __forceinline__ void gd_slot(const uint32_t* __restrict__ sb, int ch,
 struct GemmDecodePrologueArgs { const half* suh[GD_MAX_SEG]; uint32_t* a_frag[GD_MAX_SEG]; float* rowsum[GD_MAX_SEG]; };
 
 // one CTA: batch-row slot b of one tensor's activations
+constexpr int GD_PRO_SPLIT = 4;      // CTAs along k per row slot in the input transform of the single-tensor paths
+
 __device__ __forceinline__ void gd_prologue_row(const half* __restrict__ Arow, const half* __restrict__ suh, uint32_t* __restrict__ out,
-                                                float* __restrict__ rowsum, int b, bool valid, int k)
+                                                float* __restrict__ rowsum, int b, bool valid, int k, int part_idx = 0, int parts = 1)
 {
     __shared__ float sh[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,7 +185,9 @@ __device__ __forceinline__ void gd_prologue_row(const half* __restrict__ Arow, c
     const int q = lane & 3;                                  // position of the lane's 4 values inside a 16-k tile row
     const int t0 = 2 * (q & 1), w0 = 2 * (q >> 1);
     float part = 0.0f;
-    for (int blk = warp; blk < k / 128; blk += 8) {
+    const int per = (k / 128 + parts - 1) / parts;             // 128-blocks of this CTA's k range
+    const int blk_end = min(k / 128, (part_idx + 1) * per);
+    for (int blk = part_idx * per + warp; blk < blk_end; blk += 8) {
         uint32_t h0 = 0, h1 = 0, h2 = 0, h3 = 0;
         if (valid) {
             uint2 raw = reinterpret_cast<const uint2*>(Arow + blk * 128)[lane];
@@ -224,7 +229,7 @@ __device__ __forceinline__ void gd_prologue_row(const half* __restrict__ Arow, c
     if (threadIdx.x == 0) {
         float s = 0.0f;
         for (int w = 0; w < 8; ++w) s += sh[w];
-        rowsum[b] = s;
+        rowsum[(size_t)part_idx * gridDim.x + b] = s;
     }
 }
 
@@ -233,7 +238,7 @@ static __global__ void __launch_bounds__(256) gemm_decode_prologue_kernel(const 
 {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int b = blockIdx.x, seg = blockIdx.y;
-    gd_prologue_row(A + (size_t)b * k, args.suh[seg], args.a_frag[seg], args.rowsum[seg], b, b < m, k);
+    gd_prologue_row(A + (size_t)b * k, args.suh[seg], args.a_frag[seg], args.rowsum[seg], b, b < m, k, blockIdx.z, gridDim.z);
 }
 
 // Table mode: grid (row slots, product slots).  Slot j transforms rows of A[j] (or of A[0] when a_slot_stride is 0) with
@@ -519,6 +524,11 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
                 rsum = p.rowsum[0] + (size_t)seg * SM::ROWS;
                 if (p.weights) r128 *= __half2float(p.weights[seg]);
             }
+            auto rs_of = [&](int row) -> float {
+                float a = 0.f;
+                for (int z = 0; z < p.rowsum_parts; ++z) a += rsum[(size_t)z * SM::ROWS + row];
+                return a;
+            };
             // sum of the 8 k-slices of one row, in slice order; lane = 4 consecutive columns
             auto row_sum = [&](int row) -> float4 {
                 float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -539,7 +549,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
             const int ncontrib = c_last - c_first + 1;
             if (ncontrib == 1) {
                 for (int row = 0; row < mrows && store; ++row)
-                    gd_store_row<CB>(row_sum(row), lane, CB == 2 ? rsum[row] : 0.f, svh, Cout, (size_t)row * n + n0 + lane * 4, n0, p.c_fp32, r128);
+                    gd_store_row<CB>(row_sum(row), lane, CB == 2 ? rs_of(row) : 0.f, svh, Cout, (size_t)row * n + n0 + lane * 4, n0, p.c_fp32, r128);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_red_free);
             } else {
@@ -582,7 +592,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_decode_kernel(const __grid
                         #pragma unroll
                         for (int r = 0; r < 8; ++r)
                             if (row0 + r < mrows && store)
-                                gd_store_row<CB>(a[r], lane, CB == 2 ? rsum[row0 + r] : 0.f, svh, Cout, (size_t)(row0 + r) * n + n0 + lane * 4, n0, p.c_fp32, r128);
+                                gd_store_row<CB>(a[r], lane, CB == 2 ? rs_of(row0 + r) : 0.f, svh, Cout, (size_t)(row0 + r) * n + n0 + lane * 4, n0, p.c_fp32, r128);
                     }
                 }
             }

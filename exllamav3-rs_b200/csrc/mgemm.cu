@@ -130,7 +130,7 @@ extern "C" int exl3_mgemm(exl3_ctx* ctx, exl3_stream stream, const void* A, cons
         gemm_decode_prologue_multi_kernel<<<dim3(8 * mt, bszm), 256, 0, st>>>(a0, bszm_in == 1 ? 0 : (size_t)m * k, (const half* const*)suh,
                                                                              indices, a_frag, rowsum, 8 * mt, rows, k);
         ctx->launches++;
-        p.a_frag[0] = (const uint4*)a_frag; p.rowsum[0] = rowsum;
+        p.a_frag[0] = (const uint4*)a_frag; p.rowsum[0] = rowsum; p.rowsum_parts = 1;
         p.C[0] = c_fp32 ? (void*)((float*)C + (size_t)r0 * n) : (void*)((half*)C + (size_t)r0 * n);
         p.n[0] = p.n[1] = p.n[2] = n;
         p.blk_end[0] = p.blk_end[1] = p.blk_end[2] = blocks;

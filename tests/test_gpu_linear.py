@@ -192,7 +192,8 @@ def test_gemm_decode_ragged_k_chunks(ctx, ref, m, k, n, cb):
     _gemm_case(ctx, ref, m, k, n, 4, cb, m % 2 == 0, 800 + m + k + cb)
 
 
-@pytest.mark.parametrize("m,k,n,K", [(16, 5120, 151936, 4), (7, 17408, 5120, 3), (12, 5120, 5120, 8)])
+@pytest.mark.parametrize("m,k,n,K", [(16, 5120, 151936, 4), (7, 17408, 5120, 3), (12, 5120, 5120, 8), (20, 17408, 5120, 4),
+                                     (32, 5120, 5120, 4)])
 def test_gemm_decode_model_shapes(ctx, ref, m, k, n, K):
     """the head, down_proj and o_proj shapes of the 27B-class model at decode row counts: against the reference op, and
     against the oracle on a seeded subset of 128-column blocks (the product has no cross-block terms)"""

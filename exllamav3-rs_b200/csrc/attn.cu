@@ -2,6 +2,7 @@
 #include <algorithm>
 #include "attn_paged.cuh"
 #include "attn_tc.cuh"
+#include "attn_tc2.cuh"
 #include "attn_q4.cuh"
 
 namespace {
@@ -212,6 +213,35 @@ cudaError_t launch_attn_tc(exl3_ctx* ctx, const AttnParams& p, int max_items, cu
     return cudaPeekAtLastError();
 }
 
+cudaError_t launch_attn_tc2(exl3_ctx* ctx, const AttnParams& p, int max_items, cudaStream_t st)
+{
+    EncodeTiledFn enc = attn_encode_tiled();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap maps[2];
+    const void* pools[2] = {p.kc, p.vc};
+    for (int i = 0; i < 2; ++i) {
+        cuuint64_t dims[4] = {(cuuint64_t)ATC_D, (cuuint64_t)p.nkv, 256, (cuuint64_t)p.pages};
+        cuuint64_t strides[3] = {(cuuint64_t)ATC_D * 2, (cuuint64_t)p.nkv * ATC_D * 2, (cuuint64_t)256 * p.nkv * ATC_D * 2};
+        cuuint32_t box[4] = {64, 1, (cuuint32_t)ATC_TN, 1};           // 128 tokens of one page, one 64-wide d block
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        if (enc(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(pools[i]), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    (void)ctx;
+    attn_tc2_kernel<<<dim3(max_items, p.nkv), A2_THREADS, A2_SMEM, st>>>(maps[0], maps[1], p);
+    return cudaPeekAtLastError();
+}
+
 // decode-class kernel over 4-bit pools: tensor maps over the code planes ([tokens][nkv * 16] words) and the scale planes
 // ([tokens][nkv * 4] halves, copied in 16-byte pairs of heads)
 cudaError_t launch_attn_q4(const AttnParams& p, dim3 grid, cudaStream_t st)
@@ -258,7 +288,9 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     // (sequences with 17..128 packed rows - speculative verify - stay on it too: on 32 sequences x 8 query rows x 5 heads
     // the 64-row mma.sync kernel measured 228 us against 224 us, at 16 and 24 query rows 373 / 383 us against 233 / 241 us)
     const bool use_tc = !decode_shape && !quant && ctx->mma_attn != 0 && p.scale_log2 > 0.f;
-    const int rows_per_cta = decode_shape ? 16 : (use_tc ? ATC_CTA_ROWS : 64);
+    // two arrangements of the tcgen05 kernel: 128-row items with two softmax threads per row (default), 256-row items
+    static const bool tc_256 = getenv("EXL3_B200_ATTN_TC256") != nullptr;
+    const int rows_per_cta = decode_shape ? 16 : (use_tc ? (tc_256 ? ATC_CTA_ROWS : A2_ROWS) : 64);
     const int rb_max = (max_rows + rows_per_cta - 1) / rows_per_cta;
     // resident CTAs per SM over all kv heads: about 3 for the mma.sync kernels, 1 for the tcgen05 kernel (all of TMEM)
     // (rounded down: one CTA more than fits would run alone in a second wave after all the others have finished)
@@ -273,12 +305,14 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
         per_sm = std::max(1, std::min(q4 ? 4 : 3, (int)((227 * 1024) / (smem + 1024))));
     }
     const int grid_x = std::max(1, ctx->num_sms * per_sm / p.nkv);
-    // tcgen05 kernel: two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs a
-    // 133 KB partial per kv head written and read back (4 per slot was measured 20 % slower, 1 per slot 2 % slower).
+    // tcgen05 kernels: two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs
+    // a partial per kv head written and read back (128-row kernel on 4 x 256 query rows: 154 / 168 / 171 / 188 / 205 us at
+    // 2 / 3 / 4 / 6 / 8 per slot).
     // mma.sync kernels (units handed out dynamically, 8 KB partials): three per slot; four for the generic quantised
     // kernel, which spends most of its time scaling codes and balances better on finer items (8-bit pools, 64 decode
     // sequences: 510 us against 598 us).
-    const int target_items = grid_x * (use_tc ? 2 : ((quant && !use_q4) ? 4 : 3));
+    static const int tc_items = getenv("EXL3_TUNE_TC_ITEMS") ? atoi(getenv("EXL3_TUNE_TC_ITEMS")) : 0;
+    const int target_items = grid_x * (use_tc ? (tc_items ? tc_items : 2) : ((quant && !use_q4) ? 4 : 3));
     // items <= target + sum of row blocks (every (sequence, row block) rounds its split count up once); the row blocks are
     // bounded by bsz * rb_max and, usually much tighter for ragged batches, by total_rows * G / rows_per_cta + bsz
     const long long rb_sum = std::min((long long)p.bsz * rb_max, ((long long)total_rows * G + rows_per_cta - 1) / rows_per_cta + p.bsz);
@@ -320,7 +354,7 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     cudaError_t e;
     if (!use_tc && cudaMemsetAsync(&plan->next, 0, sizeof(int), st) != cudaSuccess)      // the persistent kernel's work counter
         return exl3_fail(ctx, EXL3_ERR_CUDA, "attention: cudaMemsetAsync failed");
-    if (use_tc) e = launch_attn_tc(ctx, p, max_items, st);
+    if (use_tc) e = tc_256 ? launch_attn_tc(ctx, p, max_items, st) : launch_attn_tc2(ctx, p, max_items, st);
     else if (use_q4) e = launch_attn_q4(p, grid, st);
     else if (q4)    e = decode_shape ? launch_attn<128, 1, 4, 4>(p, grid, st) : launch_attn<128, 4, 1, 4>(p, grid, st);
     else if (quant) e = decode_shape ? launch_attn<128, 1, 4, 8>(p, grid, st) : launch_attn<128, 4, 1, 8>(p, grid, st);

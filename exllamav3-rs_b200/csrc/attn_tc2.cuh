@@ -1,0 +1,354 @@
+// Paged flash attention on tcgen05, second arrangement: one CTA = one work item (sequence, 128-row block, KV split) of one
+// kv head, TWO softmax threads per row and a double-buffered S.
+//
+// Why.  In the 256-row kernel (attn_tc.cuh) a softmax thread owns a whole row of a 128-key tile: it reads its 128 scores
+// from tensor memory in three round trips (the row maximum needs all of them, registers hold 64) and takes 128
+// exponentials, and the tensor core idles through that (tensor pipe 34 % busy, long-scoreboard stalls 4.3 per issued
+// instruction).  Here the two threads of a row take 64 keys each: one round trip, 64 exponentials, the row maximum and
+// sum exchanged through shared memory between the two warps that share a TMEM lane quadrant.  S has two buffers, so
+// S(j+1) = Q K(j+1)^T is computed while the threads work on tile j, and PV(j) follows as soon as P(j) is written.
+//
+// TMEM: S0 columns 0..127, S1 128..255 (P of a tile over the last 64 columns of its S buffer, packed fp16), O 256..383.
+// Warps 0..3: keys 0..63 of every tile, lane quadrant = warp; warps 4..7: keys 64..127; warp 8: TMA producer; warp 9: MMA
+// issuer and TMEM owner.  K/V tiles by 4-D TMA out of the paged pools through a ring of five 32 KB buffers in the order
+// the issuer consumes them: K0 K1 V0 K2 V1 K3 ...  Every wait is bounded; a wait that runs out sets the status word.
+#pragma once
+#include "attn_tc.cuh"
+
+namespace exl3 {
+
+constexpr int A2_ROWS = 128, A2_TN = 128, A2_D = 128;
+constexpr int A2_KV_SLOTS = 5;
+constexpr int A2_THREADS = 384;
+constexpr int A2_Q_BYTES = A2_ROWS * A2_D * 2;
+constexpr int A2_KV_SLOT = A2_TN * A2_D * 2;
+constexpr int A2_OFF_Q = 0;
+constexpr int A2_OFF_KV = A2_OFF_Q + A2_Q_BYTES;
+constexpr int A2_OFF_X = A2_OFF_KV + A2_KV_SLOTS * A2_KV_SLOT;        // exchange of row maxima / sums: [2 buffers][2 halves][128] floats
+constexpr int A2_OFF_BAR = A2_OFF_X + 2 * 2 * A2_ROWS * 4;
+// q_full, kv_full/kv_empty[slots], s_full[2], p_full[2], pv_done, o_full, pair[4]
+constexpr int A2_NBARS = 1 + 2 * A2_KV_SLOTS + 2 + 2 + 1 + 1 + 4;
+constexpr int A2_SMEM = A2_OFF_BAR + A2_NBARS * 8 + 16 + 1024;
+
+// Rendezvous of the two warps that own a lane quadrant, with a bounded wait like every other wait here (a named barrier
+// would leave one warp waiting for ever if its partner had left through a time-out).  False on time-out.
+__device__ __forceinline__ bool a2_pair_sync(uint64_t* bar, uint32_t& phase, int lane)
+{
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+    const bool ok = mbar_wait_warp(bar, phase);
+    phase ^= 1;
+    return ok;
+}
+
+__global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_constant__ CUtensorMap kmap,
+                                                                 const __grid_constant__ CUtensorMap vmap, const AttnParams p)
+{
+    const int item_idx = blockIdx.x;
+    if (item_idx >= p.plan->n_items) return;
+    extern __shared__ uint8_t smem_unaligned[];
+    uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + A2_OFF_BAR);
+    uint64_t* q_full = bars;
+    uint64_t* kv_full = q_full + 1;                        uint64_t* kv_empty = kv_full + A2_KV_SLOTS;
+    uint64_t* s_full = kv_empty + A2_KV_SLOTS;             // [2]
+    uint64_t* p_full = s_full + 2;                         // [2]
+    uint64_t* pv_done = p_full + 2;
+    uint64_t* o_full = pv_done + 1;
+    uint64_t* pair_bar = o_full + 1;                       // [4]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
+    float* xch = reinterpret_cast<float*>(smem + A2_OFF_X);
+    __shared__ int s_failed;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.y;
+    const int G = p.nq / p.nkv;
+    const int chunk = p.plan->chunk;
+    const AttnItem item = p.items[item_idx];
+    const int b = item.b;
+    const int row_base = p.cu_q ? p.cu_q[b] : b * p.q_len;
+    const int ql = p.cu_q ? p.cu_q[b + 1] - row_base : p.q_len;
+    const int total_k = p.seqlens[b] + (p.cu_q ? ql : p.kv_append);
+    const int splits = p.seq_splits[b];
+    const int r0 = item.rb * A2_ROWS;
+    const int i_last = min(ql - 1, (r0 + A2_ROWS - 1) / G);
+    const int vis_max = p.causal ? min(total_k, total_k - ql + i_last + 1) : total_k;
+    const int k_begin = item.split * chunk;
+    const int k_end = min(min(k_begin + chunk, total_k), vis_max);
+    const int n_tiles = k_end > k_begin ? (k_end - k_begin + A2_TN - 1) / A2_TN : 0;
+    const int32_t* bt = p.block_table + (size_t)b * p.pps;
+
+    if (tid == 0) {
+        s_failed = 0;
+        mbar_init(q_full, 8);
+        for (int i = 0; i < 2; ++i) { mbar_init(&p_full[i], 8); mbar_init(&s_full[i], 1); }
+        for (int i = 0; i < A2_KV_SLOTS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        mbar_init(pv_done, 1);
+        mbar_init(o_full, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+        mbar_fence_init();
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool failed = false;
+
+    // 64 scores per softmax thread fit the launch allocation of 168 registers; the service warps keep 152 (their code -
+    // descriptors, ring cursors - spills below about 140)
+    if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 152;");
+
+    if (warp == 8) {
+        // ===== producer: ring items in the order the issuer takes them: K0, K1, then V(j), K(j+2) for every tile j
+        if (lane == 0 && n_tiles > 0) {
+            int it = 0;
+            auto load = [&](int tile, bool is_v) -> bool {
+                const int slot = it % A2_KV_SLOTS;
+                if (it >= A2_KV_SLOTS && !mbar_wait_sleep(&kv_empty[slot], ((it / A2_KV_SLOTS) - 1) & 1)) return false;
+                const int k0 = k_begin + tile * A2_TN;
+                const int page = bt[k0 >> 8], tok = k0 & 255;
+                uint8_t* st = smem + A2_OFF_KV + slot * A2_KV_SLOT;
+                const CUtensorMap* map = is_v ? &vmap : &kmap;
+                mbar_expect_tx(&kv_full[slot], A2_KV_SLOT);
+                tma_load_4d(st, map, 0, kvh, tok, page, &kv_full[slot]);
+                tma_load_4d(st + A2_TN * 128, map, 64, kvh, tok, page, &kv_full[slot]);
+                ++it;
+                return true;
+            };
+            bool ok = load(0, false);
+            if (ok && n_tiles > 1) ok = load(1, false);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                ok = load(j, true);
+                if (ok && j + 2 < n_tiles) ok = load(j + 2, false);
+            }
+            if (!ok) failed = true;
+        }
+    } else if (warp == 9) {
+        // ===== MMA issuer.  The whole warp runs the loop with warp-uniform values; one elected lane issues.
+        if (n_tiles > 0) {
+            const bool leader = elect_one();
+            constexpr uint32_t HI_K = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);   // SBO, version 1, SWIZZLE_128B
+            constexpr uint32_t LBO_K = 1u << 16;
+            constexpr uint32_t LBO_V = (uint32_t)((A2_TN * 128) >> 4) << 16;
+            auto mk = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
+            const uint32_t q_lo = (smem_u32(smem + A2_OFF_Q) >> 4) | LBO_K;
+            const uint32_t kv_lo = smem_u32(smem + A2_OFF_KV) >> 4;
+            int it = 0;                                                     // ring items consumed so far
+            // S(tile) into S buffer sb from the K tile that is ring item `it`
+            auto s_tile = [&](int sb) -> bool {
+                const int slot = it % A2_KV_SLOTS;
+                if (!mbar_wait_sleep_warp(&kv_full[slot], (it / A2_KV_SLOTS) & 1)) return false;
+                tc_fence_after();
+                if (leader) {
+                    const uint32_t b0 = (kv_lo + slot * (A2_KV_SLOT >> 4)) | LBO_K;
+                    #pragma unroll
+                    for (int kk = 0; kk < A2_D / 16; ++kk) {
+                        const uint32_t ao = ((kk >> 2) * (A2_ROWS * 128) + (kk & 3) * 32) >> 4;
+                        const uint32_t bo = ((kk >> 2) * (A2_TN * 128) + (kk & 3) * 32) >> 4;
+                        tc_mma_f16(tmem_base + sb * 128, mk(q_lo + ao, HI_K), mk(b0 + bo, HI_K), ATC_IDESC_S, kk > 0 ? 1u : 0u);
+                    }
+                    tc_commit(&s_full[sb]);
+                    tc_commit(&kv_empty[slot]);
+                }
+                __syncwarp();
+                ++it;
+                return true;
+            };
+            if (!mbar_wait_sleep_warp(q_full, 0)) failed = true;
+            if (!failed && !s_tile(0)) failed = true;
+            if (!failed && n_tiles > 1 && !s_tile(1)) failed = true;
+            for (int j = 0; j < n_tiles && !failed; ++j) {
+                const int sb = j & 1;
+                const int slot = it % A2_KV_SLOTS;                          // V of tile j
+                if (!mbar_wait_warp(&p_full[sb], (j >> 1) & 1) ||
+                    !mbar_wait_sleep_warp(&kv_full[slot], (it / A2_KV_SLOTS) & 1)) { failed = true; break; }
+                tc_fence_after();
+                if (leader) {
+                    const uint32_t b0 = (kv_lo + slot * (A2_KV_SLOT >> 4)) | LBO_V;
+                    #pragma unroll
+                    for (int kk = 0; kk < A2_TN / 16; ++kk)
+                        tc_mma_f16_ts(tmem_base + 256, tmem_base + sb * 128 + 64 + kk * 8, mk(b0 + kk * (2048 >> 4), HI_K), ATC_IDESC_PV,
+                                      (j > 0 || kk > 0) ? 1u : 0u);
+                    tc_commit(pv_done);                                     // O holds tiles 0..j: it may be rescaled or read
+                    tc_commit(&kv_empty[slot]);
+                }
+                __syncwarp();
+                ++it;
+                // S(j+2) goes into the buffer P(j) was read from: the tensor core runs PV(j) first
+                if (j + 2 < n_tiles && !s_tile(sb)) { failed = true; break; }
+            }
+            if (!failed && leader) tc_commit(o_full);
+        }
+    } else if (warp < 8) {
+        // ===== softmax: thread = (row, half of the tile's keys)
+        const int q = warp & 3, h = warp >> 2;
+        const int lr = q * 32 + lane;
+        const int row = r0 + lr;
+        const int qidx = row / G;
+        const bool valid = row < ql * G;
+        const int head = kvh * G + (row - qidx * G);
+        const int lim = valid ? (p.causal ? min(total_k, total_k - ql + qidx + 1) : total_k) : 0;
+        {   // this thread's d block (64 of the 128 dims) of its Q row -> shared memory, K-major 128B-swizzled
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(row_base + qidx) * p.nq + head) * A2_D) + h * 8;
+            uint8_t* qs = smem + A2_OFF_Q + h * (A2_ROWS * 128) + lr * 128;
+            #pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(qs + ((c ^ (lr & 7)) << 4)) = v;
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_full);
+        }
+        float m_used = -INFINITY, m_true = -INFINITY, l_part = 0.f;
+        uint32_t pair_phase = 0;
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        const uint32_t tmem_o = tmem_base + lane_addr + 256 + h * 64;       // this thread's 64 columns of O
+        const float scale = p.scale_log2;
+        // The scores of tile j+1 are requested before P(j) is announced: a TMEM read issued after the issuer has queued
+        // PV(j) and S(j+2) waits behind those 1024 tensor-core cycles (per-tile time 2770 cycles with the read at the top of
+        // the loop).  S(j+1) was issued before PV(j), so waiting for it here cannot hold anything up.
+        float sv[64];
+        auto request_scores = [&](int j) -> bool {
+            const int sb = j & 1;
+            if (!mbar_wait_warp(&s_full[sb], (j >> 1) & 1)) return false;
+            tc_fence_after();
+            float (&lo)[32] = *reinterpret_cast<float (*)[32]>(&sv[0]);
+            float (&hi)[32] = *reinterpret_cast<float (*)[32]>(&sv[32]);
+            tc_ld32(tmem_base + lane_addr + sb * 128 + h * 64, lo);
+            tc_ld32(tmem_base + lane_addr + sb * 128 + h * 64 + 32, hi);
+            return true;
+        };
+        if (n_tiles > 0) {
+            if (!request_scores(0)) failed = true;
+            tc_wait_ld();
+        }
+        for (int j = 0; j < n_tiles && !failed; ++j) {
+            const int sb = j & 1;
+            const uint32_t tmem_s = tmem_base + lane_addr + sb * 128;
+            const int kbase = k_begin + j * A2_TN;
+            const int nvis = min(lim, k_end) - kbase - h * 64;       // keys of this thread's half the row may see (may be <= 0)
+            if (nvis < 64) {
+                #pragma unroll
+                for (int e = 0; e < 64; ++e) sv[e] = e < nvis ? sv[e] : -INFINITY;
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+            #pragma unroll
+            for (int e = 0; e < 64; e += 4) { mx0 = fmax3(mx0, sv[e], sv[e + 1]); mx1 = fmax3(mx1, sv[e + 2], sv[e + 3]); }
+            // row maximum over both halves: the partner is the same lane of warp (warp ^ 4)
+            float* xm = xch + (size_t)sb * 2 * A2_ROWS;
+            xm[h * A2_ROWS + lr] = fmaxf(mx0, mx1);
+            if (!a2_pair_sync(&pair_bar[q], pair_phase, lane)) { failed = true; break; }
+            m_true = fmaxf(m_true, fmaxf(fmaxf(mx0, mx1), xm[(h ^ 1) * A2_ROWS + lr]) * scale);   // raw scores: the scale is positive
+            // lazy reference update, decided identically by both threads of the row
+            const bool move = m_true > m_used + ATC_RESCALE_THRESHOLD || (m_used == -INFINITY && m_true > -INFINITY);
+            const bool rescale = move && m_used != -INFINITY && j > 0;
+            const float corr = rescale ? ex2_approx(m_used - m_true) : 1.0f;
+            if (move) m_used = m_true;
+            const float nref = (m_used == -INFINITY) ? 0.f : -m_used;
+            uint32_t pw[32];
+            float l0 = 0.f, l1 = 0.f;
+            #pragma unroll
+            for (int e = 0; e < 64; e += 2) {
+                const float e0 = ex2_approx(fmaf(sv[e], scale, nref)), e1 = ex2_approx(fmaf(sv[e + 1], scale, nref));
+                l0 += e0; l1 += e1;
+                pw[e >> 1] = pack_h2(e0, e1);
+            }
+            // P over the last 64 columns of the S buffer (column 64 + c = keys 2c, 2c+1).  The partner has read its scores
+            // out of those columns before it reached the pair barrier above.
+            tc_st32u(tmem_s + 64 + h * 32, pw);
+            if (__any_sync(0xffffffffu, rescale)) {
+                // O holds tiles 0..j-1 once PV(j-1) has completed (its commit is completion j-1 of pv_done)
+                if (!mbar_wait_warp(pv_done, (j - 1) & 1)) { failed = true; break; }
+                tc_fence_after();
+                #pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    float part[32];
+                    tc_ld32(tmem_o + c * 32, part);
+                    tc_wait_ld();
+                    #pragma unroll
+                    for (int e = 0; e < 32; ++e) part[e] *= corr;
+                    tc_st32(tmem_o + c * 32, part);
+                }
+            }
+            l_part = l_part * corr + (l0 + l1);
+            // rows of V past the end of the sequence may hold anything (0 * NaN would poison O): cleared before PV reads them
+            if (h == 0 && kbase + A2_TN > k_end) {
+                // V of tile j is ring item 2 + 2j for j < n_tiles - 1 ... the last tile's V is the last item: 2 n_tiles - 1
+                const int itv = 2 * n_tiles - 1, slot = itv % A2_KV_SLOTS;
+                if (!mbar_wait_sleep_warp(&kv_full[slot], (itv / A2_KV_SLOTS) & 1)) { failed = true; break; }
+                uint8_t* vst = smem + A2_OFF_KV + slot * A2_KV_SLOT;
+                const int first_bad = k_end - kbase;                        // 1..127
+                for (int i = lr; i < (A2_TN - first_bad) * 16; i += 128) {
+                    const int key = first_bad + (i >> 4), c = i & 15;
+                    *reinterpret_cast<uint4*>(vst + (c >> 3) * (A2_TN * 128) + key * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+                }
+                fence_proxy_async();
+            }
+            tc_wait_st();
+            const bool more = j + 1 < n_tiles;
+            if (more && !request_scores(j + 1)) { failed = true; break; }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[sb]);
+            if (more) tc_wait_ld();
+        }
+        // ===== epilogue: row sums of the two halves, then O (TMEM) -> output or split-KV partial, this thread's 64 columns
+        failed = __any_sync(0xffffffffu, failed);
+        float l_run = l_part;
+        if (!failed) {
+            float* xl = xch;                                     // the maxima buffers are idle now
+            bool ok = a2_pair_sync(&pair_bar[q], pair_phase, lane);      // both warps are past their last read of them
+            xl[h * A2_ROWS + lr] = l_part;
+            ok = a2_pair_sync(&pair_bar[q], pair_phase, lane) && ok;
+            l_run = l_part + xl[(h ^ 1) * A2_ROWS + lr];
+            if (!ok) failed = true;
+        }
+        if (!failed && n_tiles > 0 && !mbar_wait_sleep_warp(o_full, 0)) failed = true;
+        if (!failed) {
+            tc_fence_after();
+            const float inv = (splits == 1) ? (l_run > 0.f ? 1.0f / l_run : 0.f) : 1.0f;
+            half* orow = p.o + ((size_t)(row_base + qidx) * p.nq + head) * A2_D + h * 64;
+            float* pp = p.partial + (((size_t)item_idx * p.nkv + kvh) * A2_ROWS + lr) * (A2_D + 2);
+            #pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                float ov[32];
+                if (n_tiles > 0) {
+                    tc_ld32(tmem_o + c * 32, ov);
+                    tc_wait_ld();
+                } else {
+                    #pragma unroll
+                    for (int e = 0; e < 32; ++e) ov[e] = 0.f;
+                }
+                if (valid) {
+                    if (splits == 1) {
+                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+                        #pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            dst[e] = make_uint4(pack_h2(ov[e * 8] * inv, ov[e * 8 + 1] * inv), pack_h2(ov[e * 8 + 2] * inv, ov[e * 8 + 3] * inv),
+                                                pack_h2(ov[e * 8 + 4] * inv, ov[e * 8 + 5] * inv), pack_h2(ov[e * 8 + 6] * inv, ov[e * 8 + 7] * inv));
+                    } else {
+                        #pragma unroll
+                        for (int e = 0; e < 32; e += 2) *reinterpret_cast<float2*>(pp + h * 64 + c * 32 + e) = make_float2(ov[e], ov[e + 1]);
+                    }
+                }
+            }
+            if (valid && splits != 1 && h == 0) { pp[A2_D] = m_used; pp[A2_D + 1] = l_run; }
+        }
+    }
+
+    if (failed) s_failed = 1;
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+    if (tid == 0 && s_failed) atomicExch(p.status, 3);
+}
+
+}  // namespace exl3

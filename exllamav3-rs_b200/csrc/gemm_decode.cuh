@@ -7,24 +7,26 @@
 //
 // Layout of the work.  A CTA has 16 warps = 8 k-slices x 2 column halves.  Its unit of work is (128-column block,
 // 512-k chunk); inside a unit warp (ks, ch) owns the 4 x 4 weight tiles of k-slice ks (64 k) and column half ch (64
-// columns).  Units are ordered column-block-major and dealt to the CTAs as contiguous ranges (stream-K), so a warp walks
-// down k with its accumulators in registers and only meets the other warps when the CTA leaves a column block: the 8
-// k-slices are added in a fixed order through shared memory, a block shared with a neighbouring CTA goes through a
-// partial-sum slot in global memory that the last CTA to arrive adds up in owner order (deterministic), and the finisher
-// applies the output Hadamard and svh.
+// columns).  Units are ordered column-block-major and dealt to the CTAs as contiguous ranges: whole column blocks per CTA
+// when that costs at most one unit more than an even split (no traffic between CTAs), else an even split (stream-K).  A
+// warp walks down k with its accumulators in registers and only meets the other warps when the CTA leaves a column
+// block: the 8 k-slices are added in a fixed order through shared memory by the warp that arrives last, a block shared
+// with a neighbouring CTA goes through a partial-sum slot in global memory that the last CTA to arrive adds up in owner
+// order (deterministic), and the finisher applies the output Hadamard and svh.
 //
-// The two warps of a k-slice share a ring of slots; a seventeenth warp is the producer for all eight rings: lane l of it
-// keeps k-slice l's ring full (one TMA box of 4 tile rows x 8 tiles of codes per slot and, for up to 8 rows, one bulk copy
-// of the slot's activations in MMA fragment order, written by gemm_decode_prologue_kernel), signalled through one "full"
-// and one "empty" mbarrier per slot.  A decoder's main loop is: wait, decode and multiply its 16 tiles, release - no
-// CTA-wide barrier and no address arithmetic.
+// The two warps of a k-slice share a ring of slots; one warp of a fifth warpgroup is the producer for all eight rings
+// (setmaxnreg moves that group's registers to the decoders): lane l of it keeps k-slice l's ring full (one TMA box of 4
+// tile rows x 8 tiles of codes per slot and, for up to 8 rows, one bulk copy of the slot's activations in MMA fragment
+// order, written by gemm_decode_prologue_kernel), signalled through one "full" and one "empty" mbarrier per slot.  A
+// decoder's main loop is: wait, decode and multiply its 16 tiles, release - no CTA-wide barrier and no address arithmetic.
 //
 // Multiplier mapping.  The 16x16 tile is stored in mma.m16n8k16 B-fragment order; read as the A operand of the
 // transposed product (weights^T . activations^T) the same registers are one A fragment, so a tile costs two MMAs for
 // up to 8 rows (N = 8 is the batch) instead of four.  For codebooks 0/1 a weight is the fp16 sum of the two halves of
 // y = lop3(x * C); y goes to the tensor core as two consecutive k entries and the activation is duplicated in the B
 // fragment, so the halves are added by the MMA in fp32; codebook 2 uses (1024 + s, -1534) the same way and is scaled
-// in the epilogue.  Per tile and lane at 4 bpw: 2 shared loads, 3 shifts, 8 byte permutes, 8 multiplies, 8 lop3, 2 MMAs.
+// in the epilogue.  Measured per tile at 4 bpw (MCG codebook, 1 row): 38.6 warp instructions, of which 18.9 on the ALU pipe
+// (shifts, permutes, lop3), 4.9 integer multiplies, 2.3 shared loads and 2 MMAs.
 #pragma once
 #include <cuda.h>
 #include "common.cuh"

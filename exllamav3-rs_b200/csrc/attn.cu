@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
     long long local = 0;
     for (int b = tid; b < bsz; b += 1024) {
         const int ql = cu_q ? cu_q[b + 1] - cu_q[b] : q_len;
-        const int tk = seqlens[b] + (cu_q ? ql : kv_append);
+        const int tk = (seqlens ? seqlens[b] : 0) + (cu_q ? ql : kv_append);
         const int pr = ql * G;
         const int rb = (pr > rows_lo && pr <= rows_hi) ? (pr + rows_per_cta - 1) / rows_per_cta : 0;
         local += (long long)tk * rb;
@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
         int ql = 0, tk = 0, rb = 0, sp = 0;
         if (b < bsz) {
             ql = cu_q ? cu_q[b + 1] - cu_q[b] : q_len;
-            tk = seqlens[b] + (cu_q ? ql : kv_append);
+            tk = (seqlens ? seqlens[b] : 0) + (cu_q ? ql : kv_append);
             const int pr = ql * G;
             rb = (pr > rows_lo && pr <= rows_hi) ? (pr + rows_per_cta - 1) / rows_per_cta : 0;
             sp = (rb > 0 && tk > 0) ? (tk + chunk - 1) / chunk : 1;
@@ -287,7 +287,7 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     // (its row maximum is taken on the raw scores, which needs a positive scale)
     // (sequences with 17..128 packed rows - speculative verify - stay on it too: on 32 sequences x 8 query rows x 5 heads
     // the 64-row mma.sync kernel measured 228 us against 224 us, at 16 and 24 query rows 373 / 383 us against 233 / 241 us)
-    const bool use_tc = !decode_shape && !quant && ctx->mma_attn != 0 && p.scale_log2 > 0.f;
+    const bool use_tc = !decode_shape && !quant && ctx->mma_attn != 0 && p.scale_log2 > 0.f && !p.contig_kv;
     // two arrangements of the tcgen05 kernel: 128-row items with two softmax threads per row (default), 256-row items
     static const bool tc_256 = getenv("EXL3_B200_ATTN_TC256") != nullptr;
     const int rows_per_cta = decode_shape ? 16 : (use_tc ? (tc_256 ? ATC_CTA_ROWS : A2_ROWS) : 64);
@@ -477,4 +477,38 @@ extern "C" int exl3_bighead_attn_paged_q(exl3_ctx* ctx, exl3_stream stream, cons
     p.scale_log2 = (sm_scale == 0.0f ? rsqrtf((float)hd) : sm_scale) * 1.4426950408889634f;
     const int total_rows = cu_q ? kv_append : bsz * q_len;
     return attn_impl(ctx, (cudaStream_t)stream, p, total_rows, q_len, true);
+}
+
+// Attention over plain tensors: q, o [bsz, q_len, nq, hd], k, v [bsz, kv_len, nkv, hd], no cache and no block table
+// (kernels/attention.cu:2292-2437).  A causal query i sees keys <= kv_len - q_len + i (:1476).  Runs the mma.sync kernels
+// with the key index taken straight from the sequence's base; kv_chunk_size is accepted and ignored (the split size comes
+// from the work list).
+extern "C" int exl3_bighead_attn(exl3_ctx* ctx, exl3_stream stream, const void* q, const void* k, const void* v, void* o,
+                                 int bsz, int q_len, int kv_len, int nq, int nkv, int hd, int kv_chunk_size, int causal,
+                                 float sm_scale)
+{
+    EXL3_REQUIRE(ctx && q && k && v && o, "attention: null argument");
+    EXL3_REQUIRE(bsz >= 0 && q_len >= 0 && kv_len >= 0 && nq > 0 && nkv > 0, "attention: bad shape");
+    EXL3_REQUIRE(kv_chunk_size > 0, "attention: kv_chunk_size must be positive");
+    EXL3_REQUIRE(nq % nkv == 0, "attention: n_q_heads must be a multiple of n_kv_heads");
+    EXL3_REQUIRE(nq / nkv <= 16, "attention: GQA ratio above 16");
+    if (hd != 128) return exl3_fail(ctx, EXL3_ERR_UNSUPPORTED, "attention: head_dim must be 128");
+    EXL3_REQUIRE(nkv <= 65535, "attention: too many kv heads");
+    EXL3_REQUIRE(aligned16(q) && aligned16(o) && aligned16(k) && aligned16(v), "attention: pointers must be 16-byte aligned");
+    if (bsz == 0 || q_len == 0) return EXL3_OK;
+    if (kv_len == 0)                                      // nothing to attend to: the reference writes zeros (l = 0)
+        return cudaMemsetAsync(o, 0, (size_t)bsz * q_len * nq * hd * 2, (cudaStream_t)stream) == cudaSuccess
+                   ? EXL3_OK : exl3_fail(ctx, EXL3_ERR_CUDA, "attention: cudaMemsetAsync failed");
+    AttnParams p;
+    memset(&p, 0, sizeof(p));
+    p.q = (const half*)q; p.o = (half*)o; p.kc = (const half*)k; p.vc = (const half*)v;
+    p.bsz = bsz; p.q_len = q_len; p.kv_append = kv_len; p.contig_kv = kv_len; p.nq = nq; p.nkv = nkv; p.pps = 1; p.pages = 1;
+    p.causal = causal;
+    p.scale_log2 = (sm_scale == 0.0f ? rsqrtf((float)hd) : sm_scale) * 1.4426950408889634f;
+    // the work lists kept across the layers of a step belong to the paged batch: plan afresh
+    const int keep = ctx->plan_keep;
+    ctx->plan_keep = 0;
+    const int rc = attn_impl(ctx, (cudaStream_t)stream, p, bsz * q_len, q_len, false);
+    ctx->plan_keep = keep;
+    return rc;
 }

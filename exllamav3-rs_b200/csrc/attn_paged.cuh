@@ -32,7 +32,7 @@ struct AttnParams {
     const uint32_t* qk; const half* sk;        // quantised pools (QUANT): [pages,256,groups*bits], [pages,256,groups]
     const uint32_t* qv; const half* sv;
     const int32_t* block_table;    // [bsz, pps]
-    const int32_t* seqlens;        // [bsz]  tokens in the cache BEFORE this step's append
+    const int32_t* seqlens;        // [bsz]  tokens in the cache BEFORE this step's append (NULL: none, all keys are "appended")
     const int32_t* cu_q;           // [bsz+1] or NULL (then rows of sequence b = [b*q_len, (b+1)*q_len))
     const AttnPlan* plan;
     const AttnItem* items;
@@ -41,6 +41,7 @@ struct AttnParams {
     float* partial;                // [n_items][nkv][ROWS][D+2]
     int* status;                   // context status word (bounded waits)
     int bsz, q_len, kv_append, nq, nkv, pps, pages, causal, k_bits, v_bits;
+    int contig_kv;                 // > 0: kc/vc are plain [bsz, contig_kv, nkv, D] tensors, no block table (mma.sync fp16 kernel only)
     float scale_log2;              // sm_scale * log2(e)
 };
 
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(AT_THREADS, (QB == 4 && WN == 4) ? AT_Q4_DECOD
         const int b = item.b;
         const int row_base = p.cu_q ? p.cu_q[b] : b * p.q_len;
         const int ql = p.cu_q ? p.cu_q[b + 1] - row_base : p.q_len;
-        const int total_k = p.seqlens[b] + (p.cu_q ? ql : p.kv_append);
+        const int total_k = (p.seqlens ? p.seqlens[b] : 0) + (p.cu_q ? ql : p.kv_append);
         const int splits = p.seq_splits[b];
         const int r0 = item.rb * ROWS;                       // first packed (query, head) row of this CTA
         // keys this row block can see at all (causal, bottom-right aligned)
@@ -139,7 +140,7 @@ __global__ void __launch_bounds__(AT_THREADS, (QB == 4 && WN == 4) ? AT_Q4_DECOD
         const int vis_max = p.causal ? min(total_k, total_k - ql + i_last + 1) : total_k;
         const int k_begin = item.split * chunk;
         const int k_end = min(min(k_begin + chunk, total_k), vis_max);
-        const int32_t* bt = p.block_table + (size_t)b * p.pps;
+        const int32_t* bt = p.block_table + (size_t)b * p.pps;      // not dereferenced for plain tensors
 
         // ---- per-thread row bookkeeping: rows g and g+8 of this warp's 16-row tile
         int qi[2], lim[2];      // query index and last visible key (exclusive) per row
@@ -209,7 +210,7 @@ __global__ void __launch_bounds__(AT_THREADS, (QB == 4 && WN == 4) ? AT_Q4_DECOD
                 // lookup per tile.  Thread layout: 16-byte chunk tid % 16 of keys tid / 16 + 8 i (D = 128: 16 chunks per
                 // key row).  Keys past the end of the split repeat the last valid key (masked later).
                 static_assert(D == 128, "loader assumes 16 chunks per key row");
-                const size_t tok0 = (size_t)bt[k0 >> 8] * EXL3_PAGE + (k0 & 255);
+                const size_t tok0 = p.contig_kv ? (size_t)b * p.contig_kv + k0 : (size_t)bt[k0 >> 8] * EXL3_PAGE + (k0 & 255);
                 const int kmax = k_end - 1 - k0;
                 const int ch = tid & 15, key0 = tid >> 4;
                 const size_t rstride = (size_t)p.nkv * D;

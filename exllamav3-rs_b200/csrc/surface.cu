@@ -95,10 +95,6 @@ extern "C" int exl3_relu2_mul(exl3_ctx* ctx, exl3_stream stream, const void* x, 
 
 // ---- exported, not built
 
-extern "C" int exl3_bighead_attn(exl3_ctx* ctx, exl3_stream, const void*, const void*, const void*, void*, int, int, int, int, int, int,
-                                 int, int, float)
-{ return not_built(ctx, "bighead_attn (attention over an unpaged KV tensor)"); }
-
 extern "C" int exl3_gated_rms_norm(exl3_ctx* ctx, exl3_stream, const void*, const void*, void*, const void*, float, float, int, int, int,
                                    int, int)
 { return not_built(ctx, "gated_rms_norm"); }

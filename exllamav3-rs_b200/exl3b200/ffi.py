@@ -389,6 +389,18 @@ class Ctx:
                                                  _ptr(o), bsz, q_len, kv_append, nq, nkv, hd, k_cache.shape[0], pps,
                                                  kv_chunk_size, int(causal), C.c_float(sm_scale)), "bighead_attn_paged")
 
+    def bighead_attn(self, q, k, v, o, causal=True, sm_scale=0.0, kv_chunk_size=256, stream=None):
+        """src/ffi.rs:458-460: attention over plain tensors q, o [bsz,q_len,nq,hd], k, v [bsz,kv_len,nkv,hd]."""
+        _chk(q, torch.float16, "q"); _chk(k, torch.float16, "k"); _chk(v, torch.float16, "v"); _chk(o, torch.float16, "o")
+        if q.dim() != 4 or k.dim() != 4 or v.dim() != 4 or o.dim() != 4:
+            raise ValueError("bighead_attn: q, k, v, o must be rank-4")
+        bsz, q_len, nq, hd = q.shape
+        if k.shape[0] != bsz or v.shape != k.shape or k.shape[3] != hd or o.shape != q.shape:
+            raise ValueError("bighead_attn: shape mismatch")
+        self.check(lib().exl3_bighead_attn(self._h, self.stream(stream), _ptr(q), _ptr(k), _ptr(v), _ptr(o), bsz, q_len,
+                                           k.shape[1], nq, k.shape[2], hd, kv_chunk_size, int(causal),
+                                           C.c_float(sm_scale)), "bighead_attn")
+
     def bighead_attn_paged_q(self, q, k, v, qk, sk, qv, sv, block_table, cache_seqlens, o, nkv, kv_chunk_size=256,
                              causal=True, sm_scale=0.0, compand_a=0.0, cu_q=None, max_q_len=None, stream=None):
         """src/ffi.rs:383-401 against the quantised pools (qk/qv int32 [pages,256,groups*bits], sk/sv fp16)."""

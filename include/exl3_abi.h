@@ -397,7 +397,9 @@ EXL3_API int exl3_mgemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const 
                         const void* const* suh, void* A_had, const void* const* svh, const int64_t* indices,
                         const void* weights, int bszm_in, int bszm_out, int m, int k, int n, int K, int c_fp32, int mcg,
                         int mul1, int num_tokens);
-/* exl3_shim_bighead_attn (src/ffi.rs:67-75 -> kernels/attention.cu): attention over an unpaged K/V [bsz,kv_len,nkv,hd].  Not built. */
+/* exl3_shim_bighead_attn (src/ffi.rs:67-75 -> kernels/attention.cu:2292-2437): attention over plain tensors, q and o
+ * [bsz,q_len,nq,hd], k and v [bsz,kv_len,nkv,hd], fp16; a causal query i sees keys <= kv_len - q_len + i.  hd = 128 only
+ * (UNSUPPORTED otherwise); kv_chunk_size must be positive and is otherwise ignored; sm_scale 0 = 1/sqrt(hd). */
 EXL3_API int exl3_bighead_attn(exl3_ctx* ctx, exl3_stream stream, const void* q, const void* k, const void* v, void* o, int bsz,
                                int q_len, int kv_len, int nq, int nkv, int hd, int kv_chunk_size, int causal, float sm_scale);
 /* exl3_shim_gated_rms_norm (src/ffi.rs:118-122).  Not built. */

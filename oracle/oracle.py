@@ -410,6 +410,21 @@ def dequant_cache_paged(qk, sk, k_out, qv, sv, v_out, seqlens, block_table, k_bi
                                   C.c_int(v_bits), C.c_int(compact), C.c_int(bonus))
 
 
+def attn_plain(q, k, v, causal=True, sm_scale=0.0):
+    """Attention over plain tensors q [bsz,q_len,nq,hd], k, v [bsz,kv_len,nkv,hd] (kernels/attention.cu:2292-2437; causal
+    limit kv_len - q_len + i, :1476).  Restated through the paged form: every sequence's keys laid into pages of its own,
+    all of them already in the cache."""
+    q, k, v = _c(q, np.float16), _c(k, np.float16), _c(v, np.float16)
+    bsz, kv_len, nkv, hd = k.shape
+    pps = max(1, (kv_len + 255) // 256)
+    kc = np.zeros((bsz * pps, 256, nkv, hd), np.float16)
+    vc = np.zeros_like(kc)
+    kc.reshape(bsz, pps * 256, nkv, hd)[:, :kv_len] = k
+    vc.reshape(bsz, pps * 256, nkv, hd)[:, :kv_len] = v
+    bt = np.arange(bsz * pps, dtype=np.int32).reshape(bsz, pps)
+    return attn_paged(q, kc, vc, bt, np.full(bsz, kv_len, np.int32), kv_append=0, causal=causal, sm_scale=sm_scale)
+
+
 def attn_paged(q, kc, vc, block_table, seqlens, kv_append=None, causal=True, sm_scale=0.0, cu_q=None, nkv=None,
                quant=None):
     """Rectangular: q [bsz,q_len,nq,hd].  Ragged: q [rows,nq,hd] with cu_q [bsz+1].

@@ -168,6 +168,16 @@ int ref_bighead_attn_paged(const void* q, const void* k, const void* v, void* kc
     });
 }
 
+int ref_bighead_attn(const void* q, const void* k, const void* v, void* o, int bsz, int q_len, int kv_len, int nq, int nkv,
+                     int hd, int kv_chunk, int causal, float sm_scale)
+{
+    return guarded([&] {
+        bighead_attn(wrap(q, {bsz, q_len, nq, hd}, at::kHalf), wrap(k, {bsz, kv_len, nkv, hd}, at::kHalf),
+                     wrap(v, {bsz, kv_len, nkv, hd}, at::kHalf), wrap(o, {bsz, q_len, nq, hd}, at::kHalf), kv_chunk,
+                     causal != 0, sm_scale);
+    });
+}
+
 int ref_bighead_attn_paged_q(const void* q, const void* k, const void* v, void* qk, void* sk, void* qv, void* sv,
                              const void* bt, const void* seqlens, void* o, int bsz, int q_len, int kv_append, int nq,
                              int nkv, int hd, int pages, int pps, int k_bits, int v_bits, int kv_chunk, int causal,

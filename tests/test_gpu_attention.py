@@ -241,3 +241,45 @@ def test_attention_reference_check_shapes(ctx, ref, q_len, ctx_len, nq, nkv):
         e_ref = _close(got, rgot, TOL_FP16, 2)
         e_rr = _close(rgot, want, TOL_FP16, 2)
     assert e_or <= max(1.0, 1.1 * e_rr) and e_ref <= 1.25, (e_or, e_ref, e_rr)
+
+
+@pytest.mark.parametrize("bsz,q_len,kv_len,nq,nkv,causal", [
+    (2, 1, 777, 16, 8, True),        # decode-like: one query over an odd-length key tensor (tiles end mid-way, no page padding)
+    (3, 8, 1000, 40, 8, True),       # a few query rows, G = 5
+    (2, 200, 200, 16, 8, True),      # self-attention of a prompt, causal
+    (2, 200, 200, 16, 8, False),     # the same without the mask (vision-tower use)
+    (1, 70, 3001, 16, 16, True),     # G = 1, keys beyond one split
+    (2, 5, 3, 16, 8, True),          # fewer keys than queries: the first rows see nothing and come out zero
+])
+def test_attention_plain_tensors(ctx, ref, bsz, q_len, kv_len, nq, nkv, causal):
+    """exl3_bighead_attn (no cache, no block table) against the oracle and the compiled reference op"""
+    torch = _torch()
+    from oracle import oracle as O
+    r = H.rng(5150 + q_len + kv_len)
+    q = r.standard_normal((bsz, q_len, nq, 128)).astype(np.float16)
+    k = (0.5 * r.standard_normal((bsz, kv_len, nkv, 128))).astype(np.float16)
+    v = (0.5 * r.standard_normal((bsz, kv_len, nkv, 128))).astype(np.float16)
+    dq, dk, dv = H.to_dev(q), H.to_dev(k), H.to_dev(v)
+    o = torch.full(q.shape, float("nan"), dtype=torch.float16, device="cuda")
+    ctx.bighead_attn(dq, dk, dv, o, causal=causal)
+    ctx.poll_status()
+    got = o.cpu().numpy()
+    want = O.attn_plain(q, k, v, causal=causal)
+    assert np.isfinite(got).all()
+    steps = 1 if q_len == 1 else 2
+    assert _close(got, want, TOL_FP16, steps) <= 1.0
+    if ref is not None and kv_len >= q_len:
+        o2 = torch.zeros(q.shape, dtype=torch.float16, device="cuda")
+        assert ref.ref_bighead_attn(H.ptr(dq), H.ptr(dk), H.ptr(dv), H.ptr(o2), bsz, q_len, kv_len, nq, nkv, 128, 256,
+                                    int(causal), C.c_float(0.0)) == 0
+        torch.cuda.synchronize()
+        assert _close(got, o2.cpu().numpy(), TOL_FP16, steps) <= 1.0
+
+
+def test_attention_plain_tensors_rejects(ctx):
+    torch = _torch()
+    q = torch.zeros((1, 1, 8, 64), dtype=torch.float16, device="cuda")
+    k = torch.zeros((1, 4, 8, 64), dtype=torch.float16, device="cuda")
+    with pytest.raises(Exception):
+        ctx.bighead_attn(q, k, k, torch.empty_like(q))                 # head_dim 64: unsupported, reported, nothing launched
+    ctx.poll_status()

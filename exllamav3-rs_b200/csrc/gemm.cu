@@ -289,12 +289,12 @@ EncodeTiledFn get_encode_tiled()
 
 constexpr int TC_MAX_SMALL_M = 0;           // row counts up to this stay on the mma.sync small-M kernel (0: none do)
 
-template <int K, int CB, int CTAS>
+template <int K, int CB, int CTAS, int BN>
 cudaError_t launch_tc(const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
-    constexpr int bytes = TcSmem<K, CTAS>::BYTES;
+    constexpr int bytes = TcSmem<K, CTAS, BN>::BYTES;
     static bool configured[64] = {};
-    auto kern = gemm_tc_kernel<K, CB, CTAS>;
+    auto kern = gemm_tc_kernel<K, CB, CTAS, BN>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -316,30 +316,31 @@ cudaError_t launch_tc(const CUtensorMap* amap, const CUtensorMap* rmap, const Ge
 }
 
 template <int K, int CB>
-cudaError_t launch_tc_ctas(bool pair, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc_ctas(bool pair, int bn, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
-    return pair ? launch_tc<K, CB, 2>(amap, rmap, p, slabs, st) : launch_tc<K, CB, 1>(amap, rmap, p, slabs, st);
+    if (pair && bn == 128) return launch_tc<K, CB, 2, 128>(amap, rmap, p, slabs, st);
+    return pair ? launch_tc<K, CB, 2, 256>(amap, rmap, p, slabs, st) : launch_tc<K, CB, 1, 256>(amap, rmap, p, slabs, st);
 }
 
 template <int K>
-cudaError_t launch_tc_cb(int cb, bool pair, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc_cb(int cb, bool pair, int bn, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
-    if (cb == 0) return launch_tc_ctas<K, 0>(pair, amap, rmap, p, slabs, st);
-    if (cb == 1) return launch_tc_ctas<K, 1>(pair, amap, rmap, p, slabs, st);
-    return launch_tc_ctas<K, 2>(pair, amap, rmap, p, slabs, st);
+    if (cb == 0) return launch_tc_ctas<K, 0>(pair, bn, amap, rmap, p, slabs, st);
+    if (cb == 1) return launch_tc_ctas<K, 1>(pair, bn, amap, rmap, p, slabs, st);
+    return launch_tc_ctas<K, 2>(pair, bn, amap, rmap, p, slabs, st);
 }
 
-cudaError_t launch_tc_k(int K, int cb, bool pair, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc_k(int K, int cb, bool pair, int bn, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
     switch (K) {
-        case 1: return launch_tc_cb<1>(cb, pair, amap, rmap, p, slabs, st);
-        case 2: return launch_tc_cb<2>(cb, pair, amap, rmap, p, slabs, st);
-        case 3: return launch_tc_cb<3>(cb, pair, amap, rmap, p, slabs, st);
-        case 4: return launch_tc_cb<4>(cb, pair, amap, rmap, p, slabs, st);
-        case 5: return launch_tc_cb<5>(cb, pair, amap, rmap, p, slabs, st);
-        case 6: return launch_tc_cb<6>(cb, pair, amap, rmap, p, slabs, st);
-        case 7: return launch_tc_cb<7>(cb, pair, amap, rmap, p, slabs, st);
-        default: return launch_tc_cb<8>(cb, pair, amap, rmap, p, slabs, st);
+        case 1: return launch_tc_cb<1>(cb, pair, bn, amap, rmap, p, slabs, st);
+        case 2: return launch_tc_cb<2>(cb, pair, bn, amap, rmap, p, slabs, st);
+        case 3: return launch_tc_cb<3>(cb, pair, bn, amap, rmap, p, slabs, st);
+        case 4: return launch_tc_cb<4>(cb, pair, bn, amap, rmap, p, slabs, st);
+        case 5: return launch_tc_cb<5>(cb, pair, bn, amap, rmap, p, slabs, st);
+        case 6: return launch_tc_cb<6>(cb, pair, bn, amap, rmap, p, slabs, st);
+        case 7: return launch_tc_cb<7>(cb, pair, bn, amap, rmap, p, slabs, st);
+        default: return launch_tc_cb<8>(cb, pair, bn, amap, rmap, p, slabs, st);
     }
 }
 
@@ -355,6 +356,13 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
     CUtensorMap amap[TC_MAX_SEG], rmap[TC_MAX_SEG];
     GemmTcParams p;
     memset(&p, 0, sizeof(p));
+    // Slab width: 256 columns, or 128 when a single row block would put 256-column slabs on at most a quarter of the SMs
+    // (q/k/v and o_proj of a verify batch: 28 and 20 slabs): the decode work, which bounds these launches, then runs on
+    // twice as many SMs.
+    int blocks256 = 0;
+    bool n128 = true;
+    for (int i = 0; i < nseg; ++i) { blocks256 += (n[i] + TC_BN - 1) / TC_BN; n128 = n128 && n[i] % 128 == 0; }
+    const int bn = (ctx->use_pair && n128 && m <= 2 * TC_BM && blocks256 * 4 <= ctx->num_sms) ? 128 : TC_BN;
     int blocks = 0;
     for (int i = 0; i < TC_MAX_SEG; ++i) {
         const int j = i < nseg ? i : nseg - 1;              // unused slots repeat the last tensor (never selected)
@@ -362,7 +370,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
             pa.a_had[i] = (half*)exl3_ws_take(ctx, &off, (size_t)m * k * 2);
             if (!pa.a_had[i]) return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "exl3_gemm: context scratch too small for the activations");
             pa.suh[i] = suh[i];
-            blocks += (n[i] + TC_BN - 1) / TC_BN;          // a trailing 128-column half slab counts (CTA pairs only)
+            blocks += (n[i] + bn - 1) / bn;                // a trailing 128-column half slab counts (CTA pairs only)
             cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
             cuuint64_t strides[1] = {(cuuint64_t)k * 2};
             cuuint32_t box[2] = {(cuuint32_t)TC_BK, 128u};
@@ -375,7 +383,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
             // half slab (4 tile rows x 8 tiles x 32K bytes) as one box
             cuuint64_t rdims[2] = {(cuuint64_t)(n[i] / 16) * 4 * K, (cuuint64_t)(k / 16)};
             cuuint64_t rstrides[1] = {(cuuint64_t)(n[i] / 16) * 32 * K};
-            cuuint32_t rbox[2] = {(cuuint32_t)(TC_BN / 2 / 16) * 4 * K, (cuuint32_t)(TC_BK / 16)};
+            cuuint32_t rbox[2] = {(cuuint32_t)(bn / 2 / 16) * 4 * K, (cuuint32_t)(TC_BK / 16)};
             r = enc(&rmap[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(trellis[i]), rdims, rstrides, rbox, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -395,7 +403,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
         gemm_prologue_plain_kernel<<<dim3(m, nseg), 256, 0, st>>>(A, pa, k);
     ctx->launches++;
     p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
-    cudaError_t e = launch_tc_k(K, cb, ctx->use_pair != 0, amap, rmap, p, blocks, st);
+    cudaError_t e = launch_tc_k(K, cb, ctx->use_pair != 0, bn, amap, rmap, p, blocks, st);
     ctx->launches++;
     if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
     return EXL3_OK;
@@ -547,22 +555,9 @@ extern "C" int exl3_gemm(exl3_ctx* ctx, exl3_stream stream, const void* A, const
         const half* suh1 = (const half*)suh; const half* svh1 = (const half*)svh;
         return gemm_decode_rows(ctx, st, (const half*)A, 1, &trellis, &C, &suh1, &svh1, &n, m, k, K, c_fp32, cb);
     }
-    // 17..32 rows on a tensor with few column slabs: the tcgen05 grid would be one CTA pair per 256-column slab, i.e. 20 of
-    // the 74 pair slots for n = 5120, each walking all of k at the decoders' pace (17408 x 5120: about 125 us), while the
-    // streaming kernel spreads (column block, k chunk) units over every SM.  Measured at 4 bpw: 17408 x 5120 takes 110 us in
-    // two passes against 126 us (92 us at 20 rows), but 5120 x 5120 takes 65 us against 44 us: the slab walk is short
-    // there.  So: few slabs and a long reduction dimension.
-    if (m <= 2 * GD_MAX_M && ctx->use_decode && (n + TC_BN - 1) / TC_BN <= ctx->num_sms / 4 && k >= 12288) {
-        const half* suh1 = (const half*)suh; const half* svh1 = (const half*)svh;
-        for (int r0 = 0; r0 < m; r0 += GD_MAX_M) {
-            const int rows = m - r0 < GD_MAX_M ? m - r0 : GD_MAX_M;
-            const void* a1 = (const half*)A + (size_t)r0 * k;
-            void* c1 = c_fp32 ? (void*)((float*)C + (size_t)r0 * n) : (void*)((half*)C + (size_t)r0 * n);
-            const int rc = gemm_decode_rows(ctx, st, (const half*)a1, 1, &trellis, &c1, &suh1, &svh1, &n, rows, k, K, c_fp32, cb);
-            if (rc != EXL3_OK) return rc;
-        }
-        return EXL3_OK;
-    }
+    // (17..32 rows on a tensor with few column slabs and a long reduction dimension, 17408 x 5120, used to run as two
+    // 16-row passes of the streaming kernel: 100 us against 126 us on 256-column slabs.  With 128-column slabs the
+    // tcgen05 kernel takes 80 us, so every row count above 16 goes there.)
     int tc_rows = 0;
     if (m > TC_MAX_SMALL_M && (n % TC_BN == 0 || ctx->use_pair) && ctx->use_tc) {
         tc_rows = m;

@@ -119,23 +119,6 @@ __device__ __forceinline__ void gd_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// The 8 states of a lane at 4 bpw with the two nibble shifts written as multiplies, which the FMA pipe executes; the
-// permutes and the logic op of the codebook are what keeps the ALU pipe busy.
-__device__ __forceinline__ void lane_states4(const uint32_t* __restrict__ tile, int lane, int lane_prev, uint32_t (&st)[8])
-{
-    const uint32_t b = tile[lane], a = tile[lane_prev];
-    const uint32_t c = __funnelshift_r(b, a, 16);
-    const uint32_t bl = b * 16u, cl = c * 16u;
-    st[7] = __byte_perm(b, 0, 0x4410);
-    st[6] = __byte_perm(bl, 0, 0x4421);
-    st[5] = __byte_perm(b, 0, 0x4421);
-    st[4] = __byte_perm(bl, 0, 0x4432);
-    st[3] = __byte_perm(b, 0, 0x4432);
-    st[2] = __byte_perm(cl, 0, 0x4421);
-    st[1] = __byte_perm(c, 0, 0x4421);
-    st[0] = __byte_perm(cl, 0, 0x4432);
-}
-
 // One slot = 4 tile rows x 4 tiles of one warp: decode and multiply.
 template <int K, int CB, int MT>
 __device__ __forceinline__ void gd_slot(const uint32_t* __restrict__ sb, int ch, int lane, int lane_prev, uint4 (&af)[MT][GD_SLOT_ROWS],

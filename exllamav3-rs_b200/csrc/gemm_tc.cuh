@@ -30,10 +30,10 @@ constexpr int TC_A_TILE = 128 * TC_BK * 2;               // one 128-row activati
 constexpr int TC_A_STAGE = 2 * TC_A_TILE;                // 32 KB
 constexpr float TC_R128 = 0.088388347648f;
 
-template <int K, int CTAS> struct TcSmem {
+template <int K, int CTAS, int BN = 256> struct TcSmem {
     static constexpr int SA = CTAS == 2 ? 4 : 3;         // stages: activations,
     static constexpr int SB = CTAS == 2 ? 4 : 2;         //         decoded weights,
-    static constexpr int NB = TC_BN / CTAS;              // columns this CTA decodes
+    static constexpr int NB = BN / CTAS;                 // columns this CTA decodes
     static constexpr int B_STAGE = NB * TC_BK * 2;
     static constexpr int RAW_ROW = (NB / 16) * 32 * K;   // one tile row of codes: NB/16 tiles x 32K bytes
     static constexpr int RAW_STAGE = (TC_BK / 16) * RAW_ROW;
@@ -45,7 +45,7 @@ template <int K, int CTAS> struct TcSmem {
     static constexpr int OFF_B = OFF_A + SA * TC_A_STAGE;
     static constexpr int OFF_RAW = OFF_B + SB * B_STAGE;
     static constexpr int OFF_SVH = OFF_RAW + SR * RAW_STAGE;
-    static constexpr int OFF_BAR = OFF_SVH + TC_BN * 2;
+    static constexpr int OFF_BAR = OFF_SVH + BN * 2;
     static constexpr int N_BARS = 4 * SA + 2 * SR + 2 * SB + 2;      // the A ring has 2 * SA slots for one-tile blocks
     static constexpr int OFF_TMEM = OFF_BAR + N_BARS * 8;
     static constexpr int BYTES = OFF_TMEM + 16 + 1024;      // + slack to align the base to 1024 bytes
@@ -194,9 +194,24 @@ __device__ __forceinline__ uint64_t tc_smem_desc(const void* p)
 }
 
 // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 128 (one CTA) or 256 (a CTA pair)
-constexpr uint32_t TC_IDESC = (1u << 4) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-constexpr uint32_t TC_IDESC_PAIR = (1u << 4) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+constexpr uint32_t tc_idesc(int n, int m) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24); }
 
+
+// Exact fp16 weights of two states, as decode_pair, with one ALU-pipe instruction less: the two halves of each raw
+// register are added with half-selecting operands (both halves of the result hold the weight) and one permute merges the
+// two sums, instead of two permutes and one packed add (256-row GEMM at 5120 x 17408: 51.4 -> 48.6 us).
+template <int CB>
+__device__ __forceinline__ half2 tc_decode_pair(uint32_t s0, uint32_t s1)
+{
+    if constexpr (CB == 2) return decode_pair<CB>(s0, s1);
+    else {
+        const uint32_t y0 = decode_raw<CB>(s0), y1 = decode_raw<CB>(s1);
+        const half2 a = *reinterpret_cast<const half2*>(&y0), b = *reinterpret_cast<const half2*>(&y1);
+        const half2 w0 = __hadd2(__low2half2(a), __high2half2(a));
+        const half2 w1 = __hadd2(__low2half2(b), __high2half2(b));
+        return __lows2half2(w0, w1);
+    }
+}
 
 // in-register unnormalised 32-point Walsh-Hadamard transform (Sylvester order)
 __device__ __forceinline__ void fwht32(float (&v)[32])
@@ -214,7 +229,9 @@ __device__ __forceinline__ void fwht32(float (&v)[32])
 
 // CTAS = 1: grid (slabs, ceil(m / 256)).  CTAS = 2: grid (2 * slabs, ceil(m / 512)), cluster (2,1,1).
 // The activations come through `amap*` (A_had [m][k] fp16, box 64 x 128, 128-byte swizzle), one map per weight tensor.
-template <int K, int CB, int CTAS>
+// BN = columns per slab: 256, or 128 (pair form only) for launches whose 256-column slabs would leave most SMs without
+// work (one row block, at most a quarter as many slabs as SMs): the decode work of a tensor then spreads over twice the CTAs.
+template <int K, int CB, int CTAS, int BN = 256>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap amap0,
                                                                const __grid_constant__ CUtensorMap amap1,
                                                                const __grid_constant__ CUtensorMap amap2,
@@ -222,8 +239,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                                                                const __grid_constant__ CUtensorMap rmap1,
                                                                const __grid_constant__ CUtensorMap rmap2, const GemmTcParams p)
 {
-    using SM = TcSmem<K, CTAS>;
+    using SM = TcSmem<K, CTAS, BN>;
     constexpr bool PAIR = CTAS == 2;
+    constexpr uint32_t IDESC = tc_idesc(BN, 128 * CTAS);
     constexpr int NT = SM::NB / 16;                       // tile columns this CTA decodes (16 or 8)
     extern __shared__ uint8_t smem_unaligned[];
     // aligned to 1024 bytes by an offset from the array, not through an integer, so that the compiler still knows the
@@ -241,7 +259,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     const int rank = PAIR ? (int)cluster_ctarank() : 0;                  // 0 = leader of the pair
     const int slab = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int seg = (slab >= p.blk_end[0]) + (slab >= p.blk_end[1]);
-    const int n0 = (slab - (seg == 0 ? 0 : (seg == 1 ? p.blk_end[0] : p.blk_end[1]))) * TC_BN;     // first column of the slab
+    const int n0 = (slab - (seg == 0 ? 0 : (seg == 1 ? p.blk_end[0] : p.blk_end[1]))) * BN;     // first column of the slab
     const int nd0 = n0 + rank * SM::NB;                                  // first column this CTA decodes
     const int m0 = blockIdx.y * (TC_BM * CTAS);
     const int row_t0 = m0 + rank * 128, row_t1 = row_t0 + 128 * CTAS;    // first rows of this CTA's two M tiles
@@ -280,7 +298,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     }
     // (the last slab of a tensor with n % 256 == 128 has one valid half: its other half decodes zero-filled codes into
     // columns that are never stored)
-    if (svh) for (int i = tid; i < TC_BN; i += TC_THREADS)
+    if (svh) for (int i = tid; i < BN; i += TC_THREADS)
         reinterpret_cast<half*>(smem + SM::OFF_SVH)[i] = n0 + i < n ? svh[n0 + i] : __float2half(0.f);
     tc_fence_before();
     __syncthreads();
@@ -357,11 +375,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                     for (int kk = 0; kk < TC_BK / 16; ++kk) {
                         const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
                         if constexpr (PAIR) {
-                            tc_mma_f16_pair(tmem_base, mk(a0 + 2 * kk), mk(b0 + 2 * kk), TC_IDESC_PAIR, acc);      // +32 bytes per K=16
-                            if (two_tiles) tc_mma_f16_pair(tmem_base + TC_BN, mk(a0 + (TC_A_TILE >> 4) + 2 * kk), mk(b0 + 2 * kk), TC_IDESC_PAIR, acc);
+                            tc_mma_f16_pair(tmem_base, mk(a0 + 2 * kk), mk(b0 + 2 * kk), IDESC, acc);      // +32 bytes per K=16
+                            if (two_tiles) tc_mma_f16_pair(tmem_base + BN, mk(a0 + (TC_A_TILE >> 4) + 2 * kk), mk(b0 + 2 * kk), IDESC, acc);
                         } else {
-                            tc_mma_f16(tmem_base, mk(a0 + 2 * kk), mk(b0 + 2 * kk), TC_IDESC, acc);
-                            if (two_tiles) tc_mma_f16(tmem_base + TC_BN, mk(a0 + (TC_A_TILE >> 4) + 2 * kk), mk(b0 + 2 * kk), TC_IDESC, acc);
+                            tc_mma_f16(tmem_base, mk(a0 + 2 * kk), mk(b0 + 2 * kk), IDESC, acc);
+                            if (two_tiles) tc_mma_f16(tmem_base + BN, mk(a0 + (TC_A_TILE >> 4) + 2 * kk), mk(b0 + 2 * kk), IDESC, acc);
                         }
                     }
                     // arrive when the MMAs above have finished reading the stage (in both CTAs of a pair)
@@ -390,7 +408,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         // in lockstep on every stage, the waits of a stage cost as much as its decode work).
         constexpr int GW = TC_DECODERS / 2;                        // warps per group
         constexpr int TPW = (TC_BK / 16) * NT / GW;                // tiles per warp and stage: 4 (pair) or 8
-        constexpr int TB = 4;                                      // tiles decoded together (register budget)
+        constexpr int TB = TPW < 4 ? TPW : 4;                      // tiles decoded together (register budget)
         const int dw = warp - 2;
         const int grp = (dw >> 2) & 1;
         const int wi = (dw & 3) + 4 * (dw >> 3);                   // 0..7 inside the group
@@ -418,13 +436,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             for (int h = 0; h < TPW; h += TB) {
                 uint32_t st[TB][8];
                 #pragma unroll
-                for (int i = 0; i < TB; ++i) lane_states<K>(raw + raw_off[h + i], lane, st[i]);
+                for (int i = 0; i < TB; ++i) {
+                    if constexpr (K == 4) lane_states4(raw + raw_off[h + i], lane, (lane + 31) & 31, st[i]);
+                    else lane_states<K>(raw + raw_off[h + i], lane, st[i]);
+                }
                 #pragma unroll
                 for (int i = 0; i < TB; ++i) {
-                    const half2 w0 = decode_pair<CB>(st[i][0], st[i][1]);      // rows 2t, 2t+1   col g
-                    const half2 w1 = decode_pair<CB>(st[i][2], st[i][3]);      // rows 2t+8, +9   col g
-                    const half2 w2 = decode_pair<CB>(st[i][4], st[i][5]);      // rows 2t, 2t+1   col g+8
-                    const half2 w3 = decode_pair<CB>(st[i][6], st[i][7]);      // rows 2t+8, +9   col g+8
+                    const half2 w0 = tc_decode_pair<CB>(st[i][0], st[i][1]);      // rows 2t, 2t+1   col g
+                    const half2 w1 = tc_decode_pair<CB>(st[i][2], st[i][3]);      // rows 2t+8, +9   col g
+                    const half2 w2 = tc_decode_pair<CB>(st[i][4], st[i][5]);      // rows 2t, 2t+1   col g+8
+                    const half2 w3 = tc_decode_pair<CB>(st[i][6], st[i][7]);      // rows 2t+8, +9   col g+8
                     *reinterpret_cast<half2*>(bt + st_off[h + i][0]) = w0;
                     *reinterpret_cast<half2*>(bt + st_off[h + i][1]) = w1;
                     *reinterpret_cast<half2*>(bt + st_off[h + i][0] + 1024) = w2;
@@ -451,9 +472,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             // TMEM lane quadrant q; each of the four warps of a quadrant takes one (M tile, 128-column half) pair
             const int q = warp & 3, mt = (warp - 2) >> 3, sel = ((warp - 2) >> 2) & 1;
             const half* svh_s = reinterpret_cast<const half*>(smem + SM::OFF_SVH) + sel * 128;
-            if ((mt == 0 || two_tiles) && n0 + sel * 128 < n) {
+            if ((mt == 0 || two_tiles) && sel * 128 < BN && n0 + sel * 128 < n) {
                 const int row = (mt ? row_t1 : row_t0) + q * 32 + lane;
-                const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + mt * TC_BN + sel * 128;
+                const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + mt * BN + sel * 128;
                 // The 128-point transform of a row is split so that a thread never holds more than 32 accumulators:
                 // the two outer butterfly levels (strides 32 and 64) run on 8-column slices and go back to TMEM, the five
                 // inner levels run on each 32-column chunk as it is read for the store.

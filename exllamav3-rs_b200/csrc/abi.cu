@@ -27,6 +27,7 @@ extern "C" int exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** ou
     ctx->mma_attn = 1;
     ctx->use_tc = getenv("EXL3_B200_NO_TC") ? 0 : 1;
     ctx->use_pair = getenv("EXL3_B200_NO_PAIR") ? 0 : 1;
+    ctx->fuse_transform = getenv("EXL3_B200_NO_FUSED_TRANSFORM") ? 0 : 1;
     ctx->use_decode = (getenv("EXL3_B200_NO_DECODE") || getenv("EXL3_B200_NO_TC")) ? 0 : 1;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete ctx; cudaGetLastError(); return EXL3_ERR_CUDA; }

@@ -18,10 +18,11 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
                                                          const int32_t* __restrict__ cu_q, int bsz, int q_len,
                                                          int kv_append, int G, int rows_per_cta, int rows_lo, int rows_hi, int chunk_mult, int target_items,
                                                          int max_items, AttnPlan* plan, AttnItem* items, int* seq_base,
-                                                         int* seq_splits, int* status)
+                                                         int* seq_splits, int* order, int causal, int* status)
 {
     __shared__ long long s_total;
     __shared__ int s_scan[1024];
+    __shared__ int s_cursor[1024];
     __shared__ int s_carry, s_chunk;
     const int tid = threadIdx.x;
     if (tid == 0) { s_total = 0; s_carry = 0; }
@@ -77,8 +78,46 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
         if (tid == 1023) s_carry += s_scan[1023];
         __syncthreads();
     }
+    // Launch order: longest items first (counting sort by key tiles, most first).  Items differ in length - last splits,
+    // causal cuts, short sequences - and a long one started late leaves the other SMs idle at the end of the kernel
+    // (four 256-row chunks: a quarter of the SM time).
+    const int n_items = s_carry < max_items ? s_carry : max_items;
+    s_scan[tid] = 0; s_cursor[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < n_items; i += 1024) {
+        const AttnItem it = items[i];
+        const int ql = cu_q ? cu_q[it.b + 1] - cu_q[it.b] : q_len;
+        const int tk = (seqlens ? seqlens[it.b] : 0) + (cu_q ? ql : kv_append);
+        const int i_last = min(ql - 1, (it.rb * rows_per_cta + rows_per_cta - 1) / G);
+        const int vis = causal > 0 ? min(tk, tk - ql + i_last + 1) : tk;
+        const int k_begin = it.split * chunk;
+        const int k_end = min(min(k_begin + chunk, tk), vis);
+        int key = k_end > k_begin ? (k_end - k_begin + chunk_mult - 1) / chunk_mult : 0;
+        key = causal >= 0 ? 1023 - min(key, 1023) : 0;          // bin 0 = longest (causal < 0: A/B switch, plan order kept)
+        items[i].pad = key;
+        atomicAdd(&s_scan[key], 1);
+    }
+    __syncthreads();
+    {
+        const int cnt = s_scan[tid];
+        __syncthreads();
+        for (int o = 1; o < 1024; o <<= 1) {                   // inclusive scan over the bins
+            int v = tid >= o ? s_scan[tid - o] : 0;
+            __syncthreads();
+            s_scan[tid] += v;
+            __syncthreads();
+        }
+        const int excl = s_scan[tid] - cnt;
+        __syncthreads();
+        s_scan[tid] = excl;                                    // first position of bin tid
+        __syncthreads();
+    }
+    for (int i = tid; i < n_items; i += 1024) {
+        const int key = items[i].pad;
+        order[causal < 0 ? i : s_scan[key] + atomicAdd(&s_cursor[key], 1)] = i;
+    }
     if (tid == 0) {
-        plan->n_items = s_carry < max_items ? s_carry : max_items;
+        plan->n_items = n_items;
         plan->chunk = chunk;
         // the host sizes the list from bounds on the batch; a list that does not fit would silently drop work, so it is
         // reported through the status word like a device-side wait that ran out
@@ -209,7 +248,7 @@ cudaError_t launch_attn_tc(exl3_ctx* ctx, const AttnParams& p, int max_items, cu
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     (void)ctx;
-    attn_tc_kernel<<<dim3(max_items, p.nkv), ATC_THREADS, ATC_SMEM, st>>>(maps[0], maps[1], p);
+    attn_tc_kernel<<<dim3((unsigned)max_items * p.nkv), ATC_THREADS, ATC_SMEM, st>>>(maps[0], maps[1], p);
     return cudaPeekAtLastError();
 }
 
@@ -230,15 +269,18 @@ cudaError_t launch_attn_tc2(exl3_ctx* ctx, const AttnParams& p, int max_items, c
             return cudaErrorInvalidValue;
     }
     static bool configured[64] = {};
+    static const int tune_h = getenv("EXL3_TUNE_TC_H") ? atoi(getenv("EXL3_TUNE_TC_H")) : 0;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_tc2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_tc2_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     (void)ctx;
-    attn_tc2_kernel<<<dim3(max_items, p.nkv), A2_THREADS, A2_SMEM, st>>>(maps[0], maps[1], p);
+    if (tune_h == 4) attn_tc2_kernel<4><<<dim3((unsigned)max_items * p.nkv), a2_threads(4), A2_SMEM, st>>>(maps[0], maps[1], p);
+    else attn_tc2_kernel<2><<<dim3((unsigned)max_items * p.nkv), a2_threads(2), A2_SMEM, st>>>(maps[0], maps[1], p);
     return cudaPeekAtLastError();
 }
 
@@ -321,32 +363,36 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     // The work list depends on the batch's lengths, not on the layer: inside exl3_step_forward it is built by the first
     // layer's call into the context's slot for this class and reused by the other layers.
     const int cls = decode_shape ? 0 : 1;
-    const size_t list_bytes = 256 + (((size_t)max_items * sizeof(AttnItem) + 255) & ~(size_t)255) + 2 * (((size_t)p.bsz * 4 + 255) & ~(size_t)255);
+    const size_t list_bytes = 256 + (((size_t)max_items * sizeof(AttnItem) + 255) & ~(size_t)255) + 2 * (((size_t)p.bsz * 4 + 255) & ~(size_t)255) +
+                              (((size_t)max_items * 4 + 255) & ~(size_t)255);
     const bool keep = ctx->plan_keep && list_bytes <= ctx->plan_slot_bytes;
     size_t off = *ws_off;                                // scratch of an earlier pass that may still be running
-    AttnPlan* plan; AttnItem* items; int* seq_base; int* seq_splits;
+    AttnPlan* plan; AttnItem* items; int* seq_base; int* seq_splits; int* order;
     if (keep) {
         uint8_t* slot = ctx->plan_slots + cls * ctx->plan_slot_bytes;
         plan = (AttnPlan*)slot;
         items = (AttnItem*)(slot + 256);
         seq_base = (int*)(slot + 256 + (((size_t)max_items * sizeof(AttnItem) + 255) & ~(size_t)255));
         seq_splits = (int*)((uint8_t*)seq_base + (((size_t)p.bsz * 4 + 255) & ~(size_t)255));
+        order = (int*)((uint8_t*)seq_splits + (((size_t)p.bsz * 4 + 255) & ~(size_t)255));
     } else {
         plan = (AttnPlan*)exl3_ws_take(ctx, &off, sizeof(AttnPlan));
         items = (AttnItem*)exl3_ws_take(ctx, &off, (size_t)max_items * sizeof(AttnItem));
         seq_base = (int*)exl3_ws_take(ctx, &off, (size_t)p.bsz * 4);
         seq_splits = (int*)exl3_ws_take(ctx, &off, (size_t)p.bsz * 4);
+        order = (int*)exl3_ws_take(ctx, &off, (size_t)max_items * 4);
     }
     float* partial = (float*)exl3_ws_take(ctx, &off, (size_t)max_items * p.nkv * rows_per_cta * (D + 2) * 4);
-    if (!plan || !items || !seq_base || !seq_splits || !partial)
+    if (!plan || !items || !seq_base || !seq_splits || !order || !partial)
         return exl3_fail(ctx, EXL3_ERR_WORKSPACE, "attention: context scratch too small for the split-KV partials");
-    p.plan = plan; p.items = items; p.seq_base = seq_base; p.seq_splits = seq_splits; p.partial = partial;
+    p.plan = plan; p.items = items; p.seq_base = seq_base; p.seq_splits = seq_splits; p.order = order; p.partial = partial;
     p.status = ctx->status;
     *ws_off = off;
 
+    static const bool no_lpt = getenv("EXL3_TUNE_NO_LPT") != nullptr;
     if (!(keep && ctx->plan_valid[cls])) {
         attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, rows_lo, rows_hi,
-                                              use_tc ? ATC_TN : AT_TK, target_items, max_items, plan, items, seq_base, seq_splits, ctx->status);
+                                              use_tc ? ATC_TN : AT_TK, target_items, max_items, plan, items, seq_base, seq_splits, order, no_lpt ? -1 : (p.causal ? 1 : 0), ctx->status);
         ctx->launches++;
         if (keep) ctx->plan_valid[cls] = 1;
     }

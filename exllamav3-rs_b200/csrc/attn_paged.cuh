@@ -36,6 +36,7 @@ struct AttnParams {
     const int32_t* cu_q;           // [bsz+1] or NULL (then rows of sequence b = [b*q_len, (b+1)*q_len))
     const AttnPlan* plan;
     const AttnItem* items;
+    const int* order;              // [n_items] item indices, longest first: the order in which CTAs / work units take them
     const int* seq_base;           // [bsz] first item of sequence b
     const int* seq_splits;         // [bsz]
     float* partial;                // [n_items][nkv][ROWS][D+2]
@@ -127,7 +128,7 @@ __global__ void __launch_bounds__(AT_THREADS, (QB == 4 && WN == 4) ? AT_Q4_DECOD
         __syncthreads();
         const int unit = s_unit;
         if (unit >= n_units) break;
-        const int item_idx = unit / p.nkv, kvh = unit - item_idx * p.nkv;
+        const int item_idx = p.order[unit / p.nkv], kvh = unit % p.nkv;
         const AttnItem item = p.items[item_idx];
         const int b = item.b;
         const int row_base = p.cu_q ? p.cu_q[b] : b * p.q_len;

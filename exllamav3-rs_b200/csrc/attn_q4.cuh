@@ -87,7 +87,7 @@ attn_q4_decode_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
         __syncthreads();
         const int unit = s_unit;
         if (unit >= n_units) break;
-        const int item_idx = unit / p.nkv, kvh = unit - item_idx * p.nkv;
+        const int item_idx = p.order[unit / p.nkv], kvh = unit % p.nkv;
         const AttnItem item = p.items[item_idx];
         const int b = item.b;
         const int row_base = p.cu_q ? p.cu_q[b] : b * p.q_len;

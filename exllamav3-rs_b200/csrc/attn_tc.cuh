@@ -86,6 +86,12 @@ __device__ __forceinline__ void tc_st32u(uint32_t taddr, const uint32_t (&r)[32]
                    "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
 }
 
+__device__ __forceinline__ void tc_st16u(uint32_t taddr, const uint32_t (&r)[16])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
 __device__ __forceinline__ float ex2_approx(float x)
 {
     float y;
@@ -120,8 +126,9 @@ __device__ __forceinline__ float fmax3(float a, float b, float c)
 __global__ void __launch_bounds__(ATC_THREADS, 1) attn_tc_kernel(const __grid_constant__ CUtensorMap kmap,
                                                                 const __grid_constant__ CUtensorMap vmap, const AttnParams p)
 {
-    const int item_idx = blockIdx.x;
-    if (item_idx >= p.plan->n_items) return;
+    // grid max_items * nkv: the CTAs of one item are neighbours in launch order, items come longest first
+    if ((int)(blockIdx.x / p.nkv) >= p.plan->n_items) return;
+    const int item_idx = p.order[blockIdx.x / p.nkv];
     extern __shared__ uint8_t smem_unaligned[];
     // aligned to 1024 bytes by an offset from the array, not through an integer, so that the compiler still knows the
     // pointer is in shared memory (32-bit addresses, ld/st.shared) instead of falling back to generic accesses
@@ -136,7 +143,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attn_tc_kernel(const __grid_co
     __shared__ int s_failed;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = blockIdx.y;
+    const int kvh = blockIdx.x % p.nkv;
     const int G = p.nq / p.nkv;
     const int chunk = p.plan->chunk;
     const AttnItem item = p.items[item_idx];

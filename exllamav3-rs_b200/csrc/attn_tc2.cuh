@@ -1,17 +1,24 @@
 // Paged flash attention on tcgen05, second arrangement: one CTA = one work item (sequence, 128-row block, KV split) of one
-// kv head, TWO softmax threads per row and a double-buffered S.
+// kv head, H = 2 or 4 softmax threads per row and a double-buffered S.
 //
 // Why.  In the 256-row kernel (attn_tc.cuh) a softmax thread owns a whole row of a 128-key tile: it reads its 128 scores
 // from tensor memory in three round trips (the row maximum needs all of them, registers hold 64) and takes 128
 // exponentials, and the tensor core idles through that (tensor pipe 34 % busy, long-scoreboard stalls 4.3 per issued
-// instruction).  Here the two threads of a row take 64 keys each: one round trip, 64 exponentials, the row maximum and
-// sum exchanged through shared memory between the two warps that share a TMEM lane quadrant.  S has two buffers, so
-// S(j+1) = Q K(j+1)^T is computed while the threads work on tile j, and PV(j) follows as soon as P(j) is written.
+// instruction).  Here the H threads of a row take 128 / H keys each: one round trip, the row maximum and sum exchanged
+// through shared memory between the H warps that share a TMEM lane quadrant.  S has two buffers, so S(j+1) = Q K(j+1)^T is
+// computed while the threads work on tile j, and PV(j) follows as soon as P(j) is written.
+//
+// Measured per tile in steady state (clock64 in one CTA, 8192-key context): 2150 cycles, the same for H = 2 and H = 4:
+// row maximum 200, rendezvous of the row's warps 200, exponentials 1250 (the special-function unit's 16 per clock and SM
+// would allow 1024), P store 140, wait for and request of the next scores 220, loop 140; the issuer sees P 375 cycles
+// after it was announced and needs 410 + 710 cycles to issue PV(j) and S(j+2).  The tensor core (1024 cycles of work per
+// tile) is never what the softmax threads wait for.  Four 256-row chunks, 145 us: about half of that is the tile loop,
+// the rest the start and end of each CTA (4.2 CTAs per SM) and, before the work list was ordered longest first, the tail.
 //
 // TMEM: S0 columns 0..127, S1 128..255 (P of a tile over the last 64 columns of its S buffer, packed fp16), O 256..383.
-// Warps 0..3: keys 0..63 of every tile, lane quadrant = warp; warps 4..7: keys 64..127; warp 8: TMA producer; warp 9: MMA
-// issuer and TMEM owner.  K/V tiles by 4-D TMA out of the paged pools through a ring of five 32 KB buffers in the order
-// the issuer consumes them: K0 K1 V0 K2 V1 K3 ...  Every wait is bounded; a wait that runs out sets the status word.
+// Warps 0..4H-1: softmax, lane quadrant = warp % 4, key part = warp / 4; then the TMA producer and the MMA issuer (which
+// owns the TMEM allocation).  K/V tiles by 4-D TMA out of the paged pools through a ring of five 32 KB buffers in the
+// order the issuer consumes them: K0 K1 V0 K2 V1 K3 ...  Every wait is bounded; a wait that runs out sets the status word.
 #pragma once
 #include "attn_tc.cuh"
 
@@ -19,13 +26,14 @@ namespace exl3 {
 
 constexpr int A2_ROWS = 128, A2_TN = 128, A2_D = 128;
 constexpr int A2_KV_SLOTS = 5;
-constexpr int A2_THREADS = 384;
+constexpr int A2_MAX_H = 4;                                           // softmax threads per row: 2 or 4
+constexpr int a2_threads(int H) { return (4 * H + 2) * 32; }
 constexpr int A2_Q_BYTES = A2_ROWS * A2_D * 2;
 constexpr int A2_KV_SLOT = A2_TN * A2_D * 2;
 constexpr int A2_OFF_Q = 0;
 constexpr int A2_OFF_KV = A2_OFF_Q + A2_Q_BYTES;
-constexpr int A2_OFF_X = A2_OFF_KV + A2_KV_SLOTS * A2_KV_SLOT;        // exchange of row maxima / sums: [2 buffers][2 halves][128] floats
-constexpr int A2_OFF_BAR = A2_OFF_X + 2 * 2 * A2_ROWS * 4;
+constexpr int A2_OFF_X = A2_OFF_KV + A2_KV_SLOTS * A2_KV_SLOT;        // exchange of row maxima / sums: [2 buffers][H parts][128] floats
+constexpr int A2_OFF_BAR = A2_OFF_X + 2 * A2_MAX_H * A2_ROWS * 4;
 // q_full, kv_full/kv_empty[slots], s_full[2], p_full[2], pv_done, o_full, pair[4]
 constexpr int A2_NBARS = 1 + 2 * A2_KV_SLOTS + 2 + 2 + 1 + 1 + 4;
 constexpr int A2_SMEM = A2_OFF_BAR + A2_NBARS * 8 + 16 + 1024;
@@ -41,11 +49,16 @@ __device__ __forceinline__ bool a2_pair_sync(uint64_t* bar, uint32_t& phase, int
     return ok;
 }
 
-__global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_constant__ CUtensorMap kmap,
-                                                                 const __grid_constant__ CUtensorMap vmap, const AttnParams p)
+template <int H>
+__global__ void __launch_bounds__(a2_threads(H), 1) attn_tc2_kernel(const __grid_constant__ CUtensorMap kmap,
+                                                                    const __grid_constant__ CUtensorMap vmap, const AttnParams p)
 {
-    const int item_idx = blockIdx.x;
-    if (item_idx >= p.plan->n_items) return;
+    static_assert(H == 2 || H == 4, "two or four softmax threads per row");
+    constexpr int NSW = 4 * H;                     // softmax warps; warp NSW = TMA producer, NSW + 1 = MMA issuer and TMEM owner
+    constexpr int KPT = A2_TN / H;                 // keys of a tile, and columns of O, per softmax thread
+    // grid max_items * nkv: the CTAs of one item are neighbours in launch order, items come longest first
+    if ((int)(blockIdx.x / p.nkv) >= p.plan->n_items) return;
+    const int item_idx = p.order[blockIdx.x / p.nkv];
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + A2_OFF_BAR);
@@ -61,7 +74,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
     __shared__ int s_failed;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = blockIdx.y;
+    const int kvh = blockIdx.x % p.nkv;
     const int G = p.nq / p.nkv;
     const int chunk = p.plan->chunk;
     const AttnItem item = p.items[item_idx];
@@ -80,15 +93,15 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
 
     if (tid == 0) {
         s_failed = 0;
-        mbar_init(q_full, 8);
-        for (int i = 0; i < 2; ++i) { mbar_init(&p_full[i], 8); mbar_init(&s_full[i], 1); }
+        mbar_init(q_full, NSW);
+        for (int i = 0; i < 2; ++i) { mbar_init(&p_full[i], NSW); mbar_init(&s_full[i], 1); }
         for (int i = 0; i < A2_KV_SLOTS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
         mbar_init(pv_done, 1);
         mbar_init(o_full, 1);
-        for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+        for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], H);
         mbar_fence_init();
     }
-    if (warp == 9) {
+    if (warp == NSW + 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -98,11 +111,11 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
 
-    // 64 scores per softmax thread fit the launch allocation of 168 registers; the service warps keep 152 (their code -
-    // descriptors, ring cursors - spills below about 140)
-    if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 152;");
+    // H = 2: 64 scores per softmax thread fit the launch allocation of 168 registers; the service warps keep 152 (their
+    // code - descriptors, ring cursors - spills below about 140).  H = 4: 576 threads, 112 registers each, 32 scores.
+    if constexpr (H == 2) { if (warp >= NSW) asm volatile("setmaxnreg.dec.sync.aligned.u32 152;"); }
 
-    if (warp == 8) {
+    if (warp == NSW) {
         // ===== producer: ring items in the order the issuer takes them: K0, K1, then V(j), K(j+2) for every tile j
         if (lane == 0 && n_tiles > 0) {
             int it = 0;
@@ -127,7 +140,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
             }
             if (!ok) failed = true;
         }
-    } else if (warp == 9) {
+    } else if (warp == NSW + 1) {
         // ===== MMA issuer.  The whole warp runs the loop with warp-uniform values; one elected lane issues.
         if (n_tiles > 0) {
             const bool leader = elect_one();
@@ -183,8 +196,8 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
             }
             if (!failed && leader) tc_commit(o_full);
         }
-    } else if (warp < 8) {
-        // ===== softmax: thread = (row, half of the tile's keys)
+    } else if (warp < NSW) {
+        // ===== softmax: thread = (row, part h of the tile's keys)
         const int q = warp & 3, h = warp >> 2;
         const int lr = q * 32 + lane;
         const int row = r0 + lr;
@@ -192,13 +205,15 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
         const bool valid = row < ql * G;
         const int head = kvh * G + (row - qidx * G);
         const int lim = valid ? (p.causal ? min(total_k, total_k - ql + qidx + 1) : total_k) : 0;
-        {   // this thread's d block (64 of the 128 dims) of its Q row -> shared memory, K-major 128B-swizzled
-            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(row_base + qidx) * p.nq + head) * A2_D) + h * 8;
-            uint8_t* qs = smem + A2_OFF_Q + h * (A2_ROWS * 128) + lr * 128;
+        {   // this thread's 128 / H dims of its Q row -> shared memory, K-major 128B-swizzled (two 64-wide d blocks)
+            constexpr int CH = 16 / H;                           // 16-byte chunks per thread
+            const int c0 = h * CH;                               // first chunk of the row's 16
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(row_base + qidx) * p.nq + head) * A2_D) + c0;
+            uint8_t* qs = smem + A2_OFF_Q + (c0 >> 3) * (A2_ROWS * 128) + lr * 128;
             #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < CH; ++c) {
                 const uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(qs + ((c ^ (lr & 7)) << 4)) = v;
+                *reinterpret_cast<uint4*>(qs + ((((c0 & 7) + c) ^ (lr & 7)) << 4)) = v;
             }
             fence_proxy_async();
             __syncwarp();
@@ -207,20 +222,19 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
         float m_used = -INFINITY, m_true = -INFINITY, l_part = 0.f;
         uint32_t pair_phase = 0;
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-        const uint32_t tmem_o = tmem_base + lane_addr + 256 + h * 64;       // this thread's 64 columns of O
+        const uint32_t tmem_o = tmem_base + lane_addr + 256 + h * KPT;      // this thread's columns of O
         const float scale = p.scale_log2;
         // The scores of tile j+1 are requested before P(j) is announced: a TMEM read issued after the issuer has queued
         // PV(j) and S(j+2) waits behind those 1024 tensor-core cycles (per-tile time 2770 cycles with the read at the top of
         // the loop).  S(j+1) was issued before PV(j), so waiting for it here cannot hold anything up.
-        float sv[64];
+        float sv[KPT];
         auto request_scores = [&](int j) -> bool {
             const int sb = j & 1;
             if (!mbar_wait_warp(&s_full[sb], (j >> 1) & 1)) return false;
             tc_fence_after();
-            float (&lo)[32] = *reinterpret_cast<float (*)[32]>(&sv[0]);
-            float (&hi)[32] = *reinterpret_cast<float (*)[32]>(&sv[32]);
-            tc_ld32(tmem_base + lane_addr + sb * 128 + h * 64, lo);
-            tc_ld32(tmem_base + lane_addr + sb * 128 + h * 64 + 32, hi);
+            #pragma unroll
+            for (int c = 0; c < KPT / 32; ++c)
+                tc_ld32(tmem_base + lane_addr + sb * 128 + h * KPT + c * 32, *reinterpret_cast<float (*)[32]>(&sv[c * 32]));
             return true;
         };
         if (n_tiles > 0) {
@@ -231,42 +245,46 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
             const int sb = j & 1;
             const uint32_t tmem_s = tmem_base + lane_addr + sb * 128;
             const int kbase = k_begin + j * A2_TN;
-            const int nvis = min(lim, k_end) - kbase - h * 64;       // keys of this thread's half the row may see (may be <= 0)
-            if (nvis < 64) {
+            const int nvis = min(lim, k_end) - kbase - h * KPT;      // keys of this thread's part the row may see (may be <= 0)
+            if (nvis < KPT) {
                 #pragma unroll
-                for (int e = 0; e < 64; ++e) sv[e] = e < nvis ? sv[e] : -INFINITY;
+                for (int e = 0; e < KPT; ++e) sv[e] = e < nvis ? sv[e] : -INFINITY;
             }
             float mx0 = -INFINITY, mx1 = -INFINITY;
             #pragma unroll
-            for (int e = 0; e < 64; e += 4) { mx0 = fmax3(mx0, sv[e], sv[e + 1]); mx1 = fmax3(mx1, sv[e + 2], sv[e + 3]); }
-            // row maximum over both halves: the partner is the same lane of warp (warp ^ 4)
-            float* xm = xch + (size_t)sb * 2 * A2_ROWS;
+            for (int e = 0; e < KPT; e += 4) { mx0 = fmax3(mx0, sv[e], sv[e + 1]); mx1 = fmax3(mx1, sv[e + 2], sv[e + 3]); }
+            // row maximum over all parts: the partners are the same lane of the other warps of this lane quadrant
+            float* xm = xch + (size_t)sb * A2_MAX_H * A2_ROWS;
             xm[h * A2_ROWS + lr] = fmaxf(mx0, mx1);
             if (!a2_pair_sync(&pair_bar[q], pair_phase, lane)) { failed = true; break; }
-            m_true = fmaxf(m_true, fmaxf(fmaxf(mx0, mx1), xm[(h ^ 1) * A2_ROWS + lr]) * scale);   // raw scores: the scale is positive
+            float mrow = xm[lr];
+            #pragma unroll
+            for (int hh = 1; hh < H; ++hh) mrow = fmaxf(mrow, xm[hh * A2_ROWS + lr]);
+            m_true = fmaxf(m_true, mrow * scale);                   // raw scores: the scale is positive
             // lazy reference update, decided identically by both threads of the row
             const bool move = m_true > m_used + ATC_RESCALE_THRESHOLD || (m_used == -INFINITY && m_true > -INFINITY);
             const bool rescale = move && m_used != -INFINITY && j > 0;
             const float corr = rescale ? ex2_approx(m_used - m_true) : 1.0f;
             if (move) m_used = m_true;
             const float nref = (m_used == -INFINITY) ? 0.f : -m_used;
-            uint32_t pw[32];
+            uint32_t pw[KPT / 2];
             float l0 = 0.f, l1 = 0.f;
             #pragma unroll
-            for (int e = 0; e < 64; e += 2) {
+            for (int e = 0; e < KPT; e += 2) {
                 const float e0 = ex2_approx(fmaf(sv[e], scale, nref)), e1 = ex2_approx(fmaf(sv[e + 1], scale, nref));
                 l0 += e0; l1 += e1;
                 pw[e >> 1] = pack_h2(e0, e1);
             }
-            // P over the last 64 columns of the S buffer (column 64 + c = keys 2c, 2c+1).  The partner has read its scores
-            // out of those columns before it reached the pair barrier above.
-            tc_st32u(tmem_s + 64 + h * 32, pw);
+            // P over the last 64 columns of the S buffer (column 64 + c = keys 2c, 2c+1).  The partners have read their
+            // scores out of those columns before they reached the barrier above.
+            if constexpr (H == 2) tc_st32u(tmem_s + 64 + h * 32, pw);
+            else tc_st16u(tmem_s + 64 + h * 16, pw);
             if (__any_sync(0xffffffffu, rescale)) {
                 // O holds tiles 0..j-1 once PV(j-1) has completed (its commit is completion j-1 of pv_done)
                 if (!mbar_wait_warp(pv_done, (j - 1) & 1)) { failed = true; break; }
                 tc_fence_after();
                 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < KPT / 32; ++c) {
                     float part[32];
                     tc_ld32(tmem_o + c * 32, part);
                     tc_wait_ld();
@@ -305,17 +323,19 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
             bool ok = a2_pair_sync(&pair_bar[q], pair_phase, lane);      // both warps are past their last read of them
             xl[h * A2_ROWS + lr] = l_part;
             ok = a2_pair_sync(&pair_bar[q], pair_phase, lane) && ok;
-            l_run = l_part + xl[(h ^ 1) * A2_ROWS + lr];
+            l_run = xl[lr];
+            #pragma unroll
+            for (int hh = 1; hh < H; ++hh) l_run += xl[hh * A2_ROWS + lr];
             if (!ok) failed = true;
         }
         if (!failed && n_tiles > 0 && !mbar_wait_sleep_warp(o_full, 0)) failed = true;
         if (!failed) {
             tc_fence_after();
             const float inv = (splits == 1) ? (l_run > 0.f ? 1.0f / l_run : 0.f) : 1.0f;
-            half* orow = p.o + ((size_t)(row_base + qidx) * p.nq + head) * A2_D + h * 64;
+            half* orow = p.o + ((size_t)(row_base + qidx) * p.nq + head) * A2_D + h * KPT;
             float* pp = p.partial + (((size_t)item_idx * p.nkv + kvh) * A2_ROWS + lr) * (A2_D + 2);
             #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < KPT / 32; ++c) {
                 float ov[32];
                 if (n_tiles > 0) {
                     tc_ld32(tmem_o + c * 32, ov);
@@ -333,7 +353,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
                                                 pack_h2(ov[e * 8 + 4] * inv, ov[e * 8 + 5] * inv), pack_h2(ov[e * 8 + 6] * inv, ov[e * 8 + 7] * inv));
                     } else {
                         #pragma unroll
-                        for (int e = 0; e < 32; e += 2) *reinterpret_cast<float2*>(pp + h * 64 + c * 32 + e) = make_float2(ov[e], ov[e + 1]);
+                        for (int e = 0; e < 32; e += 2) *reinterpret_cast<float2*>(pp + h * KPT + c * 32 + e) = make_float2(ov[e], ov[e + 1]);
                     }
                 }
             }
@@ -344,7 +364,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn_tc2_kernel(const __grid_co
     if (failed) s_failed = 1;
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == NSW + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }

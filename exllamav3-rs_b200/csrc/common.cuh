@@ -29,6 +29,7 @@ struct exl3_ctx {
     int use_tc;             // 1: tcgen05 GEMM for large M (default), 0: small-M kernel in passes (for A/B runs)
     int use_decode;         // 1: the streaming decode kernel takes calls of up to 16 rows (default), 0: they go the way of larger row counts
     int use_pair;           // 1: the tcgen05 GEMM runs on CTA pairs (cta_group::2, default), 0: one CTA per tile
+    int fuse_transform;     // 1: in the step runner the norm / activation kernels write the tensor-core GEMM's transformed activations (default), 0: separate launches
     // Work lists of the attention kernels kept across the layers of one exl3_step_forward call (they depend on the batch's
     // lengths only, not on the layer): slot 0 = decode class, slot 1 = long class.  plan_keep is set for the duration of a
     // step; outside of it every attention call builds its list anew.
@@ -60,6 +61,17 @@ static inline int exl3_check_launch(exl3_ctx* ctx, const char* what)
 }
 
 static inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+
+// Transformed activations of up to three EXL3 tensors that share an input, written by the kernel that produces the input
+// (norm, activation) instead of by the GEMM's own transform launch: where each tensor's copy goes and its sign vector.
+struct exl3_pre_act { const half* suh[3]; half* a_had[3]; int nseg; };
+// gemm.cu: fills `pre` and returns true when exl3_gemm_fanout_pre can run these tensors at m rows (tensor-core path)
+bool exl3_tc_pre_buffers(exl3_ctx* ctx, int count, const exl3_linear* const* w, int m, exl3_pre_act* pre);
+int exl3_gemm_fanout_pre(exl3_ctx* ctx, exl3_stream stream, int count, const exl3_linear* const* w, void* const* C, int m, int c_fp32);
+// elementwise.cu
+int exl3_rms_norm_pre(exl3_ctx* ctx, exl3_stream stream, const void* x, int x_fp32, const void* w, float* r, float eps,
+                      float cbias, float cscale, int rows, int dim, const exl3_pre_act* pre);
+int exl3_silu_mul_pre(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* y, int rows, int dim, const exl3_pre_act* pre);
 
 // Carve `bytes` out of the context scratch starting at *off (256-byte aligned); NULL when it does not fit.
 static inline void* exl3_ws_take(exl3_ctx* ctx, size_t* off, size_t bytes)

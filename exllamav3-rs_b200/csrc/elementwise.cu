@@ -154,6 +154,88 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(const TI* __restrict__ x
     }
 }
 
+// 128-point Hadamard transform of a block whose element 4 * lane + j sits in v[j] of lane `lane`, after the fp16 sign
+// multiply: same arithmetic as the large-M GEMM's input transform (fp16 product, fp32 butterflies, one fp16 rounding).
+__device__ __forceinline__ uint2 had128_signed_lane(half2 a, half2 b, const half* __restrict__ suh, int col, int lane)
+{
+    const uint2 sr = reinterpret_cast<const uint2*>(suh)[col];
+    a = __hmul2(a, *reinterpret_cast<const half2*>(&sr.x));
+    b = __hmul2(b, *reinterpret_cast<const half2*>(&sr.y));
+    float v0 = __low2float(a), v1 = __high2float(a), v2 = __low2float(b), v3 = __high2float(b);
+    const float s0 = v0 + v1, d0 = v0 - v1, s1 = v2 + v3, d1 = v2 - v3;
+    v0 = s0 + s1; v1 = d0 + d1; v2 = s0 - s1; v3 = d0 - d1;
+    #pragma unroll
+    for (int i = 1; i < 32; i <<= 1) {
+        const float p0 = __shfl_xor_sync(0xffffffffu, v0, i), p1 = __shfl_xor_sync(0xffffffffu, v1, i);
+        const float p2 = __shfl_xor_sync(0xffffffffu, v2, i), p3 = __shfl_xor_sync(0xffffffffu, v3, i);
+        const bool up = lane & i;
+        v0 = (up ? -v0 : v0) + p0; v1 = (up ? -v1 : v1) + p1;
+        v2 = (up ? -v2 : v2) + p2; v3 = (up ? -v3 : v3) + p3;
+    }
+    constexpr float R128 = 0.088388347648f;
+    a = __floats2half2_rn(v0 * R128, v1 * R128);
+    b = __floats2half2_rn(v2 * R128, v3 * R128);
+    uint2 o; o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
+    return o;
+}
+
+// rms_norm_kernel whose fp16 result goes straight through the input transform of the EXL3 tensors that read it (up to
+// three: q/k/v or gate/up, each with its own sign vector) instead of to memory: the norm's own output and the separate
+// transform launch drop out.  A warp's 32 float4 columns of one pass are one 128-block (dim % 128 == 0).
+template <typename TI, bool RES_IN>
+__global__ void __launch_bounds__(1024) rms_norm_had_kernel(const TI* __restrict__ x, const half* __restrict__ w, float* __restrict__ r,
+                                                            float eps, float cbias, float cscale, int dim, const exl3_pre_act pre)
+{
+    __shared__ float sh[32];
+    const int cols = dim >> 2, lane = threadIdx.x & 31;
+    const size_t row = blockIdx.x;
+    float4 v[8];
+    float sum = 0.0f;
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < cols) {
+            float4 f;
+            if constexpr (sizeof(TI) == 2) {
+                uint2 raw = reinterpret_cast<const uint2*>(x + row * dim)[c];
+                half2 a = *reinterpret_cast<half2*>(&raw.x), b = *reinterpret_cast<half2*>(&raw.y);
+                f = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+            } else {
+                f = reinterpret_cast<const float4*>(x + row * dim)[c];
+            }
+            if constexpr (RES_IN) {
+                float4 q = reinterpret_cast<const float4*>(r + row * dim)[c];
+                f.x += q.x; f.y += q.y; f.z += q.z; f.w += q.w;
+                reinterpret_cast<float4*>(r + row * dim)[c] = f;
+            }
+            sum = fmaf(f.x, f.x, sum); sum = fmaf(f.y, f.y, sum); sum = fmaf(f.z, f.z, sum); sum = fmaf(f.w, f.w, sum);
+            v[i] = f;
+        }
+    }
+    sum = block_sum(sum, sh);
+    const float rmf = rsqrtf(sum / (float)dim + eps) * cscale;
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < cols) {                                         // warp-uniform: cols % 32 == 0
+            float4 f = v[i];
+            if (w) {
+                uint2 raw = reinterpret_cast<const uint2*>(w)[c];
+                half2 a = *reinterpret_cast<half2*>(&raw.x), b = *reinterpret_cast<half2*>(&raw.y);
+                f.x = f.x * (__low2float(a) + cbias) * rmf;  f.y = f.y * (__high2float(a) + cbias) * rmf;
+                f.z = f.z * (__low2float(b) + cbias) * rmf;  f.w = f.w * (__high2float(b) + cbias) * rmf;
+            } else {
+                f.x *= rmf; f.y *= rmf; f.z *= rmf; f.w *= rmf;
+            }
+            const half2 a = __floats2half2_rn(f.x, f.y), b = __floats2half2_rn(f.z, f.w);      // what rms_norm_kernel stores
+            #pragma unroll
+            for (int sgm = 0; sgm < 3; ++sgm)
+                if (sgm < pre.nseg)
+                    reinterpret_cast<uint2*>(pre.a_had[sgm] + row * dim)[c] = had128_signed_lane(a, b, pre.suh[sgm], c, lane);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------- RoPE
 // One warp per (row, head); lane holds elements lane + 32*i.  Arithmetic follows kernels/rope.cu:55-255: optional
 // RMSNorm (value rounded to fp16, weight + bias in fp16, fp16 product), then the rotation in fp32 with __sinf/__cosf of
@@ -262,6 +344,27 @@ __global__ void __launch_bounds__(256) silu_mul_tail_kernel(const half* x, const
     half a = x[i];
     half r = hrcp(__hadd(__float2half_rn(1.0f), hexp(__hneg(a))));
     z[i] = __hmul(__hmul(a, r), y[i]);
+}
+
+// silu_mul_kernel whose result goes straight through the input transform of the EXL3 tensor that reads it (down_proj):
+// one warp per 128-block of a row, lane = 4 consecutive elements.
+__global__ void __launch_bounds__(256) silu_mul_had_kernel(const half* __restrict__ x, const half* __restrict__ y,
+                                                           const half* __restrict__ suh, half* __restrict__ a_had, long long blocks, int bpr)
+{
+    const int lane = threadIdx.x & 31;
+    const long long blk = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (blk >= blocks) return;
+    const uint2 xr = reinterpret_cast<const uint2*>(x + blk * 128)[lane], yr = reinterpret_cast<const uint2*>(y + blk * 128)[lane];
+    const half2 one = __float2half2_rn(1.0f);
+    half2 z[2];
+    #pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const half2 a = *reinterpret_cast<const half2*>(&xr.x + j), b = *reinterpret_cast<const half2*>(&yr.x + j);
+        const half2 rr = h2rcp(__hadd2(one, h2exp(__hneg2(a))));
+        z[j] = __hmul2(__hmul2(a, rr), b);
+    }
+    const int col = (int)(blk % bpr) * 32 + lane;               // uint2 index inside the sign vector
+    reinterpret_cast<uint2*>(a_had + blk * 128)[lane] = had128_signed_lane(z[0], z[1], suh, col, lane);
 }
 
 __global__ void __launch_bounds__(256) add_kernel(const half* __restrict__ x, const half* __restrict__ y,
@@ -480,4 +583,42 @@ extern "C" int exl3_embed(exl3_ctx* ctx, exl3_stream stream, const int64_t* ids,
     embed_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(ids, (const half*)table, out, rows, dim, vocab);
     ctx->launches++;
     return exl3_check_launch(ctx, "embed");
+}
+
+// ---- producers that write the tensor-core GEMM's transformed activations themselves (internal: used by the step runner)
+
+int exl3_rms_norm_pre(exl3_ctx* ctx, exl3_stream stream, const void* x, int x_fp32, const void* w, float* r, float eps,
+                      float cbias, float cscale, int rows, int dim, const exl3_pre_act* pre)
+{
+    EXL3_REQUIRE(ctx && x && pre && pre->nseg >= 1 && pre->nseg <= 3, "rms_norm (fused transform): bad argument");
+    EXL3_REQUIRE(rows >= 0 && dim > 0 && dim % 128 == 0 && dim <= 32768, "rms_norm (fused transform): dim % 128 == 0, dim <= 32768 required");
+    EXL3_REQUIRE(aligned16(x) && aligned16(w) && aligned16(r), "rms_norm (fused transform): pointers must be 16-byte aligned");
+    if (rows == 0) return EXL3_OK;
+    const int cols = dim / 4;
+    int threads = cols <= 2048 ? 256 : 1024;
+    if (cols < 256) threads = ((cols + 31) / 32) * 32;
+    cudaStream_t st = (cudaStream_t)stream;
+    const half* wp = (const half*)w;
+    if (x_fp32) {
+        if (r) rms_norm_had_kernel<float, true><<<rows, threads, 0, st>>>((const float*)x, wp, r, eps, cbias, cscale, dim, *pre);
+        else   rms_norm_had_kernel<float, false><<<rows, threads, 0, st>>>((const float*)x, wp, r, eps, cbias, cscale, dim, *pre);
+    } else {
+        if (r) rms_norm_had_kernel<half, true><<<rows, threads, 0, st>>>((const half*)x, wp, r, eps, cbias, cscale, dim, *pre);
+        else   rms_norm_had_kernel<half, false><<<rows, threads, 0, st>>>((const half*)x, wp, r, eps, cbias, cscale, dim, *pre);
+    }
+    ctx->launches++;
+    return exl3_check_launch(ctx, "rms_norm (fused transform)");
+}
+
+int exl3_silu_mul_pre(exl3_ctx* ctx, exl3_stream stream, const void* x, const void* y, int rows, int dim, const exl3_pre_act* pre)
+{
+    EXL3_REQUIRE(ctx && x && y && pre && pre->nseg == 1, "silu_mul (fused transform): bad argument");
+    EXL3_REQUIRE(rows >= 0 && dim > 0 && dim % 128 == 0, "silu_mul (fused transform): dim % 128 == 0 required");
+    EXL3_REQUIRE(aligned16(x) && aligned16(y), "silu_mul (fused transform): pointers must be 16-byte aligned");
+    if (rows == 0) return EXL3_OK;
+    const long long blocks = (long long)rows * (dim / 128);
+    silu_mul_had_kernel<<<(unsigned)((blocks + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const half*)x, (const half*)y, pre->suh[0], pre->a_had[0],
+                                                                                      blocks, dim / 128);
+    ctx->launches++;
+    return exl3_check_launch(ctx, "silu_mul (fused transform)");
 }

@@ -346,8 +346,11 @@ cudaError_t launch_tc_k(int K, int cb, bool pair, int bn, const CUtensorMap* ama
 
 // Tensor-core path for rows [0, m) and `nseg` weight tensors that share the activations, k, bits and codebook:
 // one launch of the input transforms (each tensor has its own suh) and one of the tcgen05 kernel.
+// With `pre` the transformed activations are already in place (written into the buffers exl3_tc_pre_buffers named, by the
+// kernel that produced the input), and the transform launch is skipped.
 int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const void* const* trellis, void* const* C,
-                 const half* const* suh, const half* const* svh, const int* n, int m, int k, int K, int c_fp32, int cb)
+                 const half* const* suh, const half* const* svh, const int* n, int m, int k, int K, int c_fp32, int cb,
+                 bool pre = false)
 {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled is not available from this driver");
@@ -396,12 +399,14 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
     }
     bool all_signed = true;
     for (int i = 0; i < nseg; ++i) all_signed = all_signed && pa.suh[i] != nullptr;
-    if (k % 256 == 0 && all_signed) {
+    if (pre) {
+        // nothing to launch
+    } else if (k % 256 == 0 && all_signed) {
         const long long pairs = (long long)m * (k / 256);
         gemm_prologue_mma_kernel<<<dim3((unsigned)((pairs + 8 * GP_PAIRS - 1) / (8 * GP_PAIRS)), nseg), 256, 0, st>>>(A, pa, k, pairs);
     } else
         gemm_prologue_plain_kernel<<<dim3(m, nseg), 256, 0, st>>>(A, pa, k);
-    ctx->launches++;
+    if (!pre) ctx->launches++;
     p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
     cudaError_t e = launch_tc_k(K, cb, ctx->use_pair != 0, bn, amap, rmap, p, blocks, st);
     ctx->launches++;
@@ -619,6 +624,45 @@ extern "C" int exl3_gemm_fanout(exl3_ctx* ctx, exl3_stream stream, const void* A
         if (rc != EXL3_OK) return rc;
     }
     return EXL3_OK;
+}
+
+// The tensor-core path with the input transform done by the producer of the activations (see exl3_pre_act).  The buffers
+// are the ones gemm_tc_rows carves from the start of the context scratch, so the two calls agree on them by construction.
+static bool tc_pre_applies(exl3_ctx* ctx, int count, const exl3_linear* const* w, int m)
+{
+    if (!ctx || !w || count < 1 || count > TC_MAX_SEG || m <= GD_MAX_M || !ctx->use_tc) return false;
+    for (int i = 0; i < count; ++i) {
+        if (!w[i] || !w[i]->trellis || !w[i]->suh) return false;
+        if (w[i]->k != w[0]->k || w[i]->K != w[0]->K || w[i]->cb != w[0]->cb) return false;
+        if (w[i]->k % 128 != 0 || w[i]->n % 128 != 0 || !(w[i]->n % TC_BN == 0 || (ctx->use_pair && count == 1))) return false;
+        if (w[i]->K < 1 || w[i]->K > 8 || !aligned16(w[i]->trellis) || !aligned16(w[i]->suh) || !aligned16(w[i]->svh)) return false;
+    }
+    return true;
+}
+
+bool exl3_tc_pre_buffers(exl3_ctx* ctx, int count, const exl3_linear* const* w, int m, exl3_pre_act* pre)
+{
+    if (!tc_pre_applies(ctx, count, w, m)) return false;
+    size_t off = 0;
+    pre->nseg = count;
+    for (int i = 0; i < 3; ++i) { pre->suh[i] = nullptr; pre->a_had[i] = nullptr; }
+    for (int i = 0; i < count; ++i) {
+        pre->a_had[i] = (half*)exl3_ws_take(ctx, &off, (size_t)m * w[0]->k * 2);
+        if (!pre->a_had[i]) return false;
+        pre->suh[i] = (const half*)w[i]->suh;
+    }
+    return true;
+}
+
+int exl3_gemm_fanout_pre(exl3_ctx* ctx, exl3_stream stream, int count, const exl3_linear* const* w, void* const* C, int m, int c_fp32)
+{
+    EXL3_REQUIRE(tc_pre_applies(ctx, count, w, m) && C, "exl3_gemm (activations transformed by the producer): not applicable to these tensors");
+    const void* tr[TC_MAX_SEG]; const half* suh[TC_MAX_SEG]; const half* svh[TC_MAX_SEG]; int n[TC_MAX_SEG];
+    for (int i = 0; i < count; ++i) {
+        EXL3_REQUIRE(C[i] && aligned16(C[i]), "exl3_gemm: bad output pointer");
+        tr[i] = w[i]->trellis; suh[i] = (const half*)w[i]->suh; svh[i] = (const half*)w[i]->svh; n[i] = w[i]->n;
+    }
+    return gemm_tc_rows(ctx, (cudaStream_t)stream, nullptr, count, tr, C, suh, svh, n, m, w[0]->k, w[0]->K, c_fp32, w[0]->cb, true);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

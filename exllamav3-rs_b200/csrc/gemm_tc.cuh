@@ -242,7 +242,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     using SM = TcSmem<K, CTAS, BN>;
     constexpr bool PAIR = CTAS == 2;
     constexpr uint32_t IDESC = tc_idesc(BN, 128 * CTAS);
-    constexpr int NT = SM::NB / 16;                       // tile columns this CTA decodes (16 or 8)
+    constexpr int NT = SM::NB / 16;                       // tile columns this CTA decodes (16, 8 or 4)
+    // decoder warps per group: a group takes a K step together, four tiles per warp where the stage has enough of them
+    constexpr int GW = (TC_BK / 16) * NT / 4 < 8 ? (TC_BK / 16) * NT / 4 : 8;
+    constexpr int NG = TC_DECODERS / GW;                  // groups, taking K steps in turn
     extern __shared__ uint8_t smem_unaligned[];
     // aligned to 1024 bytes by an offset from the array, not through an integer, so that the compiler still knows the
     // pointer is in shared memory (32-bit addresses, ld/st.shared) instead of falling back to generic accesses
@@ -281,8 +284,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     if (tid == 0) {
         s_failed = 0;
         for (int i = 0; i < 2 * SM::SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
-        for (int i = 0; i < SM::SR; ++i) { mbar_init(&r_full[i], 1); mbar_init(&r_empty[i], TC_DECODERS / 2); }
-        for (int i = 0; i < SM::SB; ++i) { mbar_init(&b_full[i], TC_DECODERS / 2 * CTAS); mbar_init(&b_empty[i], 1); }
+        for (int i = 0; i < SM::SR; ++i) { mbar_init(&r_full[i], 1); mbar_init(&r_empty[i], GW); }
+        for (int i = 0; i < SM::SB; ++i) { mbar_init(&b_full[i], GW * CTAS); mbar_init(&b_empty[i], 1); }
         mbar_init(acc_full, 1);
         mbar_init(drain, 1);
         mbar_fence_init();
@@ -403,15 +406,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         }
     } else if (warp < 2 + TC_DECODERS) {
         // ===== decoders: raw codes -> fp16 weights in the K-major swizzled B tile.
-        // The 16 warps form two groups of 8 (two warps per scheduler each) that take alternate K steps: while one group
-        // waits on its barriers, fences and arrives, the other decodes, so the schedulers stay busy (with all 16 warps
-        // in lockstep on every stage, the waits of a stage cost as much as its decode work).
-        constexpr int GW = TC_DECODERS / 2;                        // warps per group
-        constexpr int TPW = (TC_BK / 16) * NT / GW;                // tiles per warp and stage: 4 (pair) or 8
-        constexpr int TB = TPW < 4 ? TPW : 4;                      // tiles decoded together (register budget)
+        // The 16 warps form NG groups (two of 8 warps, or four of 4 on 128-column slabs; every group has a warp on each
+        // scheduler) that take K steps in turn: while one group waits on its barriers, fences and arrives, the others
+        // decode, so the schedulers stay busy (with all 16 warps in lockstep on every stage, the waits of a stage cost as
+        // much as its decode work; with two tiles per warp and stage they cost a third of it).
+        constexpr int TPW = (TC_BK / 16) * NT / GW;                // tiles per warp and stage: 4, or 8 (one CTA per slab)
+        constexpr int TB = 4;                                      // tiles decoded together (register budget)
+        static_assert(TPW % TB == 0 && SM::SR >= NG, "decoder groups");
         const int dw = warp - 2;
-        const int grp = (dw >> 2) & 1;
-        const int wi = (dw & 3) + 4 * (dw >> 3);                   // 0..7 inside the group
+        const int grp = (dw >> 2) % NG;
+        const int wi = (dw & 3) + 4 * (dw / (4 * NG));             // 0..GW-1 inside the group
         const int g = lane >> 2, t = lane & 3;
         // Tile (r, nt) of a stage: tile row r covers k = 16r..16r+15, i.e. 16-byte chunks 2r and 2r+1 of a 128-byte B
         // row; B row = column 16nt + g (and + 8, 1024 bytes further on); the chunk index is XORed with (row & 7) = g.
@@ -427,7 +431,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         if constexpr (PAIR) asm volatile("mapa.shared::cluster.u32 %0, %0, 0;" : "+r"(bfull_addr));
         int sr = grp % SM::SR, sb = grp % SM::SB;
         uint32_t par_r = 0, par_b = 1;                             // b_empty is waited from the second round on
-        for (int ks = grp; ks < ksteps; ks += 2) {
+        for (int ks = grp; ks < ksteps; ks += NG) {
             if (!mbar_wait_sleep_warp(&r_full[sr], par_r)) { failed = true; break; }
             if (ks >= SM::SB && !mbar_wait_sleep_warp(&b_empty[sb], par_b)) { failed = true; break; }
             const uint32_t* raw = reinterpret_cast<const uint32_t*>(smem + SM::OFF_RAW + sr * SM::RAW_STAGE);
@@ -459,8 +463,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                 asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bfull_addr + 8u * sb) : "memory");
                 mbar_arrive(&r_empty[sr]);
             }
-            sr += 2; if (sr >= SM::SR) { sr -= SM::SR; par_r ^= 1; }
-            sb += 2; if (sb >= SM::SB) { sb -= SM::SB; par_b ^= 1; }
+            sr += NG; if (sr >= SM::SR) { sr -= SM::SR; par_r ^= 1; }
+            sb += NG; if (sb >= SM::SB) { sb -= SM::SB; par_b ^= 1; }
         }
     }
 

@@ -85,6 +85,46 @@ def test_ragged_step_equals_sequence_by_sequence(ctx):
         assert int(t1[0]) == int(tok[b])
 
 
+def test_fused_input_transform_equals_separate_launches(ctx):
+    """From 128 rows on the norm and activation kernels of the step write the tensor-core GEMM's transformed activations
+    themselves.  The fp32 butterflies run in another order than in the separate transform launch (shuffles against two
+    small tensor-core products), so a transformed activation that sits on an fp16 rounding boundary may come out one
+    step apart, and every later fp16 rounding of that row can then fall the other way: per sequence the two paths are
+    either bit-identical or 3e-4 .. 9e-4 of the logits' RMS apart, each 9e-4 .. 1.1e-3 from the oracle.  Bars: 5e-3
+    between the two, 1e-2 against the oracle for both."""
+    import os
+    import exl3b200
+    from oracle import oracle_model
+    q_lens = [1, 8, 256, 1, 40]
+    ctx_lens = [300, 1000, 512, 64, 0]
+    model, nm, ids, q_lens, ctx_lens, bt = _setup(0, 4, 1, q_lens, ctx_lens, 123, n_layers=2)
+    pools0 = [(L["k_cache"].clone(), L["v_cache"].clone()) for L in model.layers]
+    args = lambda: (H.to_dev(ids), H.to_dev(q_lens), H.to_dev(ctx_lens), H.to_dev(bt), int(q_lens.max()))  # noqa: E731
+    n0 = ctx.launch_count()
+    tok, logits = model.step(ctx, *args(), want_logits=True)
+    fused_launches = ctx.launch_count() - n0
+    ctx.poll_status()
+    os.environ["EXL3_B200_NO_FUSED_TRANSFORM"] = "1"
+    try:
+        ctx2 = exl3b200.Ctx(0)
+    finally:
+        del os.environ["EXL3_B200_NO_FUSED_TRANSFORM"]
+    for L, (k0, v0) in zip(model.layers, pools0):
+        L["k_cache"].copy_(k0); L["v_cache"].copy_(v0)
+    n0 = ctx2.launch_count()
+    tok2, logits2 = model.step(ctx2, *args(), want_logits=True)
+    plain_launches = ctx2.launch_count() - n0
+    ctx2.poll_status()
+    err = H.rel_rms_err(logits.cpu().numpy(), logits2.cpu().numpy())
+    print(f"fused vs separate: relative RMS difference {err:.2e}")
+    assert err < 5e-3
+    wtok, wlog = oracle_model.step(nm, ids, q_lens, ctx_lens, bt)
+    assert H.rel_rms_err(logits.cpu().numpy(), wlog) < 1e-2 and H.rel_rms_err(logits2.cpu().numpy(), wlog) < 1e-2
+    assert np.array_equal(tok.cpu().numpy(), wtok)
+    assert np.array_equal(tok.cpu().numpy(), tok2.cpu().numpy())
+    assert fused_launches == plain_launches - 3 * 2           # three transform launches fewer per layer
+
+
 @pytest.mark.parametrize("kv_bits", [0, 4])
 def test_multi_step_greedy_generation_with_page_allocator(ctx, kv_bits):
     """A continuous batch over many steps: ragged prefill of four prompts, then 20 greedy decode steps, on pools and pages

@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
                                                          const int32_t* __restrict__ cu_q, int bsz, int q_len,
                                                          int kv_append, int G, int rows_per_cta, int rows_lo, int rows_hi, int chunk_mult, int target_items,
                                                          int max_items, AttnPlan* plan, AttnItem* items, int* seq_base,
-                                                         int* seq_splits, int* order, int causal, int* status)
+                                                         int* seq_splits, int* order, int causal, int slots, int* status)
 {
     __shared__ long long s_total;
     __shared__ int s_scan[1024];
@@ -37,14 +37,40 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const int32_t* __restri
     }
     atomicAdd((unsigned long long*)&s_total, (unsigned long long)local);
     __syncthreads();
-    if (tid == 0) {
-        long long c = (s_total + target_items - 1) / target_items;
+    // Keys per split: total work / target_items.  slots > 0 (kernels whose CTAs are whole items, target_items = two per CTA
+    // slot): one item per slot instead when that already gives two or more items per slot, because every row block and
+    // every sequence rounds its split count up.  Then the longest-first order balances the slots and fewer items save the
+    // fixed cost of a CTA and the partials (four 256-row chunks: 125 us at one item per slot, 135 at two, 150 at three; 32
+    // x 8 verify rows: 125 against 133 us), while a batch of few long items (one 256-row chunk over 32768 keys: 20 items
+    // on 18 slots) keeps the finer split.
+    auto chunk_for = [&](long long t) {
+        long long c = (s_total + t - 1) / t;
         c = (c + chunk_mult - 1) / chunk_mult * chunk_mult;       // splits start on a key-tile boundary of the kernel
         if (c < 256) c = 256;
         if (c > (1 << 30)) c = 1 << 30;
-        s_chunk = (int)c;
+        return (int)c;
+    };
+    if (slots <= 0) {
+        if (tid == 0) s_chunk = chunk_for(target_items);
+        __syncthreads();
+    } else {
+        __shared__ long long s_count;
+        const int c1 = chunk_for(slots);
+        if (tid == 0) s_count = 0;
+        __syncthreads();
+        long long cnt = 0;
+        for (int b = tid; b < bsz; b += 1024) {
+            const int ql = cu_q ? cu_q[b + 1] - cu_q[b] : q_len;
+            const int tk = (seqlens ? seqlens[b] : 0) + (cu_q ? ql : kv_append);
+            const int pr = ql * G;
+            const int rb = (pr > rows_lo && pr <= rows_hi) ? (pr + rows_per_cta - 1) / rows_per_cta : 0;
+            cnt += (long long)rb * (tk > 0 ? (tk + c1 - 1) / c1 : 1);
+        }
+        atomicAdd((unsigned long long*)&s_count, (unsigned long long)cnt);
+        __syncthreads();
+        if (tid == 0) s_chunk = s_count >= 2LL * slots ? c1 : chunk_for(target_items);
+        __syncthreads();
     }
-    __syncthreads();
     const int chunk = s_chunk;
     for (int b0 = 0; b0 < bsz; b0 += 1024) {
         const int b = b0 + tid;
@@ -392,7 +418,8 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     static const bool no_lpt = getenv("EXL3_TUNE_NO_LPT") != nullptr;
     if (!(keep && ctx->plan_valid[cls])) {
         attn_plan_kernel<<<1, 1024, 0, st>>>(p.seqlens, p.cu_q, p.bsz, p.q_len, p.kv_append, G, rows_per_cta, rows_lo, rows_hi,
-                                              use_tc ? ATC_TN : AT_TK, target_items, max_items, plan, items, seq_base, seq_splits, order, no_lpt ? -1 : (p.causal ? 1 : 0), ctx->status);
+                                              use_tc ? ATC_TN : AT_TK, target_items, max_items, plan, items, seq_base, seq_splits, order, no_lpt ? -1 : (p.causal ? 1 : 0),
+                                              (use_tc && !tc_items) ? grid_x : 0, ctx->status);
         ctx->launches++;
         if (keep) ctx->plan_valid[cls] = 1;
     }

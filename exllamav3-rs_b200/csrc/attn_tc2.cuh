@@ -91,6 +91,22 @@ __global__ void __launch_bounds__(a2_threads(H), 1) attn_tc2_kernel(const __grid
     const int n_tiles = k_end > k_begin ? (k_end - k_begin + A2_TN - 1) / A2_TN : 0;
     const int32_t* bt = p.block_table + (size_t)b * p.pps;
 
+    // Softmax thread = (row, part h of a tile's keys).  Its 128 / H dims of the Q row are requested here, before the
+    // barriers and the TMEM allocation are set up: a global-memory round trip on a busy GPU is as long as that set-up.
+    constexpr int QCH = 16 / H;                                  // 16-byte chunks per thread
+    const int sm_q = warp & 3, sm_h = warp >> 2;
+    const int sm_lr = sm_q * 32 + lane;
+    const int sm_row = r0 + sm_lr;
+    const int sm_qidx = sm_row / G;
+    const bool sm_valid = warp < NSW && sm_row < ql * G;
+    const int sm_head = kvh * G + (sm_row - sm_qidx * G);
+    uint4 qv[QCH];
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(row_base + sm_qidx) * p.nq + sm_head) * A2_D) + sm_h * QCH;
+        #pragma unroll
+        for (int c = 0; c < QCH; ++c) qv[c] = sm_valid ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+    }
+
     if (tid == 0) {
         s_failed = 0;
         mbar_init(q_full, NSW);
@@ -198,23 +214,14 @@ __global__ void __launch_bounds__(a2_threads(H), 1) attn_tc2_kernel(const __grid
         }
     } else if (warp < NSW) {
         // ===== softmax: thread = (row, part h of the tile's keys)
-        const int q = warp & 3, h = warp >> 2;
-        const int lr = q * 32 + lane;
-        const int row = r0 + lr;
-        const int qidx = row / G;
-        const bool valid = row < ql * G;
-        const int head = kvh * G + (row - qidx * G);
+        const int q = sm_q, h = sm_h, lr = sm_lr, qidx = sm_qidx, head = sm_head;
+        const bool valid = sm_valid;
         const int lim = valid ? (p.causal ? min(total_k, total_k - ql + qidx + 1) : total_k) : 0;
-        {   // this thread's 128 / H dims of its Q row -> shared memory, K-major 128B-swizzled (two 64-wide d blocks)
-            constexpr int CH = 16 / H;                           // 16-byte chunks per thread
-            const int c0 = h * CH;                               // first chunk of the row's 16
-            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(row_base + qidx) * p.nq + head) * A2_D) + c0;
+        {   // Q row part -> shared memory, K-major 128B-swizzled (two 64-wide d blocks)
+            const int c0 = h * QCH;                              // first chunk of the row's 16
             uint8_t* qs = smem + A2_OFF_Q + (c0 >> 3) * (A2_ROWS * 128) + lr * 128;
             #pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                const uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(qs + ((((c0 & 7) + c) ^ (lr & 7)) << 4)) = v;
-            }
+            for (int c = 0; c < QCH; ++c) *reinterpret_cast<uint4*>(qs + ((((c0 & 7) + c) ^ (lr & 7)) << 4)) = qv[c];
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(q_full);
@@ -329,35 +336,59 @@ __global__ void __launch_bounds__(a2_threads(H), 1) attn_tc2_kernel(const __grid
             if (!ok) failed = true;
         }
         if (!failed && n_tiles > 0 && !mbar_wait_sleep_warp(o_full, 0)) failed = true;
+        // Split-KV partials ([128 rows][D + 2] floats per item and kv head) go through shared memory: written by each
+        // thread straight to its own row, a store instruction touched 32 rows = 32 sectors for 256 bytes, and the 32 such
+        // instructions per thread took 6400 cycles per CTA; staged, a warp writes whole rows.  The K/V ring is idle by now
+        // (the last PV product has completed, nothing is in flight).
+        constexpr int SROW = A2_D + 4;                            // staging row stride in floats: 16-byte aligned, conflict-free
+        float* stage = reinterpret_cast<float*>(smem + A2_OFF_KV);
+        static_assert(A2_ROWS * (A2_D + 4) * 4 <= A2_KV_SLOTS * A2_KV_SLOT, "staging fits the K/V ring");
         if (!failed) {
             tc_fence_after();
             const float inv = (splits == 1) ? (l_run > 0.f ? 1.0f / l_run : 0.f) : 1.0f;
             half* orow = p.o + ((size_t)(row_base + qidx) * p.nq + head) * A2_D + h * KPT;
-            float* pp = p.partial + (((size_t)item_idx * p.nkv + kvh) * A2_ROWS + lr) * (A2_D + 2);
-            #pragma unroll 1
+            float oall[KPT];
+            if (n_tiles > 0) {
+                #pragma unroll
+                for (int c = 0; c < KPT / 32; ++c) tc_ld32(tmem_o + c * 32, *reinterpret_cast<float (*)[32]>(&oall[c * 32]));
+                tc_wait_ld();
+            } else {
+                #pragma unroll
+                for (int e = 0; e < KPT; ++e) oall[e] = 0.f;
+            }
+            #pragma unroll
             for (int c = 0; c < KPT / 32; ++c) {
-                float ov[32];
-                if (n_tiles > 0) {
-                    tc_ld32(tmem_o + c * 32, ov);
-                    tc_wait_ld();
-                } else {
-                    #pragma unroll
-                    for (int e = 0; e < 32; ++e) ov[e] = 0.f;
-                }
-                if (valid) {
-                    if (splits == 1) {
+                const float* ov = &oall[c * 32];
+                if (splits == 1) {
+                    if (valid) {
                         uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
                         #pragma unroll
                         for (int e = 0; e < 4; ++e)
                             dst[e] = make_uint4(pack_h2(ov[e * 8] * inv, ov[e * 8 + 1] * inv), pack_h2(ov[e * 8 + 2] * inv, ov[e * 8 + 3] * inv),
                                                 pack_h2(ov[e * 8 + 4] * inv, ov[e * 8 + 5] * inv), pack_h2(ov[e * 8 + 6] * inv, ov[e * 8 + 7] * inv));
-                    } else {
-                        #pragma unroll
-                        for (int e = 0; e < 32; e += 2) *reinterpret_cast<float2*>(pp + h * KPT + c * 32 + e) = make_float2(ov[e], ov[e + 1]);
                     }
+                } else {
+                    float4* dst = reinterpret_cast<float4*>(stage + lr * SROW + h * KPT + c * 32);
+                    #pragma unroll
+                    for (int e = 0; e < 8; ++e) dst[e] = make_float4(ov[4 * e], ov[4 * e + 1], ov[4 * e + 2], ov[4 * e + 3]);
                 }
             }
-            if (valid && splits != 1 && h == 0) { pp[A2_D] = m_used; pp[A2_D + 1] = l_run; }
+            if (splits != 1 && h == 0) { stage[lr * SROW + A2_D] = m_used; stage[lr * SROW + A2_D + 1] = l_run; }
+        }
+        if (splits != 1) {                                        // CTA-uniform
+            // every softmax warp comes here exactly once, whatever its `failed`
+            asm volatile("bar.sync 1, %0;" ::"n"(NSW * 32) : "memory");
+            if (!failed) {
+                float* pbase = p.partial + ((size_t)item_idx * p.nkv + kvh) * A2_ROWS * (A2_D + 2);
+                const int n_valid = min(A2_ROWS, ql * G - r0);    // valid rows of this block are its first ones
+                for (int r = warp; r < n_valid; r += NSW) {
+                    const float2* srow = reinterpret_cast<const float2*>(stage + r * SROW);
+                    float2* drow = reinterpret_cast<float2*>(pbase + (size_t)r * (A2_D + 2));
+                    drow[lane] = srow[lane];
+                    drow[lane + 32] = srow[lane + 32];
+                    if (lane == 0) drow[64] = srow[64];
+                }
+            }
         }
     }
 

@@ -290,7 +290,7 @@ EncodeTiledFn get_encode_tiled()
 constexpr int TC_MAX_SMALL_M = 0;           // row counts up to this stay on the mma.sync small-M kernel (0: none do)
 
 template <int K, int CB, int CTAS, int BN>
-cudaError_t launch_tc(const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc(const CUtensorMap* amap, const CUtensorMap* rmap, const CUtensorMap* cmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
     constexpr int bytes = TcSmem<K, CTAS, BN>::BYTES;
     static bool configured[64] = {};
@@ -312,35 +312,35 @@ cudaError_t launch_tc(const CUtensorMap* amap, const CUtensorMap* rmap, const Ge
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, amap[0], amap[1], amap[2], rmap[0], rmap[1], rmap[2], p);
+    return cudaLaunchKernelEx(&cfg, kern, amap[0], amap[1], amap[2], rmap[0], rmap[1], rmap[2], cmap[0], cmap[1], cmap[2], p);
 }
 
 template <int K, int CB>
-cudaError_t launch_tc_ctas(bool pair, int bn, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc_ctas(bool pair, int bn, const CUtensorMap* amap, const CUtensorMap* rmap, const CUtensorMap* cmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
-    if (pair && bn == 128) return launch_tc<K, CB, 2, 128>(amap, rmap, p, slabs, st);
-    return pair ? launch_tc<K, CB, 2, 256>(amap, rmap, p, slabs, st) : launch_tc<K, CB, 1, 256>(amap, rmap, p, slabs, st);
+    if (pair && bn == 128) return launch_tc<K, CB, 2, 128>(amap, rmap, cmap, p, slabs, st);
+    return pair ? launch_tc<K, CB, 2, 256>(amap, rmap, cmap, p, slabs, st) : launch_tc<K, CB, 1, 256>(amap, rmap, cmap, p, slabs, st);
 }
 
 template <int K>
-cudaError_t launch_tc_cb(int cb, bool pair, int bn, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc_cb(int cb, bool pair, int bn, const CUtensorMap* amap, const CUtensorMap* rmap, const CUtensorMap* cmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
-    if (cb == 0) return launch_tc_ctas<K, 0>(pair, bn, amap, rmap, p, slabs, st);
-    if (cb == 1) return launch_tc_ctas<K, 1>(pair, bn, amap, rmap, p, slabs, st);
-    return launch_tc_ctas<K, 2>(pair, bn, amap, rmap, p, slabs, st);
+    if (cb == 0) return launch_tc_ctas<K, 0>(pair, bn, amap, rmap, cmap, p, slabs, st);
+    if (cb == 1) return launch_tc_ctas<K, 1>(pair, bn, amap, rmap, cmap, p, slabs, st);
+    return launch_tc_ctas<K, 2>(pair, bn, amap, rmap, cmap, p, slabs, st);
 }
 
-cudaError_t launch_tc_k(int K, int cb, bool pair, int bn, const CUtensorMap* amap, const CUtensorMap* rmap, const GemmTcParams& p, int slabs, cudaStream_t st)
+cudaError_t launch_tc_k(int K, int cb, bool pair, int bn, const CUtensorMap* amap, const CUtensorMap* rmap, const CUtensorMap* cmap, const GemmTcParams& p, int slabs, cudaStream_t st)
 {
     switch (K) {
-        case 1: return launch_tc_cb<1>(cb, pair, bn, amap, rmap, p, slabs, st);
-        case 2: return launch_tc_cb<2>(cb, pair, bn, amap, rmap, p, slabs, st);
-        case 3: return launch_tc_cb<3>(cb, pair, bn, amap, rmap, p, slabs, st);
-        case 4: return launch_tc_cb<4>(cb, pair, bn, amap, rmap, p, slabs, st);
-        case 5: return launch_tc_cb<5>(cb, pair, bn, amap, rmap, p, slabs, st);
-        case 6: return launch_tc_cb<6>(cb, pair, bn, amap, rmap, p, slabs, st);
-        case 7: return launch_tc_cb<7>(cb, pair, bn, amap, rmap, p, slabs, st);
-        default: return launch_tc_cb<8>(cb, pair, bn, amap, rmap, p, slabs, st);
+        case 1: return launch_tc_cb<1>(cb, pair, bn, amap, rmap, cmap, p, slabs, st);
+        case 2: return launch_tc_cb<2>(cb, pair, bn, amap, rmap, cmap, p, slabs, st);
+        case 3: return launch_tc_cb<3>(cb, pair, bn, amap, rmap, cmap, p, slabs, st);
+        case 4: return launch_tc_cb<4>(cb, pair, bn, amap, rmap, cmap, p, slabs, st);
+        case 5: return launch_tc_cb<5>(cb, pair, bn, amap, rmap, cmap, p, slabs, st);
+        case 6: return launch_tc_cb<6>(cb, pair, bn, amap, rmap, cmap, p, slabs, st);
+        case 7: return launch_tc_cb<7>(cb, pair, bn, amap, rmap, cmap, p, slabs, st);
+        default: return launch_tc_cb<8>(cb, pair, bn, amap, rmap, cmap, p, slabs, st);
     }
 }
 
@@ -356,7 +356,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
     if (!enc) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled is not available from this driver");
     size_t off = 0;
     ProloguePlainArgs pa;
-    CUtensorMap amap[TC_MAX_SEG], rmap[TC_MAX_SEG];
+    CUtensorMap amap[TC_MAX_SEG], rmap[TC_MAX_SEG], cmap[TC_MAX_SEG];
     GemmTcParams p;
     memset(&p, 0, sizeof(p));
     // Slab width: 256 columns, or 128 when a single row block would put 256-column slabs on at most a quarter of the SMs
@@ -391,8 +391,19 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled failed for the trellis");
+            // the fp16 output as [m][n]: an epilogue warp stores its 32 rows x 128 columns as two boxes of 64 columns
+            if (!c_fp32) {
+                cuuint64_t cdims[2] = {(cuuint64_t)n[i], (cuuint64_t)m};
+                cuuint64_t cstrides[1] = {(cuuint64_t)n[i] * 2};
+                cuuint32_t cbox[2] = {64u, 32u};
+                r = enc(&cmap[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, C[i], cdims, cstrides, cbox, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                if (r != CUDA_SUCCESS) return exl3_fail(ctx, EXL3_ERR_CUDA, "exl3_gemm: cuTensorMapEncodeTiled failed for the output");
+            } else
+                cmap[i] = amap[i];                             // never dereferenced: fp32 outputs are stored by the threads
         } else {
-            pa.a_had[i] = pa.a_had[j]; pa.suh[i] = pa.suh[j]; amap[i] = amap[j]; rmap[i] = rmap[j];
+            pa.a_had[i] = pa.a_had[j]; pa.suh[i] = pa.suh[j]; amap[i] = amap[j]; rmap[i] = rmap[j]; cmap[i] = cmap[j];
         }
         p.trellis[i] = (const uint32_t*)trellis[j]; p.C[i] = C[j]; p.svh[i] = svh[j]; p.n[i] = n[j];
         p.blk_end[i] = i < nseg ? blocks : 0x7fffffff;
@@ -408,7 +419,7 @@ int gemm_tc_rows(exl3_ctx* ctx, cudaStream_t st, const half* A, int nseg, const 
         gemm_prologue_plain_kernel<<<dim3(m, nseg), 256, 0, st>>>(A, pa, k);
     if (!pre) ctx->launches++;
     p.status = ctx->status; p.m = m; p.k = k; p.c_fp32 = c_fp32;
-    cudaError_t e = launch_tc_k(K, cb, ctx->use_pair != 0, bn, amap, rmap, p, blocks, st);
+    cudaError_t e = launch_tc_k(K, cb, ctx->use_pair != 0, bn, amap, rmap, cmap, p, blocks, st);
     ctx->launches++;
     if (e != cudaSuccess) { cudaGetLastError(); return exl3_fail(ctx, EXL3_ERR_CUDA, cudaGetErrorString(e)); }
     return EXL3_OK;

@@ -68,6 +68,16 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+// shared -> global tensor store (rows and columns past the tensor's extent are clipped), committed as a bulk group
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_wait_read()
+{
+    asm volatile("cp.async.bulk.commit_group;\n\tcp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -237,7 +247,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                                                                const __grid_constant__ CUtensorMap amap2,
                                                                const __grid_constant__ CUtensorMap rmap0,
                                                                const __grid_constant__ CUtensorMap rmap1,
-                                                               const __grid_constant__ CUtensorMap rmap2, const GemmTcParams p)
+                                                               const __grid_constant__ CUtensorMap rmap2,
+                                                               const __grid_constant__ CUtensorMap cmap0,
+                                                               const __grid_constant__ CUtensorMap cmap1,
+                                                               const __grid_constant__ CUtensorMap cmap2, const GemmTcParams p)
 {
     using SM = TcSmem<K, CTAS, BN>;
     constexpr bool PAIR = CTAS == 2;
@@ -268,6 +281,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     const int row_t0 = m0 + rank * 128, row_t1 = row_t0 + 128 * CTAS;    // first rows of this CTA's two M tiles
     const CUtensorMap* amap = seg == 0 ? &amap0 : (seg == 1 ? &amap1 : &amap2);
     const CUtensorMap* rmap = seg == 0 ? &rmap0 : (seg == 1 ? &rmap1 : &rmap2);       // trellis as [k/16][row of uint64]
+    const CUtensorMap* cmap = seg == 0 ? &cmap0 : (seg == 1 ? &cmap1 : &cmap2);       // fp16 output [m][n], box 64 x 32, 128-byte swizzle
     // (selected with compares: indexing the parameter arrays with `seg` would put a copy of them in local memory)
     const uint32_t* trellis = seg == 0 ? p.trellis[0] : (seg == 1 ? p.trellis[1] : p.trellis[2]);
     const half* svh = seg == 0 ? p.svh[0] : (seg == 1 ? p.svh[1] : p.svh[2]);
@@ -479,6 +493,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             if ((mt == 0 || two_tiles) && sel * 128 < BN && n0 + sel * 128 < n) {
                 const int row = (mt ? row_t1 : row_t0) + q * 32 + lane;
                 const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + mt * BN + sel * 128;
+                uint8_t* stage_w = smem + SM::OFF_A + (warp - 2) * 8192;        // 8 KB of the idle activation ring per warp
                 // The 128-point transform of a row is split so that a thread never holds more than 32 accumulators:
                 // the two outer butterfly levels (strides 32 and 64) run on 8-column slices and go back to TMEM, the five
                 // inner levels run on each 32-column chunk as it is read for the store.
@@ -510,9 +525,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                         for (int e = 0; e < 32; ++e) v[e] *= TC_R128;
                     }
                     if (row < p.m) {
-                        const size_t off = (size_t)row * n + n0 + sel * 128 + j * 32;
-                        const half* sv = svh_s + j * 32;
                         if (p.c_fp32) {
+                            const size_t off = (size_t)row * n + n0 + sel * 128 + j * 32;
+                            const half* sv = svh_s + j * 32;
                             float4* dst = reinterpret_cast<float4*>((float*)Cout + off);
                             #pragma unroll
                             for (int e = 0; e < 32; e += 4) {
@@ -523,21 +538,40 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                                 }
                                 dst[e >> 2] = o;
                             }
-                        } else {
-                            uint4* dst = reinterpret_cast<uint4*>((half*)Cout + off);
-                            #pragma unroll
-                            for (int e = 0; e < 32; e += 8) {
-                                uint32_t w[4];
-                                #pragma unroll
-                                for (int h = 0; h < 4; ++h) {
-                                    half2 x = __floats2half2_rn(v[e + 2 * h], v[e + 2 * h + 1]);
-                                    if (svh) x = __hmul2(x, *reinterpret_cast<const half2*>(sv + e + 2 * h));
-                                    w[h] = *reinterpret_cast<uint32_t*>(&x);
-                                }
-                                dst[e >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
                         }
                     }
+                    if (!p.c_fp32) {
+                        // fp16 output: this warp's 32 rows x 128 columns go through shared memory (two boxes of 64 columns,
+                        // rows of 128 bytes, 16-byte chunks XORed with row & 7) and leave by two tensor stores.  Written
+                        // by each thread to its own row, a store instruction touched 32 rows - 32 half-used sectors - and
+                        // the 256 such instructions of a CTA took 12 500 cycles, 12 % of a 512-row item.  The activation
+                        // and weight rings are free by now: the accumulators are complete.
+                        const half* sv = svh_s + j * 32;
+                        uint8_t* box = stage_w + (j >> 1) * 4096 + lane * 128;
+                        #pragma unroll
+                        for (int e = 0; e < 32; e += 8) {
+                            uint32_t w[4];
+                            #pragma unroll
+                            for (int h = 0; h < 4; ++h) {
+                                half2 x = __floats2half2_rn(v[e + 2 * h], v[e + 2 * h + 1]);
+                                if (svh) x = __hmul2(x, *reinterpret_cast<const half2*>(sv + e + 2 * h));
+                                w[h] = *reinterpret_cast<uint32_t*>(&x);
+                            }
+                            const int chunk = (j & 1) * 4 + (e >> 3);
+                            *reinterpret_cast<uint4*>(box + ((chunk ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
+                if (!p.c_fp32) {
+                    fence_proxy_async();
+                    __syncwarp();
+                    const int row_w = (mt ? row_t1 : row_t0) + q * 32;          // first row of this warp
+                    if (lane == 0 && row_w < p.m) {
+                        tma_store_2d(cmap, stage_w, n0 + sel * 128, row_w);
+                        tma_store_2d(cmap, stage_w + 4096, n0 + sel * 128 + 64, row_w);
+                        bulk_commit_wait_read();
+                    }
+                    __syncwarp();
                 }
             }
         }

@@ -348,23 +348,35 @@ __global__ void __launch_bounds__(256) silu_mul_tail_kernel(const half* x, const
 
 // silu_mul_kernel whose result goes straight through the input transform of the EXL3 tensor that reads it (down_proj):
 // one warp per 128-block of a row, lane = 4 consecutive elements.
+constexpr int SH_BLOCKS = 4;          // 128-blocks per warp: their loads are all in flight before the first is used
 __global__ void __launch_bounds__(256) silu_mul_had_kernel(const half* __restrict__ x, const half* __restrict__ y,
                                                            const half* __restrict__ suh, half* __restrict__ a_had, long long blocks, int bpr)
 {
     const int lane = threadIdx.x & 31;
-    const long long blk = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (blk >= blocks) return;
-    const uint2 xr = reinterpret_cast<const uint2*>(x + blk * 128)[lane], yr = reinterpret_cast<const uint2*>(y + blk * 128)[lane];
-    const half2 one = __float2half2_rn(1.0f);
-    half2 z[2];
+    const long long blk0 = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * SH_BLOCKS;
+    if (blk0 >= blocks) return;
+    uint2 xr[SH_BLOCKS], yr[SH_BLOCKS];
     #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const half2 a = *reinterpret_cast<const half2*>(&xr.x + j), b = *reinterpret_cast<const half2*>(&yr.x + j);
-        const half2 rr = h2rcp(__hadd2(one, h2exp(__hneg2(a))));
-        z[j] = __hmul2(__hmul2(a, rr), b);
+    for (int u = 0; u < SH_BLOCKS; ++u) {
+        const long long blk = blk0 + u < blocks ? blk0 + u : blocks - 1;         // the tail repeats the last block
+        xr[u] = reinterpret_cast<const uint2*>(x + blk * 128)[lane];
+        yr[u] = reinterpret_cast<const uint2*>(y + blk * 128)[lane];
     }
-    const int col = (int)(blk % bpr) * 32 + lane;               // uint2 index inside the sign vector
-    reinterpret_cast<uint2*>(a_had + blk * 128)[lane] = had128_signed_lane(z[0], z[1], suh, col, lane);
+    const half2 one = __float2half2_rn(1.0f);
+    #pragma unroll
+    for (int u = 0; u < SH_BLOCKS; ++u) {
+        const long long blk = blk0 + u;
+        if (blk >= blocks) break;                                                // warp-uniform
+        half2 z[2];
+        #pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const half2 a = *reinterpret_cast<const half2*>(&xr[u].x + j), b = *reinterpret_cast<const half2*>(&yr[u].x + j);
+            const half2 rr = h2rcp(__hadd2(one, h2exp(__hneg2(a))));
+            z[j] = __hmul2(__hmul2(a, rr), b);
+        }
+        const int col = (int)(blk % bpr) * 32 + lane;           // uint2 index inside the sign vector
+        reinterpret_cast<uint2*>(a_had + blk * 128)[lane] = had128_signed_lane(z[0], z[1], suh, col, lane);
+    }
 }
 
 __global__ void __launch_bounds__(256) add_kernel(const half* __restrict__ x, const half* __restrict__ y,
@@ -617,7 +629,7 @@ int exl3_silu_mul_pre(exl3_ctx* ctx, exl3_stream stream, const void* x, const vo
     EXL3_REQUIRE(aligned16(x) && aligned16(y), "silu_mul (fused transform): pointers must be 16-byte aligned");
     if (rows == 0) return EXL3_OK;
     const long long blocks = (long long)rows * (dim / 128);
-    silu_mul_had_kernel<<<(unsigned)((blocks + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const half*)x, (const half*)y, pre->suh[0], pre->a_had[0],
+    silu_mul_had_kernel<<<(unsigned)((blocks + 8 * SH_BLOCKS - 1) / (8 * SH_BLOCKS)), 256, 0, (cudaStream_t)stream>>>((const half*)x, (const half*)y, pre->suh[0], pre->a_had[0],
                                                                                       blocks, dim / 128);
     ctx->launches++;
     return exl3_check_launch(ctx, "silu_mul (fused transform)");

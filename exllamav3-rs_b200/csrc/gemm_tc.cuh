@@ -74,10 +74,6 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
 }
-__device__ __forceinline__ void bulk_commit_wait_read()
-{
-    asm volatile("cp.async.bulk.commit_group;\n\tcp.async.bulk.wait_group.read 0;" ::: "memory");
-}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -560,17 +556,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                             const int chunk = (j & 1) * 4 + (e >> 3);
                             *reinterpret_cast<uint4*>(box + ((chunk ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
+                        if (j & 1) {                                // a box of 64 columns is complete: it leaves while the next is computed
+                            fence_proxy_async();
+                            __syncwarp();
+                            const int row_w = (mt ? row_t1 : row_t0) + q * 32;          // first row of this warp
+                            if (lane == 0 && row_w < p.m) {
+                                tma_store_2d(cmap, stage_w + (j >> 1) * 4096, n0 + sel * 128 + (j >> 1) * 64, row_w);
+                                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            }
+                        }
                     }
                 }
                 if (!p.c_fp32) {
-                    fence_proxy_async();
-                    __syncwarp();
-                    const int row_w = (mt ? row_t1 : row_t0) + q * 32;          // first row of this warp
-                    if (lane == 0 && row_w < p.m) {
-                        tma_store_2d(cmap, stage_w, n0 + sel * 128, row_w);
-                        tma_store_2d(cmap, stage_w + 4096, n0 + sel * 128 + 64, row_w);
-                        bulk_commit_wait_read();
-                    }
+                    // the CTA may not leave (and free its shared memory) before the stores have read it
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                     __syncwarp();
                 }
             }

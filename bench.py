@@ -395,6 +395,17 @@ def run_ours(args):
     step_e2e()
     ms_e2e, _ = timed(step_e2e, args.steps)
     ctx.poll_status()
+    # per-stage device times of the same step, launched kernel by kernel with events at the stage boundaries (outside the
+    # timed regions; the graph replay above has no stage boundaries to time)
+    stages = None
+    if rank == 0:
+        ctx.stage_profile(True)
+        for _ in range(2):
+            model.step(ctx, d_ids, d_q, d_sl, d_bt, max_q, tokens_out=tok_static)
+        torch.cuda.synchronize()
+        stages, _ = ctx.stage_times(reset=True)
+        ctx.stage_profile(False)
+        stages = {k: round(v, 3) for k, v in stages.items()}
 
     ms_step = ms_total / args.steps
     rows_job = reduce_sum(rows, world, dev)             # every shard has the same row count; summed for the record
@@ -458,7 +469,7 @@ def run_ours(args):
                 "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": bsz * 8},
                 "gpu_launches": int(launches), "launch_mode": "cuda graph replay" if graph is not None else "stream launches",
-                "clocks": clocks, "roofline": roof, "roofline_decode": roof_decode, "cpu_baseline": cpu}
+                "stage_ms": stages, "clocks": clocks, "roofline": roof, "roofline_decode": roof_decode, "cpu_baseline": cpu}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -28,6 +28,8 @@ extern "C" int exl3_ctx_create(int device, size_t workspace_bytes, exl3_ctx** ou
     ctx->use_tc = getenv("EXL3_B200_NO_TC") ? 0 : 1;
     ctx->use_pair = getenv("EXL3_B200_NO_PAIR") ? 0 : 1;
     ctx->fuse_transform = getenv("EXL3_B200_NO_FUSED_TRANSFORM") ? 0 : 1;
+    ctx->stage_prof = 0; ctx->prof_ev = nullptr; ctx->prof_stage = nullptr; ctx->prof_ev_n = 0; ctx->stage_steps = 0;
+    for (int i = 0; i < EXL3_STAGES; ++i) ctx->stage_ms[i] = 0.0;
     ctx->use_decode = (getenv("EXL3_B200_NO_DECODE") || getenv("EXL3_B200_NO_TC")) ? 0 : 1;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete ctx; cudaGetLastError(); return EXL3_ERR_CUDA; }
@@ -70,12 +72,31 @@ extern "C" void exl3_ctx_destroy(exl3_ctx* ctx)
     if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->plan_slots) cudaFree(ctx->plan_slots);
+    for (int i = 0; i < ctx->prof_ev_n; ++i) cudaEventDestroy(ctx->prof_ev[i]);
+    delete[] ctx->prof_ev;
+    delete[] ctx->prof_stage;
     delete ctx;
 }
 
 extern "C" const char* exl3_last_error(const exl3_ctx* ctx) { return ctx ? ctx->err : "null context"; }
 
 extern "C" uint64_t exl3_ctx_launch_count(const exl3_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int exl3_ctx_stage_profile(exl3_ctx* ctx, int enable)
+{
+    if (!ctx) return EXL3_ERR_INVALID;
+    ctx->stage_prof = enable ? 1 : 0;
+    return EXL3_OK;
+}
+
+extern "C" int exl3_ctx_stage_times(exl3_ctx* ctx, double* ms, int* steps, int reset)
+{
+    if (!ctx || !ms) return EXL3_ERR_INVALID;
+    for (int i = 0; i < EXL3_STAGES; ++i) ms[i] = ctx->stage_ms[i];
+    if (steps) *steps = ctx->stage_steps;
+    if (reset) { for (int i = 0; i < EXL3_STAGES; ++i) ctx->stage_ms[i] = 0.0; ctx->stage_steps = 0; }
+    return EXL3_OK;
+}
 
 extern "C" int exl3_ctx_poll_status(exl3_ctx* ctx, exl3_stream stream)
 {

@@ -459,6 +459,8 @@ int attn_impl(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     // Decode class = sequences with at most 16 packed rows.  Over 4-bit pools it also takes up to 48 rows (speculative
     // verify: 8 query rows x 5 heads) as row blocks of 16 that each walk the codes again: the kernel that builds its
     // operands from the codes is that much cheaper per key than the generic one (4 verify sequences: 90 us per layer there).
+    // (Sending the decode rows of a ragged fp16 batch through the tcgen05 kernel as well, as items of 128 rows with 5 in
+    // use, was measured on the benchmark step: the attention stage takes the same 28.0 ms of the step's 83.)
     const int dec_rows = q4_decode_kernel_applies(p, quant) ? 48 : 16;
     if (max_rows <= dec_rows) return attn_pass(ctx, st, p, total_rows, max_rows, 0, dec_rows, true, quant, &off);
     if (!p.cu_q) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 1 << 30, false, quant, &off);

@@ -29,6 +29,11 @@ struct exl3_ctx {
     int use_tc;             // 1: tcgen05 GEMM for large M (default), 0: small-M kernel in passes (for A/B runs)
     int use_decode;         // 1: the streaming decode kernel takes calls of up to 16 rows (default), 0: they go the way of larger row counts
     int use_pair;           // 1: the tcgen05 GEMM runs on CTA pairs (cta_group::2, default), 0: one CTA per tile
+    // per-stage device times of exl3_step_forward (off by default): events recorded at the stage boundaries of a step that
+    // is not being captured, read back at its end
+    int stage_prof;
+    cudaEvent_t* prof_ev; int* prof_stage; int prof_ev_n;
+    double stage_ms[EXL3_STAGES]; int stage_steps;
     int fuse_transform;     // 1: in the step runner the norm / activation kernels write the tensor-core GEMM's transformed activations (default), 0: separate launches
     // Work lists of the attention kernels kept across the layers of one exl3_step_forward call (they depend on the batch's
     // lengths only, not on the layer): slot 0 = decode class, slot 1 = long class.  plan_keep is set for the duration of a

@@ -123,8 +123,59 @@ extern "C" int exl3_step_build_descriptors(exl3_ctx* ctx, exl3_stream stream, co
 
 #define STEP_TRY(expr) do { int rc_ = (expr); if (rc_ != EXL3_OK) return rc_; } while (0)
 
+// Stage boundaries of a profiled step: an event per boundary on the step's stream, read back when the step has been
+// issued.  Mirrors the reference's per-stage accumulators (EXL3_TRUNK_PROF, src/model.rs:72-116,158-187), which bracket
+// the stages with device synchronisations; here the step runs as it always does and only the last event is waited for.
+namespace {
+struct StageProf {
+    exl3_ctx* ctx; cudaStream_t st; int n;
+    void mark(int stage)
+    {
+        if (n < ctx->prof_ev_n && cudaEventRecord(ctx->prof_ev[n], st) == cudaSuccess) { ctx->prof_stage[n] = stage; ++n; }
+    }
+};
+}  // namespace
+#define STAGE(id) do { if (prof) prof->mark(id); } while (0)
+
+static int step_forward_impl(exl3_ctx* ctx, exl3_stream stream, const exl3_model* m, const exl3_batch* b,
+                             void* scratch, size_t scratch_bytes, int64_t* out_tokens, float* logits, StageProf* prof);
+
 extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_model* m, const exl3_batch* b,
                                  void* scratch, size_t scratch_bytes, int64_t* out_tokens, float* logits)
+{
+    EXL3_REQUIRE(ctx && m, "step_forward: null argument");
+    StageProf sp{ctx, (cudaStream_t)stream, 0};
+    StageProf* prof = nullptr;
+    if (ctx->stage_prof && m->n_layers > 0) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing((cudaStream_t)stream, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone) {
+            const int need = 3 + 5 * m->n_layers;           // start, embedding, five per layer, head
+            if (ctx->prof_ev_n < need) {
+                for (int i = 0; i < ctx->prof_ev_n; ++i) cudaEventDestroy(ctx->prof_ev[i]);
+                delete[] ctx->prof_ev; delete[] ctx->prof_stage;
+                ctx->prof_ev = new cudaEvent_t[need]; ctx->prof_stage = new int[need]; ctx->prof_ev_n = 0;
+                for (int i = 0; i < need; ++i) {
+                    if (cudaEventCreate(&ctx->prof_ev[i]) != cudaSuccess) break;
+                    ctx->prof_ev_n = i + 1;
+                }
+            }
+            if (ctx->prof_ev_n >= need) prof = &sp;
+        } else cudaGetLastError();
+    }
+    STAGE(0);
+    const int rc = step_forward_impl(ctx, stream, m, b, scratch, scratch_bytes, out_tokens, logits, prof);
+    if (prof && rc == EXL3_OK && sp.n > 1 && cudaEventSynchronize(ctx->prof_ev[sp.n - 1]) == cudaSuccess) {
+        for (int i = 1; i < sp.n; ++i) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, ctx->prof_ev[i - 1], ctx->prof_ev[i]) == cudaSuccess) ctx->stage_ms[ctx->prof_stage[i]] += ms;
+        }
+        ctx->stage_steps++;
+    }
+    return rc;
+}
+
+static int step_forward_impl(exl3_ctx* ctx, exl3_stream stream, const exl3_model* m, const exl3_batch* b,
+                             void* scratch, size_t scratch_bytes, int64_t* out_tokens, float* logits, StageProf* prof)
 {
     EXL3_REQUIRE(ctx && m && b && scratch && out_tokens, "step_forward: null argument");
     EXL3_REQUIRE(m->layers && m->n_layers > 0 && m->embed && m->final_norm && m->inv_freq, "step_forward: incomplete model");
@@ -147,6 +198,7 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
     STEP_TRY(exl3_step_build_descriptors(ctx, stream, b->q_lens, b->cache_seqlens, bsz, rows, s.cu_q, s.row_pos, s.last_row));
     STEP_TRY(exl3_embed(ctx, stream, b->ids, m->embed, s.resid, rows, hidden, m->vocab));
 
+    STAGE(0);                           // descriptors and embedding
     const half* pending = nullptr;      // output of the previous block's MLP, added to the residual by the next norm
     // (measured on the 27B-class shard: 84.6 against 85.3 ms at 1052 rows, but 22.7 against 22.5 ms at 32 rows, where the norm's
     // one CTA per row leaves the three transforms of a row to 32 CTAs: fused from 128 rows on)
@@ -168,6 +220,7 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
                 STEP_TRY(exl3_gemm_fanout(ctx, stream, s.a_in, 3, w, out, rows, 0));
             }
         }
+        STAGE(1);                       // attention norm + q/k/v
         STEP_TRY(exl3_rope(ctx, stream, s.q, nullptr, s.k, nullptr, m->inv_freq, m->n_freq, 0, nullptr, s.row_pos, L.q_norm, L.k_norm,
                            m->norm_eps, 0.f, m->rope_mode, m->attn_factor, 1, rows, m->nq, m->nkv, m->hd));
         if (m->kv_bits == 0)
@@ -179,7 +232,9 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
                                                b->cache_seqlens, s.cu_q, s.attn_o, bsz, b->max_q_len, rows, m->nq,
                                                m->nkv, m->hd, m->pages, b->pages_per_seq, m->kv_bits, m->kv_bits, 256, 1,
                                                0.f, 0.f));
+        STAGE(2);                       // rope, KV write, attention
         STEP_TRY(linear(ctx, stream, L.o_proj, s.attn_o, s.proj, rows, 0));
+        STAGE(3);                       // o_proj
         {
             const exl3_linear* w[2] = {&L.gate_proj, &L.up_proj};
             void* out[2] = {s.gate, s.up};
@@ -192,6 +247,7 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
                 STEP_TRY(exl3_gemm_fanout(ctx, stream, s.a_in, 2, w, out, rows, 0));
             }
         }
+        STAGE(4);                       // MLP norm + gate/up
         {
             const exl3_linear* w[1] = {&L.down_proj};
             void* out[1] = {s.proj};
@@ -204,6 +260,7 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
                 STEP_TRY(linear(ctx, stream, L.down_proj, s.act, s.proj, rows, 0));
             }
         }
+        STAGE(5);                       // activation + down_proj
         pending = s.proj;
     }
 
@@ -219,6 +276,7 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
             ctx->launches++;
             STEP_TRY(exl3_check_launch(ctx, "step advance"));
         }
+        STAGE(6);                       // final norm, lm_head, argmax
         return EXL3_OK;
     }
     // head: only the last row of every sequence (src/model.rs:1038-1050 last_only), logits in fp32
@@ -239,5 +297,6 @@ extern "C" int exl3_step_forward(exl3_ctx* ctx, exl3_stream stream, const exl3_m
         ctx->launches++;
         STEP_TRY(exl3_check_launch(ctx, "step advance"));
     }
+    STAGE(6);                           // final norm, lm_head, argmax
     return EXL3_OK;
 }

@@ -133,6 +133,21 @@ class Ctx:
     def launch_count(self):
         return int(lib().exl3_ctx_launch_count(self._h))
 
+    STAGES = ("descriptors + embedding", "attention norm + q/k/v", "rope + KV write + attention", "o_proj",
+              "MLP norm + gate/up", "activation + down_proj", "head")
+
+    def stage_profile(self, enable=True):
+        """Per-stage device times of the step runner (the reference's EXL3_TRUNK_PROF, src/model.rs:72-116)."""
+        self.check(lib().exl3_ctx_stage_profile(self._h, int(bool(enable))), "ctx_stage_profile")
+
+    def stage_times(self, reset=True):
+        """({stage name: ms per step}, profiled steps) since the last reset."""
+        ms = (C.c_double * len(self.STAGES))()
+        steps = C.c_int(0)
+        self.check(lib().exl3_ctx_stage_times(self._h, ms, C.byref(steps), int(bool(reset))), "ctx_stage_times")
+        n = max(steps.value, 1)
+        return {name: ms[i] / n for i, name in enumerate(self.STAGES)}, steps.value
+
     # ------------------------------------------------------------------------------------------ EXL3 linear
     def exl3_gemm(self, a, trellis, c, suh, a_had, svh, mcg=False, mul1=False, stream=None):
         """src/ffi.rs:274-291.  a [..,k] fp16, trellis [k/16,n/16,16K] int16, c [..,n] fp16|fp32."""

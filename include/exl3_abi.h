@@ -68,6 +68,14 @@ EXL3_API int  exl3_ctx_poll_status(exl3_ctx* ctx, exl3_stream stream);
  * returns EXL3_ERR_DEVICE_WAIT and later calls on the context work as before.  No counterpart in the reference (its
  * waits are unbounded spins, kernels/quant/exl3_gemm_inner.cuh barrier code). */
 EXL3_API int  exl3_selftest_bounded_wait(exl3_ctx* ctx, exl3_stream stream, uint32_t polls);
+/* Per-stage device times of exl3_step_forward, the counterpart of the reference's EXL3_TRUNK_PROF accumulators
+ * (src/model.rs:72-116,158-187).  While enabled, a step that is not being captured into a graph records an event at each
+ * stage boundary and waits for the last one before it returns.  Stages: 0 descriptors + embedding, 1 attention norm +
+ * q/k/v, 2 rope + KV write + attention, 3 o_proj, 4 MLP norm + gate/up, 5 activation + down_proj, 6 head. */
+#define EXL3_STAGES 7
+EXL3_API int exl3_ctx_stage_profile(exl3_ctx* ctx, int enable);
+/* ms[EXL3_STAGES]: milliseconds summed over the `*steps` profiled steps since the last reset. */
+EXL3_API int exl3_ctx_stage_times(exl3_ctx* ctx, double* ms, int* steps, int reset);
 /* number of kernels this context has launched since creation (for launch accounting in benchmarks) */
 EXL3_API uint64_t exl3_ctx_launch_count(const exl3_ctx* ctx);
 EXL3_API const char* exl3_version(void);

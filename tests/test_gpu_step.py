@@ -125,6 +125,44 @@ def test_fused_input_transform_equals_separate_launches(ctx):
     assert fused_launches == plain_launches - 3 * 2           # three transform launches fewer per layer
 
 
+def test_stage_profile(ctx):
+    """The step runner's per-stage timer: off by default, sums device time per stage over the profiled steps, leaves the
+    step's results alone and stays out of a graph capture."""
+    import exl3b200
+    model, nm, ids, q_lens, ctx_lens, bt = _setup(0, 4, 1, [1, 8, 40], [300, 100, 0], 321, n_layers=2)
+    args = lambda: (H.to_dev(ids), H.to_dev(q_lens), H.to_dev(ctx_lens), H.to_dev(bt), int(q_lens.max()))  # noqa: E731
+    pools0 = [(L["k_cache"].clone(), L["v_cache"].clone()) for L in model.layers]
+    tok0, lg0 = model.step(ctx, *args(), want_logits=True)
+    times, steps = ctx.stage_times(reset=True)
+    assert steps == 0 and all(v == 0.0 for v in times.values())
+    ctx.stage_profile(True)
+    try:
+        for _ in range(3):
+            for L, (k0, v0) in zip(model.layers, pools0):
+                L["k_cache"].copy_(k0); L["v_cache"].copy_(v0)
+            tok1, lg1 = model.step(ctx, *args(), want_logits=True)
+        times, steps = ctx.stage_times(reset=True)
+        assert steps == 3
+        assert set(times) == set(ctx.STAGES) and all(v > 0.0 for v in times.values())
+        assert lg1.cpu().numpy().tobytes() == lg0.cpu().numpy().tobytes()
+        assert np.array_equal(tok1.cpu().numpy(), tok0.cpu().numpy())
+        # a captured step records nothing
+        g = exl3b200.CudaGraph(ctx)
+        import torch
+        tok_static = torch.empty(len(q_lens), dtype=torch.int64, device="cuda")
+        a = args()
+        g.capture_begin()
+        model.step(ctx, *a, stream=g.side_stream(), tokens_out=tok_static)
+        g.capture_end()
+        g.replay()
+        torch.cuda.synchronize()
+        _, steps = ctx.stage_times(reset=True)
+        assert steps == 0
+    finally:
+        ctx.stage_profile(False)
+    ctx.poll_status()
+
+
 @pytest.mark.parametrize("kv_bits", [0, 4])
 def test_multi_step_greedy_generation_with_page_allocator(ctx, kv_bits):
     """A continuous batch over many steps: ragged prefill of four prompts, then 20 greedy decode steps, on pools and pages

@@ -464,9 +464,12 @@ int attn_impl(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     const int dec_rows = q4_decode_kernel_applies(p, quant) ? 48 : 16;
     if (max_rows <= dec_rows) return attn_pass(ctx, st, p, total_rows, max_rows, 0, dec_rows, true, quant, &off);
     if (!p.cu_q) return attn_pass(ctx, st, p, total_rows, max_rows, 0, 1 << 30, false, quant, &off);
-    // Ragged batch with both classes: the decode-class pass (bound by HBM) runs on the context's second stream beside the
-    // long-class pass (bound by the tensor core and the MUFU); they touch disjoint sequences and output rows, and each
-    // has its own scratch.  Fork and join by events, which also works while the caller's stream is being captured.
+    // Ragged batch with both classes: the decode-class pass (bound by HBM) is issued on the context's second stream and
+    // the long-class pass (bound by the tensor core and the MUFU) on the caller's; they touch disjoint sequences and
+    // output rows, and each has its own scratch.  Fork and join by events, which also works while the caller's stream
+    // is being captured.  What the second stream buys is the tail of one pass filling with the other's first CTAs: a
+    // tcgen05 CTA takes a whole SM, so the bulk of the two passes runs one after the other (per layer of the benchmark
+    // step the attention stage takes the sum of the two kernels' times).
     if (cudaEventRecord(ctx->ev_fork, st) != cudaSuccess || cudaStreamWaitEvent(ctx->aux_stream, ctx->ev_fork, 0) != cudaSuccess)
         return exl3_fail(ctx, EXL3_ERR_CUDA, "attention: stream fork failed");
     int rc = attn_pass(ctx, ctx->aux_stream, p, total_rows, dec_rows, 0, dec_rows, true, quant, &off);

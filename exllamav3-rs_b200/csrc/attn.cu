@@ -376,11 +376,14 @@ int attn_pass(exl3_ctx* ctx, cudaStream_t st, AttnParams p, int total_rows, int 
     // tcgen05 kernels: two items per CTA slot: more items shorten the tail of the last wave but every extra KV split costs
     // a partial per kv head written and read back (128-row kernel on 4 x 256 query rows: 154 / 168 / 171 / 188 / 205 us at
     // 2 / 3 / 4 / 6 / 8 per slot).
-    // mma.sync kernels (units handed out dynamically, 8 KB partials): three per slot; four for the generic quantised
-    // kernel, which spends most of its time scaling codes and balances better on finer items (8-bit pools, 64 decode
-    // sequences: 510 us against 598 us).
+    // mma.sync kernels (units handed out dynamically, 8 KB partials): see below.
     static const int tc_items = getenv("EXL3_TUNE_TC_ITEMS") ? atoi(getenv("EXL3_TUNE_TC_ITEMS")) : 0;
-    const int target_items = grid_x * (use_tc ? (tc_items ? tc_items : 2) : ((quant && !use_q4) ? 4 : 3));
+    // With the units handed out longest first, fewer and longer items win on the mma.sync kernels too (64 decode
+    // sequences at 1 / 2 / 3 / 4 items per slot: fp16 pools 242 / 234 / 237 / 242 us, 4-bit pools 195 / 202 / 209 / 212 us;
+    // the 4-sequence verify step 21.5 / 22.0 / 22.6 / 23.2 ms; 8-bit pools on the generic kernel 532 / 548 / 550 us at 2 / 3 /
+    // 4): two, and one for the 4-bit kernel.
+    static const int dec_items = getenv("EXL3_TUNE_DEC_ITEMS") ? atoi(getenv("EXL3_TUNE_DEC_ITEMS")) : 0;
+    const int target_items = grid_x * (use_tc ? (tc_items ? tc_items : 2) : (dec_items ? dec_items : (use_q4 ? 1 : 2)));
     // items <= target + sum of row blocks (every (sequence, row block) rounds its split count up once); the row blocks are
     // bounded by bsz * rb_max and, usually much tighter for ragged batches, by total_rows * G / rows_per_cta + bsz
     const long long rb_sum = std::min((long long)p.bsz * rb_max, ((long long)total_rows * G + rows_per_cta - 1) / rows_per_cta + p.bsz);
